@@ -1,0 +1,549 @@
+// C ABI of the library (declared in include/chunk_attn_b200.h): argument checking, the context
+// that owns the device work lists and the partial-result scratch, and the launch sequence of one
+// decode step.  No torch, no exceptions across the boundary.
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstring>
+#include <new>
+#include <string>
+
+#include "../../include/chunk_attn_b200.h"
+#include "ca_kernels.h"
+#include "ca_plan.h"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const std::string& msg) {
+    g_last_error = msg;
+    return code;
+}
+int fail_cuda(cudaError_t e, const char* what) {
+    g_last_error = std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")";
+    return CA_ERR_CUDA;
+}
+#define CA_CUDA(call)                                        \
+    do {                                                     \
+        cudaError_t e__ = (call);                            \
+        if (e__ != cudaSuccess) return fail_cuda(e__, #call); \
+    } while (0)
+
+// Make the context's device current for the duration of a call and put the caller's back after.
+struct DeviceGuard {
+    int prev = -1;
+    bool changed = false;
+    cudaError_t err = cudaSuccess;
+    explicit DeviceGuard(int device) {
+        err = cudaGetDevice(&prev);
+        if (err == cudaSuccess && prev != device) {
+            err = cudaSetDevice(device);
+            changed = (err == cudaSuccess);
+        }
+    }
+    ~DeviceGuard() {
+        if (changed) cudaSetDevice(prev);
+    }
+};
+
+int esize_of(int dtype) { return dtype == CA_DTYPE_F16 ? 2 : (dtype == CA_DTYPE_F32 ? 4 : 0); }
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+}  // namespace
+
+struct ca_plan {
+    ca::Plan plan;
+};
+
+struct ca_context {
+    int device = 0;
+    int dtype = 0;
+    ca::Geometry geo{};
+    void* pool = nullptr;
+    int64_t max_chunks = 0;
+    int tpp_threshold = 1;
+    bool fast = false;
+    int num_sms = 1;
+    bool opt_split = false;
+    int opt_ctas = 0;
+
+    ca::Plan plan;
+    bool valid = false;
+    int delta_tokens = 0;
+    int max_tail_tokens = 0;
+
+    // work lists: one pinned staging buffer, one device buffer, one upload per refresh
+    char* host_blob = nullptr;
+    size_t host_cap = 0;
+    char* dev_blob = nullptr;
+    size_t dev_cap = 0;
+    cudaEvent_t upload_done = nullptr;
+    bool upload_pending = false;
+    // device views into dev_blob
+    const int4* d_items = nullptr;
+    const int32_t *d_tile_chunks = nullptr, *d_cta = nullptr, *d_cta_cf = nullptr, *d_cta_sf = nullptr;
+    const int32_t *d_merge_off = nullptr, *d_merge_slots = nullptr;
+    const int32_t *d_path_off = nullptr, *d_path_chunks = nullptr, *d_path_tokens = nullptr;
+    const int32_t *d_tail_chunk = nullptr, *d_tail_tokens = nullptr;
+
+    // partial results of the current step (scratch)
+    float* part_o = nullptr;
+    float2* part_ml = nullptr;
+    size_t part_cap = 0;  // slots
+    int* status = nullptr;
+};
+
+extern "C" {
+
+const char* ca_last_error(void) { return g_last_error.c_str(); }
+int ca_version(void) { return 100; }
+
+int64_t ca_chunk_bytes(int n_heads, int d_head, int chunk_size, int dtype) {
+    const int es = esize_of(dtype);
+    if (es == 0 || n_heads <= 0 || d_head <= 0 || chunk_size <= 0) return -1;
+    return (int64_t)n_heads * 2 * chunk_size * d_head * es;
+}
+
+int64_t ca_tile_elem_offset(int d_head, int dtype, int token, int elem) {
+    const int es = esize_of(dtype);
+    if (es == 0 || d_head <= 0 || token < 0 || elem < 0 || elem >= d_head) return -1;
+    const ca::Geometry g = ca::make_geometry(1, d_head, token + 1, es);
+    return ca::tile_elem_offset(g, token, elem);
+}
+
+int ca_context_create(ca_context** out, int device, int n_heads, int d_head, int chunk_size, int dtype,
+                      void* pool, int64_t max_chunks, int tpp_threshold) {
+    if (!out) return fail(CA_ERR_INVALID, "out is null");
+    *out = nullptr;
+    const int es = esize_of(dtype);
+    if (es == 0) return fail(CA_ERR_INVALID, "unsupported dtype (fp16 and fp32 only)");
+    if (n_heads <= 0 || d_head <= 0 || chunk_size <= 0) return fail(CA_ERR_INVALID, "n_heads, d_head, chunk_size must be positive");
+    if (d_head > 256) return fail(CA_ERR_INVALID, "d_head above 256 is not supported");
+    if (max_chunks < 0 || (max_chunks > 0 && !pool)) return fail(CA_ERR_INVALID, "pool is null");
+    if (reinterpret_cast<uintptr_t>(pool) % 256 != 0) return fail(CA_ERR_INVALID, "pool must be 256-byte aligned");
+    int n_dev = 0;
+    CA_CUDA(cudaGetDeviceCount(&n_dev));
+    if (device < 0 || device >= n_dev) return fail(CA_ERR_INVALID, "no such CUDA device");
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    cudaDeviceProp prop;
+    CA_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) return fail(CA_ERR_CUDA, "this library carries sm_100a code only; device is sm_" + std::to_string(prop.major * 10 + prop.minor));
+
+    ca_context* c = new (std::nothrow) ca_context();
+    if (!c) return fail(CA_ERR_INVALID, "out of host memory");
+    c->device = device;
+    c->dtype = dtype;
+    c->geo = ca::make_geometry(n_heads, d_head, chunk_size, es);
+    c->pool = pool;
+    c->max_chunks = max_chunks;
+    c->tpp_threshold = tpp_threshold < 1 ? 1 : tpp_threshold;
+    c->fast = (dtype == CA_DTYPE_F16 && d_head == ca::FAST_D && chunk_size == ca::FAST_C);
+    c->num_sms = prop.multiProcessorCount;
+    cudaError_t e = cudaEventCreateWithFlags(&c->upload_done, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaMalloc(&c->status, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(c->status, 0, sizeof(int));
+    if (e == cudaSuccess && c->fast) e = ca::configure_fast_kernels();
+    if (e != cudaSuccess) {
+        ca_context_destroy(c);
+        return fail_cuda(e, "context set-up");
+    }
+    *out = c;
+    return CA_OK;
+}
+
+void ca_context_destroy(ca_context* c) {
+    if (!c) return;
+    DeviceGuard guard(c->device);
+    if (c->upload_done) {
+        if (c->upload_pending) cudaEventSynchronize(c->upload_done);
+        cudaEventDestroy(c->upload_done);
+    }
+    if (c->host_blob) cudaFreeHost(c->host_blob);
+    if (c->dev_blob) cudaFree(c->dev_blob);
+    if (c->part_o) cudaFree(c->part_o);
+    if (c->part_ml) cudaFree(c->part_ml);
+    if (c->status) cudaFree(c->status);
+    delete c;
+}
+
+int ca_context_set_option(ca_context* c, int option, int64_t value) {
+    if (!c) return fail(CA_ERR_INVALID, "context is null");
+    if (option == CA_OPT_SPLIT_PHASES) {
+        c->opt_split = value != 0;
+    } else if (option == CA_OPT_NUM_CTAS) {
+        if (value < 0 || value > 4096) return fail(CA_ERR_INVALID, "CTA count out of range");
+        c->opt_ctas = (int)value;
+    } else {
+        return fail(CA_ERR_INVALID, "unknown option");
+    }
+    c->valid = false;  // schedules depend on the options
+    return CA_OK;
+}
+
+int ca_refresh_kernel_context(ca_context* c, const ca_chunk_info* infos, int n_infos, int n_seqs, ca_stream stream_) {
+    if (!c) return fail(CA_ERR_INVALID, "context is null");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    DeviceGuard guard(c->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    c->valid = false;
+    const int n_ctas = c->opt_ctas > 0 ? c->opt_ctas : c->num_sms;
+    std::string err = ca::build_plan(c->plan, infos, n_infos, n_seqs, c->geo.n_heads, c->geo.chunk_size,
+                                     c->tpp_threshold, n_ctas, c->max_chunks, c->opt_split, c->geo.d_head,
+                                     c->geo.esize, c->fast);
+    if (!err.empty()) return fail(CA_ERR_INVALID, "work list rejected: " + err);
+    const ca::Plan& pl = c->plan;
+
+    // pack every table into one staging buffer
+    struct Part { const void* src; size_t bytes; size_t off; };
+    Part parts[12] = {
+        {pl.items.data(), pl.items.size() * sizeof(ca::PlanItem), 0},
+        {pl.tile_chunks.data(), pl.tile_chunks.size() * 4, 0},
+        {pl.cta_item_begin.data(), pl.cta_item_begin.size() * 4, 0},
+        {pl.cta_item_begin_cf.data(), pl.cta_item_begin_cf.size() * 4, 0},
+        {pl.cta_item_begin_sf.data(), pl.cta_item_begin_sf.size() * 4, 0},
+        {pl.merge_off.data(), pl.merge_off.size() * 4, 0},
+        {pl.merge_slots.data(), pl.merge_slots.size() * 4, 0},
+        {pl.path_off.data(), pl.path_off.size() * 4, 0},
+        {pl.path_chunks.data(), pl.path_chunks.size() * 4, 0},
+        {pl.path_tokens.data(), pl.path_tokens.size() * 4, 0},
+        {pl.tail_chunk.data(), pl.tail_chunk.size() * 4, 0},
+        {pl.tail_tokens.data(), pl.tail_tokens.size() * 4, 0},
+    };
+    size_t total = 0;
+    for (Part& p : parts) {
+        p.off = total;
+        total += align_up(p.bytes, 256);
+    }
+    total = align_up(total + 256, 256);
+    if (c->upload_pending) {  // the previous upload may still be reading the staging buffer
+        CA_CUDA(cudaEventSynchronize(c->upload_done));
+        c->upload_pending = false;
+    }
+    if (total > c->host_cap) {
+        if (c->host_blob) CA_CUDA(cudaFreeHost(c->host_blob));
+        c->host_blob = nullptr;
+        c->host_cap = 0;
+        const size_t cap = align_up(total * 3 / 2, 4096);
+        CA_CUDA(cudaMallocHost(reinterpret_cast<void**>(&c->host_blob), cap));
+        c->host_cap = cap;
+    }
+    if (total > c->dev_cap) {
+        if (c->dev_blob) CA_CUDA(cudaFree(c->dev_blob));  // synchronises with work that still reads it
+        c->dev_blob = nullptr;
+        c->dev_cap = 0;
+        const size_t cap = align_up(total * 3 / 2, 4096);
+        CA_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->dev_blob), cap));
+        c->dev_cap = cap;
+    }
+    for (const Part& p : parts)
+        if (p.bytes) std::memcpy(c->host_blob + p.off, p.src, p.bytes);
+    CA_CUDA(cudaMemcpyAsync(c->dev_blob, c->host_blob, total, cudaMemcpyHostToDevice, stream));
+    CA_CUDA(cudaEventRecord(c->upload_done, stream));
+    c->upload_pending = true;
+    c->d_items = reinterpret_cast<const int4*>(c->dev_blob + parts[0].off);
+    c->d_tile_chunks = reinterpret_cast<const int32_t*>(c->dev_blob + parts[1].off);
+    c->d_cta = reinterpret_cast<const int32_t*>(c->dev_blob + parts[2].off);
+    c->d_cta_cf = reinterpret_cast<const int32_t*>(c->dev_blob + parts[3].off);
+    c->d_cta_sf = reinterpret_cast<const int32_t*>(c->dev_blob + parts[4].off);
+    c->d_merge_off = reinterpret_cast<const int32_t*>(c->dev_blob + parts[5].off);
+    c->d_merge_slots = reinterpret_cast<const int32_t*>(c->dev_blob + parts[6].off);
+    c->d_path_off = reinterpret_cast<const int32_t*>(c->dev_blob + parts[7].off);
+    c->d_path_chunks = reinterpret_cast<const int32_t*>(c->dev_blob + parts[8].off);
+    c->d_path_tokens = reinterpret_cast<const int32_t*>(c->dev_blob + parts[9].off);
+    c->d_tail_chunk = reinterpret_cast<const int32_t*>(c->dev_blob + parts[10].off);
+    c->d_tail_tokens = reinterpret_cast<const int32_t*>(c->dev_blob + parts[11].off);
+
+    // partial-result scratch, grow-only
+    const size_t slots = (size_t)pl.stats.n_slots;
+    if (slots > c->part_cap) {
+        if (c->part_o) CA_CUDA(cudaFree(c->part_o));
+        if (c->part_ml) CA_CUDA(cudaFree(c->part_ml));
+        c->part_o = nullptr;
+        c->part_ml = nullptr;
+        c->part_cap = 0;
+        const size_t cap = slots * 3 / 2 + 64;
+        CA_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->part_o), cap * ca::FAST_D * sizeof(float)));
+        CA_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->part_ml), cap * sizeof(float2)));
+        c->part_cap = cap;
+    }
+    c->max_tail_tokens = 0;
+    for (int32_t t : pl.tail_tokens) c->max_tail_tokens = t > c->max_tail_tokens ? t : c->max_tail_tokens;
+    c->delta_tokens = 0;
+    c->valid = true;
+    return CA_OK;
+}
+
+int ca_context_delta_tokens(const ca_context* c) { return c ? c->delta_tokens : -1; }
+
+int ca_append_kv(ca_context* c, const void* k, const void* v, int n_seqs, ca_stream stream_) {
+    if (!c) return fail(CA_ERR_INVALID, "context is null");
+    if (!c->valid) return fail(CA_ERR_STATE, "work list is stale: call ca_refresh_kernel_context first");
+    if (n_seqs != c->plan.n_seqs) return fail(CA_ERR_INVALID, "n_seqs differs from the refreshed work list");
+    if (n_seqs == 0) return CA_OK;
+    if (!k || !v) return fail(CA_ERR_INVALID, "k or v is null");
+    if (c->max_tail_tokens + c->delta_tokens >= c->geo.chunk_size)
+        return fail(CA_ERR_STATE, "a tail chunk is full: reserve a new tail and refresh before appending");
+    DeviceGuard guard(c->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    ca::AppendParams p;
+    p.pool = c->pool;
+    p.geo = c->geo;
+    p.k = k;
+    p.v = v;
+    p.tail_chunk = c->d_tail_chunk;
+    p.tail_tokens = c->d_tail_tokens;
+    p.n_seqs = n_seqs;
+    p.delta_tokens = c->delta_tokens;
+    const bool vec16 = c->geo.epg > 1 && reinterpret_cast<uintptr_t>(k) % 16 == 0 && reinterpret_cast<uintptr_t>(v) % 16 == 0;
+    CA_CUDA(ca::launch_append_kv(p, vec16, static_cast<cudaStream_t>(stream_)));
+    c->delta_tokens += 1;
+    return CA_OK;
+}
+
+static int check_attention_args(ca_context* c, const void* q, int n_seqs) {
+    if (!c) return fail(CA_ERR_INVALID, "context is null");
+    if (!c->valid) return fail(CA_ERR_STATE, "work list is stale: call ca_refresh_kernel_context first");
+    if (n_seqs != c->plan.n_seqs) return fail(CA_ERR_INVALID, "n_seqs differs from the refreshed work list");
+    if (n_seqs > 0 && !q) return fail(CA_ERR_INVALID, "q is null");
+    if (reinterpret_cast<uintptr_t>(q) % 16 != 0 && c->fast) return fail(CA_ERR_INVALID, "q must be 16-byte aligned");
+    return CA_OK;
+}
+
+int ca_attn_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_stream stream_) {
+    int rc = check_attention_args(c, q, n_seqs);
+    if (rc != CA_OK) return rc;
+    if (!c->fast) return fail(CA_ERR_INVALID, "partials exist only for fp16 / d_head 128 / chunk_size 64");
+    if (phases < 1 || phases > 3) return fail(CA_ERR_INVALID, "phases must be 1, 2 or 3");
+    if (phases != 3 && !c->plan.split_phases) return fail(CA_ERR_STATE, "single phases need CA_OPT_SPLIT_PHASES");
+    if (n_seqs == 0) return CA_OK;
+    DeviceGuard guard(c->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    ca::PartialParams p;
+    p.pool = static_cast<const uint8_t*>(c->pool);
+    p.n_heads = c->geo.n_heads;
+    p.q = q;
+    p.items = c->d_items;
+    p.tile_chunks = c->d_tile_chunks;
+    p.part_o = c->part_o;
+    p.part_ml = c->part_ml;
+    p.delta_tokens = c->delta_tokens;
+    p.scale_log2 = 1.4426950408889634f / std::sqrt((float)c->geo.d_head);
+    p.status = c->status;
+    if (!c->plan.split_phases) {
+        p.cta_item_begin = c->d_cta;
+        CA_CUDA(ca::launch_attn_partials(p, (int)c->plan.cta_item_begin.size() - 1, stream));
+    } else {
+        if ((phases & 1) && c->plan.n_items_cf > 0) {
+            p.cta_item_begin = c->d_cta_cf;
+            CA_CUDA(ca::launch_attn_partials(p, (int)c->plan.cta_item_begin_cf.size() - 1, stream));
+        }
+        if (phases & 2) {
+            p.cta_item_begin = c->d_cta_sf;
+            CA_CUDA(ca::launch_attn_partials(p, (int)c->plan.cta_item_begin_sf.size() - 1, stream));
+        }
+    }
+    return CA_OK;
+}
+
+int ca_attn_merge(ca_context* c, void* out, int n_seqs, ca_stream stream_) {
+    int rc = check_attention_args(c, out, n_seqs);
+    if (rc != CA_OK) return rc;
+    if (!c->fast) return fail(CA_ERR_INVALID, "partials exist only for fp16 / d_head 128 / chunk_size 64");
+    if (n_seqs == 0) return CA_OK;
+    DeviceGuard guard(c->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    ca::MergeParams m;
+    m.part_o = c->part_o;
+    m.part_ml = c->part_ml;
+    m.merge_off = c->d_merge_off;
+    m.merge_slots = c->d_merge_slots;
+    m.out = out;
+    m.n_pairs = n_seqs * c->geo.n_heads;
+    CA_CUDA(ca::launch_attn_merge(m, static_cast<cudaStream_t>(stream_), true));
+    return CA_OK;
+}
+
+int ca_attention(ca_context* c, const void* q, void* out, int n_seqs, int partition, ca_stream stream_) {
+    int rc = check_attention_args(c, q, n_seqs);
+    if (rc != CA_OK) return rc;
+    if (partition < 0 || partition > 2) return fail(CA_ERR_INVALID, "Unsupported partition type");
+    if (n_seqs == 0) return CA_OK;
+    if (!out) return fail(CA_ERR_INVALID, "out is null");
+    if (c->fast && partition != CA_PARTITION_SEQ_FIRST) {
+        rc = ca_attn_partials(c, q, n_seqs, 3, stream_);
+        if (rc != CA_OK) return rc;
+        return ca_attn_merge(c, out, n_seqs, stream_);
+    }
+    DeviceGuard guard(c->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    ca::GenericParams g;
+    g.pool = c->pool;
+    g.geo = c->geo;
+    g.q = q;
+    g.out = out;
+    g.path_off = c->d_path_off;
+    g.path_chunks = c->d_path_chunks;
+    g.path_tokens = c->d_path_tokens;
+    g.n_seqs = n_seqs;
+    g.delta_tokens = c->delta_tokens;
+    g.scale = 1.0f / std::sqrt((float)c->geo.d_head);
+    CA_CUDA(ca::launch_attn_seq_generic(g, c->dtype, static_cast<cudaStream_t>(stream_)));
+    return CA_OK;
+}
+
+int ca_scatter_prefill(ca_context* c, const void* k, const void* v, int64_t stride_token, int64_t stride_head,
+                       int first_token, int n_tokens, const int32_t* chunk_ids, ca_stream stream_) {
+    if (!c) return fail(CA_ERR_INVALID, "context is null");
+    if (n_tokens < 0 || first_token < 0) return fail(CA_ERR_INVALID, "negative token range");
+    if (n_tokens == 0) return CA_OK;
+    if (!k || !v || !chunk_ids) return fail(CA_ERR_INVALID, "k, v or chunk_ids is null");
+    const int C = c->geo.chunk_size;
+    const int n_chunks = (n_tokens + C - 1) / C;
+    for (int i = 0; i < n_chunks; i++)
+        if (chunk_ids[i] < 0 || chunk_ids[i] >= c->max_chunks) return fail(CA_ERR_INVALID, "chunk id outside the pool");
+    DeviceGuard guard(c->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    const int es = c->geo.esize;
+    const char* kb = static_cast<const char*>(k) + (int64_t)first_token * stride_token * es;
+    const char* vb = static_cast<const char*>(v) + (int64_t)first_token * stride_token * es;
+    // 16-byte moves need every source row to start on a 16-byte boundary
+    const bool vec16 = c->geo.epg > 1 && reinterpret_cast<uintptr_t>(kb) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(vb) % 16 == 0 && (stride_token * es) % 16 == 0 &&
+                       (stride_head * es) % 16 == 0;
+    for (int c0 = 0; c0 < n_chunks; c0 += ca::SCATTER_MAX_CHUNKS) {
+        const int nc = n_chunks - c0 < ca::SCATTER_MAX_CHUNKS ? n_chunks - c0 : ca::SCATTER_MAX_CHUNKS;
+        ca::ScatterParams p;
+        p.pool = c->pool;
+        p.geo = c->geo;
+        p.k = kb + (int64_t)c0 * C * stride_token * es;
+        p.v = vb + (int64_t)c0 * C * stride_token * es;
+        p.stride_token = stride_token;
+        p.stride_head = stride_head;
+        const int tok_end = (c0 + nc) * C < n_tokens ? (c0 + nc) * C : n_tokens;
+        p.n_tokens = tok_end - c0 * C;
+        std::memcpy(p.chunk_ids, chunk_ids + c0, nc * sizeof(int32_t));
+        CA_CUDA(ca::launch_scatter_prefill(p, vec16, static_cast<cudaStream_t>(stream_)));
+    }
+    return CA_OK;
+}
+
+int ca_copy_chunks(ca_context* c, const int32_t* src_ids, const int32_t* dst_ids, int n, ca_stream stream_) {
+    if (!c) return fail(CA_ERR_INVALID, "context is null");
+    if (n < 0) return fail(CA_ERR_INVALID, "negative count");
+    if (n == 0) return CA_OK;
+    if (!src_ids || !dst_ids) return fail(CA_ERR_INVALID, "id array is null");
+    for (int i = 0; i < n; i++) {
+        if (src_ids[i] < 0 || src_ids[i] >= c->max_chunks || dst_ids[i] < 0 || dst_ids[i] >= c->max_chunks)
+            return fail(CA_ERR_INVALID, "chunk id outside the pool");
+        if (src_ids[i] == dst_ids[i]) return fail(CA_ERR_INVALID, "source and destination chunk are the same");
+    }
+    DeviceGuard guard(c->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    for (int i0 = 0; i0 < n; i0 += ca::COPY_MAX_PAIRS) {
+        ca::CopyParams p;
+        p.pool = c->pool;
+        p.chunk_bytes = c->geo.chunk_elems * c->geo.esize;
+        p.n = n - i0 < ca::COPY_MAX_PAIRS ? n - i0 : ca::COPY_MAX_PAIRS;
+        std::memcpy(p.src, src_ids + i0, p.n * sizeof(int32_t));
+        std::memcpy(p.dst, dst_ids + i0, p.n * sizeof(int32_t));
+        CA_CUDA(ca::launch_copy_chunks(p, static_cast<cudaStream_t>(stream_)));
+    }
+    return CA_OK;
+}
+
+int ca_read_chunk(ca_context* c, int chunk_id, int n_tokens, void* k_out, void* v_out, ca_stream stream_) {
+    if (!c) return fail(CA_ERR_INVALID, "context is null");
+    if (chunk_id < 0 || chunk_id >= c->max_chunks) return fail(CA_ERR_INVALID, "chunk id outside the pool");
+    if (n_tokens < 0 || n_tokens > c->geo.chunk_size) return fail(CA_ERR_INVALID, "n_tokens outside the chunk");
+    if (n_tokens == 0) return CA_OK;
+    if (!k_out || !v_out) return fail(CA_ERR_INVALID, "output is null");
+    DeviceGuard guard(c->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    ca::ReadChunkParams p;
+    p.pool = c->pool;
+    p.geo = c->geo;
+    p.chunk_id = chunk_id;
+    p.n_tokens = n_tokens;
+    p.k_out = k_out;
+    p.v_out = v_out;
+    CA_CUDA(ca::launch_read_chunk(p, static_cast<cudaStream_t>(stream_)));
+    return CA_OK;
+}
+
+int ca_status_read(ca_context* c, ca_stream stream_, int32_t* status) {
+    if (!c || !status) return fail(CA_ERR_INVALID, "null argument");
+    DeviceGuard guard(c->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int32_t host = 0;
+    CA_CUDA(cudaMemcpyAsync(&host, c->status, sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+    CA_CUDA(cudaStreamSynchronize(stream));
+    *status = host;
+    if (host != 0) return fail(CA_ERR_DEVICE_STATUS, "a kernel gave up a bounded wait, status " + std::to_string(host));
+    return CA_OK;
+}
+
+int ca_context_stats(const ca_context* c, ca_plan_stats* out) {
+    if (!c || !out) return fail(CA_ERR_INVALID, "null argument");
+    if (!c->valid) return fail(CA_ERR_STATE, "work list is stale");
+    *out = c->plan.stats;
+    return CA_OK;
+}
+
+// ---- host-only planner ---------------------------------------------------------------------------------
+int ca_plan_build(ca_plan** out, const ca_chunk_info* infos, int n_infos, int n_seqs, int n_heads,
+                  int chunk_size, int tpp_threshold, int n_ctas, int64_t max_chunks, int split_phases) {
+    if (!out) return fail(CA_ERR_INVALID, "out is null");
+    *out = nullptr;
+    ca_plan* p = new (std::nothrow) ca_plan();
+    if (!p) return fail(CA_ERR_INVALID, "out of host memory");
+    std::string err = ca::build_plan(p->plan, infos, n_infos, n_seqs, n_heads, chunk_size, tpp_threshold, n_ctas,
+                                     max_chunks, split_phases != 0, ca::FAST_D, 2, true);
+    if (!err.empty()) {
+        delete p;
+        return fail(CA_ERR_INVALID, "work list rejected: " + err);
+    }
+    *out = p;
+    return CA_OK;
+}
+
+int ca_plan_array(const ca_plan* plan, int which, const int32_t** data, int64_t* count) {
+    if (!plan || !data || !count) return fail(CA_ERR_INVALID, "null argument");
+    const ca::Plan& pl = plan->plan;
+    const std::vector<int32_t>* v = nullptr;
+    switch (which) {
+        case CA_PLAN_ITEMS:
+            *data = reinterpret_cast<const int32_t*>(pl.items.data());
+            *count = (int64_t)pl.items.size() * 8;
+            return CA_OK;
+        case CA_PLAN_TILE_CHUNKS: v = &pl.tile_chunks; break;
+        case CA_PLAN_CTA_ITEM_BEGIN: v = &pl.cta_item_begin; break;
+        case CA_PLAN_MERGE_OFF: v = &pl.merge_off; break;
+        case CA_PLAN_MERGE_SLOTS: v = &pl.merge_slots; break;
+        case CA_PLAN_PATH_OFF: v = &pl.path_off; break;
+        case CA_PLAN_PATH_CHUNKS: v = &pl.path_chunks; break;
+        case CA_PLAN_PATH_TOKENS: v = &pl.path_tokens; break;
+        case CA_PLAN_TAIL_CHUNK: v = &pl.tail_chunk; break;
+        case CA_PLAN_TAIL_TOKENS: v = &pl.tail_tokens; break;
+        case CA_PLAN_CTA_ITEM_BEGIN_CF: v = &pl.cta_item_begin_cf; break;
+        case CA_PLAN_CTA_ITEM_BEGIN_SF: v = &pl.cta_item_begin_sf; break;
+        default: return fail(CA_ERR_INVALID, "unknown plan array");
+    }
+    *data = v->data();
+    *count = (int64_t)v->size();
+    return CA_OK;
+}
+
+int ca_plan_stats_get(const ca_plan* plan, ca_plan_stats* out) {
+    if (!plan || !out) return fail(CA_ERR_INVALID, "null argument");
+    *out = plan->plan.stats;
+    return CA_OK;
+}
+
+void ca_plan_destroy(ca_plan* plan) { delete plan; }
+
+}  // extern "C"

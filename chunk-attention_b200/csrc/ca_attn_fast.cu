@@ -1,0 +1,606 @@
+// Decode attention over a prefix tree of KV chunks, fp16 / d_head 128 / chunk_size 64, sm_100a.
+//
+// attn_partial_kernel — ONE persistent kernel, one CTA per SM, serves both phases of the
+// reference's two-phase decode attention:
+//   * chunk-first items (reference: attn_chunk_first_kernel_v2, cpp/chunk_attn/kernel_cuda.cu:796-883):
+//     the queries of all rows sharing a run of chunks form a small dense contraction against
+//     every K/V tile of the run.  Runs on tensor cores (mma.sync m16n8k16, fp32 accumulate) with
+//     a flash-style online softmax kept in registers across the WHOLE run, so a run emits one
+//     partial per row instead of one per chunk.
+//   * sequence-first items (reference: attn_seq_first_kernel, kernel_cuda.cu:885-1086): one row's
+//     private tail chunks, a memory-bound walk on CUDA cores: 128-bit shared-memory loads,
+//     fp32 dot products, warp-shuffle reductions.
+// Both kinds read their K/V tiles from the same ring of 32 KiB shared-memory stages, filled by a
+// dedicated producer warp with 1-D TMA bulk copies (cp.async.bulk + mbarrier transaction counts)
+// that run ahead across item boundaries; the host has cut the tile stream into equal parts, one
+// per CTA (ca_plan.h).
+//
+// attn_merge_kernel — combines the partials of each (row, head) with the usual
+// max-rescaled sum (reference: the merge inlined in kernel_cuda.cu:962-984,1042-1085).
+//
+// Every wait on an mbarrier is bounded: when the bound is hit the kernel records a status code
+// and unwinds instead of spinning forever.
+#include <cuda_fp16.h>
+
+#include "ca_kernels.h"
+#include "ca_plan.h"
+
+namespace ca {
+namespace {
+
+constexpr int NUM_STAGES = 6;
+constexpr int NUM_CONSUMER_WARPS = 8;
+constexpr int NUM_THREADS = (NUM_CONSUMER_WARPS + 1) * 32;
+constexpr int SCRATCH_FLOATS_PER_WARP = 132;  // m, l, 2 pad, o[128]
+constexpr int SCRATCH_BYTES = 2 * NUM_CONSUMER_WARPS * SCRATCH_FLOATS_PER_WARP * 4;
+constexpr int NUM_BARRIERS = 2 * NUM_STAGES + 1;
+constexpr int SMEM_BYTES = NUM_STAGES * FAST_STAGE_BYTES + SCRATCH_BYTES + NUM_BARRIERS * 8 + 16;
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // about two seconds
+constexpr float NEG_BIG = -1.0e30f;
+
+struct ItemView {
+    int tile_begin, n_tiles, head, row_begin, n_rows, slot_base, flags, last_tokens;
+};
+
+__device__ __forceinline__ ItemView load_item(const int4* items, int i) {
+    const int4 a = __ldg(items + 2 * i);
+    const int4 b = __ldg(items + 2 * i + 1);
+    return ItemView{a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+}
+
+// tokens held by tile j of an item; only the last tile of a sequence-first item can be partial
+__device__ __forceinline__ int tile_tokens(const ItemView& it, int j, int delta) {
+    if (j != it.n_tiles - 1) return FAST_C;
+    const int t = it.last_tokens + ((it.flags & ITEM_FLAG_TAIL) ? delta : 0);
+    return t < FAST_C ? t : FAST_C;
+}
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Wait for the phase with the given parity to complete; false when the bound ran out.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+    }
+    return true;
+}
+// 1-D TMA bulk copy global -> shared, completion counted in bytes on an mbarrier.
+// dst, src 16-byte aligned; bytes a multiple of 16.
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+        "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3,
+                                              uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+// D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// ---- pipeline bookkeeping shared by producer and consumers ----------------------------------------
+struct Ring {
+    uint32_t ring;        // shared address of stage 0
+    uint32_t full_bar;    // NUM_STAGES barriers, producer -> consumers (count 1 + tx bytes)
+    uint32_t empty_bar;   // NUM_STAGES barriers, consumers -> producer (count NUM_CONSUMER_WARPS)
+    uint32_t stage;
+    uint32_t phase;
+    __device__ __forceinline__ void advance() {
+        if (++stage == NUM_STAGES) {
+            stage = 0;
+            phase ^= 1;
+        }
+    }
+};
+
+__device__ __forceinline__ void report(int* status, int code) { atomicCAS(status, STATUS_OK, code); }
+
+// ---- producer: one warp, lane 0 issues --------------------------------------------------------------
+__device__ __forceinline__ void producer_loop(const PartialParams& p, Ring rg, int item_begin, int item_end, int lane) {
+    uint32_t issued = 0;
+    bool ok = true;
+    for (int i = item_begin; i < item_end && ok; i++) {
+        const ItemView it = load_item(p.items, i);
+        for (int j0 = 0; j0 < it.n_tiles && ok; j0 += 32) {
+            // each lane fetches the pool slot of one upcoming tile, lane 0 reads them by shuffle
+            const int jl = j0 + lane;
+            const int my_chunk = (jl < it.n_tiles) ? __ldg(p.tile_chunks + it.tile_begin + jl) : 0;
+            const int jn = min(32, it.n_tiles - j0);
+            for (int jj = 0; jj < jn; jj++) {
+                const int chunk = __shfl_sync(0xffffffffu, my_chunk, jj);
+                const int nt = tile_tokens(it, j0 + jj, p.delta_tokens);
+                if (nt == 0) continue;
+                if (lane == 0) {
+                    ok = mbar_wait_bounded(rg.empty_bar + 8 * rg.stage, rg.phase ^ 1);
+                    if (ok) {
+                        const uint8_t* src =
+                            p.pool + ((size_t)chunk * p.n_heads + it.head) * (size_t)FAST_STAGE_BYTES;
+                        const uint32_t bytes = (uint32_t)nt * (FAST_D * 2);
+                        const uint32_t bar = rg.full_bar + 8 * rg.stage;
+                        const uint32_t dst = rg.ring + rg.stage * FAST_STAGE_BYTES;
+                        mbar_arrive_expect_tx(bar, 2 * bytes);
+                        bulk_copy_g2s(dst, src, bytes, bar);
+                        bulk_copy_g2s(dst + FAST_TILE_BYTES, src + FAST_TILE_BYTES, bytes, bar);
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
+                issued++;
+                rg.advance();
+            }
+        }
+    }
+    if (lane == 0) {
+        if (!ok) report(p.status, STATUS_EMPTY_WAIT_TIMEOUT);
+        // Do not leave while a copy into this CTA's shared memory may still be in flight: wait
+        // (bounded) for the completion of the last fills, newest NUM_STAGES at most.
+        const uint32_t n_check = issued < (uint32_t)NUM_STAGES ? issued : (uint32_t)NUM_STAGES;
+        for (uint32_t f = issued - n_check; f < issued; f++) {
+            if (!mbar_wait_bounded(rg.full_bar + 8 * (f % NUM_STAGES), (f / NUM_STAGES) & 1)) {
+                report(p.status, STATUS_DRAIN_TIMEOUT);
+                break;
+            }
+        }
+    }
+}
+
+// ---- consumers ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ bool consumer_wait_full(const Ring& rg) {
+    const bool ok = mbar_wait_bounded(rg.full_bar + 8 * rg.stage, rg.phase);
+    return __all_sync(0xffffffffu, ok);
+}
+__device__ __forceinline__ void consumer_release(Ring& rg, int lane) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(rg.empty_bar + 8 * rg.stage);
+    rg.advance();
+}
+
+// Chunk-first item on tensor cores.  The 8 warps form MT = 8 / TS row tiles of 16 rows times TS
+// token splits; a warp owns 16 query rows and the TW = 64 / TS tokens [split * TW, ...) of every
+// tile, keeps its own (max, sum, O) and writes its own partial at the end of the item.
+template <int TS>
+__device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView& it, Ring& rg, int warp, int lane) {
+    constexpr int MT = NUM_CONSUMER_WARPS / TS;
+    constexpr int TW = FAST_C / TS;   // tokens per warp per tile
+    constexpr int NT_S = TW / 8;      // 8-token column tiles of S
+    const int mt = warp % MT;
+    const int split = warp / MT;
+    const int tok0 = split * TW;
+    const int quad = lane & 3;
+    const int r_lo = mt * 16 + (lane >> 2);
+    const int r_hi = r_lo + 8;
+    const bool v_lo = r_lo < it.n_rows;
+    const bool v_hi = r_hi < it.n_rows;
+
+    // Q as A fragments for the 8 k-steps over d_head; rows past the item are zero
+    uint32_t qa[8][4];
+    {
+        const __half* q = reinterpret_cast<const __half*>(p.q);
+        const size_t row_stride = (size_t)p.n_heads * FAST_D;
+        const __half* q_lo = q + (size_t)(it.row_begin + r_lo) * row_stride + (size_t)it.head * FAST_D;
+        const __half* q_hi = q + (size_t)(it.row_begin + r_hi) * row_stride + (size_t)it.head * FAST_D;
+#pragma unroll
+        for (int ks = 0; ks < 8; ks++) {
+            const int col = ks * 16 + 2 * quad;
+            qa[ks][0] = v_lo ? __ldg(reinterpret_cast<const uint32_t*>(q_lo + col)) : 0u;
+            qa[ks][1] = v_hi ? __ldg(reinterpret_cast<const uint32_t*>(q_hi + col)) : 0u;
+            qa[ks][2] = v_lo ? __ldg(reinterpret_cast<const uint32_t*>(q_lo + col + 8)) : 0u;
+            qa[ks][3] = v_hi ? __ldg(reinterpret_cast<const uint32_t*>(q_hi + col + 8)) : 0u;
+        }
+    }
+
+    float o[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; n++) {
+        o[n][0] = 0.f; o[n][1] = 0.f; o[n][2] = 0.f; o[n][3] = 0.f;
+    }
+    float m_lo = NEG_BIG, m_hi = NEG_BIG, l_lo = 0.f, l_hi = 0.f;
+
+    // per-lane row offsets for the two ldmatrix address patterns
+    const int k_tok = (lane & 7) + ((lane >> 4) << 3);   // K: matrices 2,3 are the next 8 tokens
+    const int k_gsel = (lane >> 3) & 1;                  //    matrices 1,3 are the next granule
+    const int v_tok = (lane & 7) + (((lane >> 3) & 1) << 3);  // V: matrices 1,3 are the next 8 tokens
+    const int v_gsel = lane >> 4;                             //    matrices 2,3 are the next granule
+
+    for (int j = 0; j < it.n_tiles; j++) {
+        if (tile_tokens(it, j, p.delta_tokens) == 0) continue;
+        if (!consumer_wait_full(rg)) return false;
+        const uint32_t kbase = rg.ring + rg.stage * FAST_STAGE_BYTES;
+        const uint32_t vbase = kbase + FAST_TILE_BYTES;
+
+        // S = Q K^T for this warp's TW tokens
+        float s[NT_S][4];
+#pragma unroll
+        for (int n = 0; n < NT_S; n++) {
+            s[n][0] = 0.f; s[n][1] = 0.f; s[n][2] = 0.f; s[n][3] = 0.f;
+        }
+#pragma unroll
+        for (int ks = 0; ks < 8; ks++) {
+#pragma unroll
+            for (int np = 0; np < NT_S / 2; np++) {
+                const int t = tok0 + np * 16 + k_tok;
+                const int g = 2 * ks + k_gsel;
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(b0, b1, b2, b3, kbase + t * (FAST_D * 2) + ((g ^ (t & 7)) << 4));
+                mma_16816(s[2 * np], qa[ks], b0, b1);
+                mma_16816(s[2 * np + 1], qa[ks], b2, b3);
+            }
+        }
+
+        // online softmax in log2 units; a thread holds rows r_lo (c0, c1) and r_hi (c2, c3)
+        float mx_lo = NEG_BIG, mx_hi = NEG_BIG;
+#pragma unroll
+        for (int n = 0; n < NT_S; n++) {
+            mx_lo = fmaxf(mx_lo, fmaxf(s[n][0], s[n][1]));
+            mx_hi = fmaxf(mx_hi, fmaxf(s[n][2], s[n][3]));
+        }
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        const float mn_lo = fmaxf(m_lo, mx_lo * p.scale_log2);
+        const float mn_hi = fmaxf(m_hi, mx_hi * p.scale_log2);
+        const float a_lo = fast_exp2(m_lo - mn_lo);
+        const float a_hi = fast_exp2(m_hi - mn_hi);
+        m_lo = mn_lo;
+        m_hi = mn_hi;
+        float sum_lo = 0.f, sum_hi = 0.f;
+        uint32_t pa[TW / 16][4];
+#pragma unroll
+        for (int n = 0; n < NT_S; n++) {
+            const float p0 = fast_exp2(fmaf(s[n][0], p.scale_log2, -mn_lo));
+            const float p1 = fast_exp2(fmaf(s[n][1], p.scale_log2, -mn_lo));
+            const float p2 = fast_exp2(fmaf(s[n][2], p.scale_log2, -mn_hi));
+            const float p3 = fast_exp2(fmaf(s[n][3], p.scale_log2, -mn_hi));
+            sum_lo += p0 + p1;
+            sum_hi += p2 + p3;
+            // the accumulator layout of two adjacent 8-token tiles is the A layout of one k-step
+            pa[n >> 1][(n & 1) * 2 + 0] = pack_half2(p0, p1);
+            pa[n >> 1][(n & 1) * 2 + 1] = pack_half2(p2, p3);
+        }
+        l_lo = l_lo * a_lo + sum_lo;
+        l_hi = l_hi * a_hi + sum_hi;
+#pragma unroll
+        for (int n = 0; n < 16; n++) {
+            o[n][0] *= a_lo; o[n][1] *= a_lo; o[n][2] *= a_hi; o[n][3] *= a_hi;
+        }
+
+        // O += P V
+#pragma unroll
+        for (int kk = 0; kk < TW / 16; kk++) {
+#pragma unroll
+            for (int dp = 0; dp < 8; dp++) {
+                const int t = tok0 + kk * 16 + v_tok;
+                const int g = 2 * dp + v_gsel;
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4_trans(b0, b1, b2, b3, vbase + t * (FAST_D * 2) + ((g ^ (t & 7)) << 4));
+                mma_16816(o[2 * dp], pa[kk], b0, b1);
+                mma_16816(o[2 * dp + 1], pa[kk], b2, b3);
+            }
+        }
+        consumer_release(rg, lane);
+    }
+
+    // the four lanes of a quad hold partial sums of the same two rows
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    const int slot0 = it.slot_base + split * it.n_rows;
+    if (v_lo) {
+        float* dst = p.part_o + (size_t)(slot0 + r_lo) * FAST_D + 2 * quad;
+#pragma unroll
+        for (int n = 0; n < 16; n++) *reinterpret_cast<float2*>(dst + 8 * n) = make_float2(o[n][0], o[n][1]);
+        if (quad == 0) p.part_ml[slot0 + r_lo] = make_float2(m_lo, l_lo);
+    }
+    if (v_hi) {
+        float* dst = p.part_o + (size_t)(slot0 + r_hi) * FAST_D + 2 * quad;
+#pragma unroll
+        for (int n = 0; n < 16; n++) *reinterpret_cast<float2*>(dst + 8 * n) = make_float2(o[n][2], o[n][3]);
+        if (quad == 0) p.part_ml[slot0 + r_hi] = make_float2(m_hi, l_hi);
+    }
+    return true;
+}
+
+// Sequence-first item on CUDA cores.  Warp w owns tokens 8w..8w+7 of every tile; a half-warp reads
+// one 256-byte token row per 128-bit load (lane = granule), so K rows are dotted against q held in
+// registers and V rows are accumulated into 8 output elements per lane.  The 8 warps' states are
+// combined through shared memory at the end of the item and one partial is written.
+__device__ __forceinline__ bool simt_item(const PartialParams& p, const ItemView& it, Ring& rg, float* scratch,
+                          uint32_t merge_bar, uint32_t& simt_count, int warp, int lane) {
+    const int g = lane & 15;
+    const int half = lane >> 4;
+    float qf[8];
+    {
+        const __half* q = reinterpret_cast<const __half*>(p.q) +
+                          ((size_t)it.row_begin * p.n_heads + it.head) * FAST_D + 8 * g;
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(q));
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float2 f = __half22float2(h[i]);
+            qf[2 * i] = f.x * p.scale_log2;
+            qf[2 * i + 1] = f.y * p.scale_log2;
+        }
+    }
+    float m = NEG_BIG, l = 0.f;
+    float o[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) o[i] = 0.f;
+
+    for (int j = 0; j < it.n_tiles; j++) {
+        const int nt = tile_tokens(it, j, p.delta_tokens);
+        if (nt == 0) continue;
+        if (!consumer_wait_full(rg)) return false;
+        if (warp * 8 < nt) {
+            const uint32_t kt = rg.ring + rg.stage * FAST_STAGE_BYTES;
+            const uint32_t vt = kt + FAST_TILE_BYTES;
+            float s[4];
+#pragma unroll
+            for (int jj = 0; jj < 4; jj++) {
+                const int t = warp * 8 + 2 * jj + half;
+                float acc = 0.f;
+                if (t < nt) {
+                    const uint4 raw = lds128(kt + t * (FAST_D * 2) + ((g ^ (t & 7)) << 4));
+                    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const float2 f = __half22float2(h[i]);
+                        acc = fmaf(qf[2 * i], f.x, acc);
+                        acc = fmaf(qf[2 * i + 1], f.y, acc);
+                    }
+                }
+                s[jj] = acc;
+            }
+            // sum over the 16 lanes of a half-warp (the 16 granules of a token row)
+#pragma unroll
+            for (int off = 8; off >= 1; off >>= 1) {
+#pragma unroll
+                for (int jj = 0; jj < 4; jj++) s[jj] += __shfl_xor_sync(0xffffffffu, s[jj], off);
+            }
+            float mx = NEG_BIG;
+#pragma unroll
+            for (int jj = 0; jj < 4; jj++) {
+                const int t = warp * 8 + 2 * jj + half;
+                if (t < nt) mx = fmaxf(mx, s[jj]);
+            }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float mn = fmaxf(m, mx);
+            const float alpha = fast_exp2(m - mn);
+            m = mn;
+            l *= alpha;
+#pragma unroll
+            for (int i = 0; i < 8; i++) o[i] *= alpha;
+#pragma unroll
+            for (int jj = 0; jj < 4; jj++) {
+                const int t = warp * 8 + 2 * jj + half;
+                if (t < nt) {
+                    const float pj = fast_exp2(s[jj] - mn);
+                    l += pj;
+                    const uint4 raw = lds128(vt + t * (FAST_D * 2) + ((g ^ (t & 7)) << 4));
+                    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const float2 f = __half22float2(h[i]);
+                        o[2 * i] = fmaf(pj, f.x, o[2 * i]);
+                        o[2 * i + 1] = fmaf(pj, f.y, o[2 * i + 1]);
+                    }
+                }
+            }
+        }
+        consumer_release(rg, lane);
+    }
+
+    // the two half-warps walked different tokens against the same running max
+    l += __shfl_xor_sync(0xffffffffu, l, 16);
+#pragma unroll
+    for (int i = 0; i < 8; i++) o[i] += __shfl_xor_sync(0xffffffffu, o[i], 16);
+
+    // combine the 8 warps: double-buffered scratch, one mbarrier phase per sequence-first item
+    float* mine = scratch + ((simt_count & 1) * NUM_CONSUMER_WARPS + warp) * SCRATCH_FLOATS_PER_WARP;
+    if (lane == 0) {
+        mine[0] = m;
+        mine[1] = l;
+    }
+    if (lane < 16) {
+        *reinterpret_cast<float4*>(mine + 4 + 8 * g) = make_float4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<float4*>(mine + 8 + 8 * g) = make_float4(o[4], o[5], o[6], o[7]);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(merge_bar);
+    bool ok = mbar_wait_bounded(merge_bar, simt_count & 1);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) return false;
+    if (warp < 4) {
+        const float* base = scratch + (simt_count & 1) * NUM_CONSUMER_WARPS * SCRATCH_FLOATS_PER_WARP;
+        const int d = warp * 32 + lane;
+        float mm = NEG_BIG;
+#pragma unroll
+        for (int w = 0; w < NUM_CONSUMER_WARPS; w++) mm = fmaxf(mm, base[w * SCRATCH_FLOATS_PER_WARP]);
+        float ll = 0.f, od = 0.f;
+#pragma unroll
+        for (int w = 0; w < NUM_CONSUMER_WARPS; w++) {
+            const float wl = base[w * SCRATCH_FLOATS_PER_WARP + 1];
+            // a warp that saw no token keeps l = 0 and contributes nothing whatever its weight
+            const float wgt = fast_exp2(base[w * SCRATCH_FLOATS_PER_WARP] - mm);
+            ll = fmaf(wgt, wl, ll);
+            od = fmaf(wgt, base[w * SCRATCH_FLOATS_PER_WARP + 4 + d], od);
+        }
+        p.part_o[(size_t)it.slot_base * FAST_D + d] = od;
+        if (d == 0) p.part_ml[it.slot_base] = make_float2(mm, ll);
+    }
+    simt_count++;
+    return true;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1) attn_partial_kernel(const PartialParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    float* scratch = reinterpret_cast<float*>(smem + NUM_STAGES * FAST_STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NUM_STAGES * FAST_STAGE_BYTES + SCRATCH_BYTES);
+
+    Ring rg;
+    rg.ring = smem_u32(smem);
+    rg.full_bar = smem_u32(bars);
+    rg.empty_bar = smem_u32(bars + NUM_STAGES);
+    rg.stage = 0;
+    rg.phase = 0;
+    const uint32_t merge_bar = smem_u32(bars + 2 * NUM_STAGES);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NUM_STAGES; i++) {
+            mbar_init(rg.full_bar + 8 * i, 1);
+            mbar_init(rg.empty_bar + 8 * i, NUM_CONSUMER_WARPS);
+        }
+        mbar_init(merge_bar, NUM_CONSUMER_WARPS);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    // no block-wide barrier below this line: the warps run decoupled
+    // let the merge kernel (a programmatic dependent launch) be scheduled as soon as SMs drain
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    const int item_begin = __ldg(p.cta_item_begin + blockIdx.x);
+    const int item_end = __ldg(p.cta_item_begin + blockIdx.x + 1);
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (warp == NUM_CONSUMER_WARPS) {
+        producer_loop(p, rg, item_begin, item_end, lane);
+        return;
+    }
+
+    uint32_t simt_count = 0;
+    for (int i = item_begin; i < item_end; i++) {
+        const ItemView it = load_item(p.items, i);
+        const int splits = it.flags >> ITEM_SPLITS_SHIFT;
+        bool ok;
+        if (splits == 0) {
+            ok = simt_item(p, it, rg, scratch, merge_bar, simt_count, warp, lane);
+        } else if (splits == 4) {
+            ok = mma_item<4>(p, it, rg, warp, lane);
+        } else if (splits == 2) {
+            ok = mma_item<2>(p, it, rg, warp, lane);
+        } else {
+            ok = mma_item<1>(p, it, rg, warp, lane);
+        }
+        if (!ok) {
+            if (lane == 0) report(p.status, STATUS_FULL_WAIT_TIMEOUT);
+            break;
+        }
+    }
+}
+
+// One warp per (row, head): out = sum_i 2^(m_i - M) O_i / sum_i 2^(m_i - M) l_i.
+__global__ void __launch_bounds__(128) attn_merge_kernel(const MergeParams p) {
+    // When launched as a programmatic dependent of the partial kernel, wait here until that
+    // kernel's results are visible; a no-op for an ordinary launch.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int pair = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (pair >= p.n_pairs) return;
+    const int lane = threadIdx.x & 31;
+    const int b = __ldg(p.merge_off + pair), e = __ldg(p.merge_off + pair + 1);
+    float mm = NEG_BIG;
+    for (int i = b; i < e; i++) mm = fmaxf(mm, p.part_ml[__ldg(p.merge_slots + i)].x);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float ll = 0.f;
+    for (int i = b; i < e; i++) {
+        const int slot = __ldg(p.merge_slots + i);
+        const float2 ml = p.part_ml[slot];
+        const float w = fast_exp2(ml.x - mm);
+        ll = fmaf(w, ml.y, ll);
+        const float4 v = *reinterpret_cast<const float4*>(p.part_o + (size_t)slot * FAST_D + 4 * lane);
+        acc.x = fmaf(w, v.x, acc.x);
+        acc.y = fmaf(w, v.y, acc.y);
+        acc.z = fmaf(w, v.z, acc.z);
+        acc.w = fmaf(w, v.w, acc.w);
+    }
+    const float inv = ll > 0.f ? 1.f / ll : 0.f;  // a row with no token yields zeros
+    const __half2 h01 = __floats2half2_rn(acc.x * inv, acc.y * inv);
+    const __half2 h23 = __floats2half2_rn(acc.z * inv, acc.w * inv);
+    uint2 packed;
+    packed.x = *reinterpret_cast<const uint32_t*>(&h01);
+    packed.y = *reinterpret_cast<const uint32_t*>(&h23);
+    *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.out) + (size_t)pair * FAST_D + 4 * lane) = packed;
+}
+
+}  // namespace
+
+cudaError_t configure_fast_kernels() {
+    // opt in to the large dynamic shared-memory carve-out, once per device (per context creation)
+    return cudaFuncSetAttribute(attn_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+}
+
+cudaError_t launch_attn_partials(const PartialParams& p, int n_ctas, cudaStream_t stream) {
+    if (n_ctas <= 0) return cudaSuccess;
+    attn_partial_kernel<<<n_ctas, NUM_THREADS, SMEM_BYTES, stream>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_attn_merge(const MergeParams& p, cudaStream_t stream, bool dependent_launch) {
+    if (p.n_pairs <= 0) return cudaSuccess;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((p.n_pairs + 3) / 4);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dependent_launch ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, attn_merge_kernel, p);
+}
+
+}  // namespace ca

@@ -1,0 +1,112 @@
+// Launchers of the CUDA kernels (internal to the library; the public surface is the C ABI).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ca_layout.h"
+
+namespace ca {
+
+// Device status word values (first failure wins).
+constexpr int STATUS_OK = 0;
+constexpr int STATUS_FULL_WAIT_TIMEOUT = 1;   // a consumer warp gave up waiting for a tile
+constexpr int STATUS_EMPTY_WAIT_TIMEOUT = 2;  // the producer gave up waiting for a free stage
+constexpr int STATUS_DRAIN_TIMEOUT = 3;       // copies still in flight at kernel exit
+
+// ---- fast path: fp16, d_head 128, chunk_size 64 -----------------------------------------------
+constexpr int FAST_D = 128;
+constexpr int FAST_C = 64;
+constexpr int FAST_TILE_BYTES = FAST_C * FAST_D * 2;  // one K or V tile
+constexpr int FAST_STAGE_BYTES = 2 * FAST_TILE_BYTES; // K tile + V tile of one (chunk, head)
+
+struct PartialParams {
+    const uint8_t* pool;         // chunk pool base
+    int n_heads;
+    const void* q;               // fp16 [n_seqs, n_heads, 128]
+    const int4* items;           // PlanItem as two int4
+    const int32_t* tile_chunks;
+    const int32_t* cta_item_begin;
+    float* part_o;               // [n_slots][128]
+    float2* part_ml;             // [n_slots] (running max in log2 units, sum of exponentials)
+    int delta_tokens;            // tokens appended to every tail since the plan was built
+    float scale_log2;            // log2(e) / sqrt(d_head)
+    int* status;
+};
+
+// Persistent kernel: chunk-first items on tensor cores and sequence-first items on CUDA cores,
+// both fed by one TMA ring.  grid = n_ctas.
+cudaError_t launch_attn_partials(const PartialParams& p, int n_ctas, cudaStream_t stream);
+cudaError_t configure_fast_kernels();  // once per device before the first launch
+
+struct MergeParams {
+    const float* part_o;
+    const float2* part_ml;
+    const int32_t* merge_off;    // [n_rows * n_heads + 1]
+    const int32_t* merge_slots;
+    void* out;                   // fp16 [n_rows, n_heads, 128]
+    int n_pairs;                 // n_rows * n_heads
+};
+cudaError_t launch_attn_merge(const MergeParams& p, cudaStream_t stream, bool dependent_launch);
+
+// ---- generic path: any d_head <= 256, any chunk size, fp16 or fp32 ----------------------------------
+struct GenericParams {
+    const void* pool;
+    Geometry geo;
+    const void* q;
+    void* out;
+    const int32_t* path_off;     // [n_seqs + 1]
+    const int32_t* path_chunks;
+    const int32_t* path_tokens;
+    int n_seqs;
+    int delta_tokens;
+    float scale;                 // 1 / sqrt(d_head)
+};
+cudaError_t launch_attn_seq_generic(const GenericParams& p, int dtype, cudaStream_t stream);
+
+// ---- pool maintenance ------------------------------------------------------------------------------------
+struct AppendParams {
+    void* pool;
+    Geometry geo;
+    const void* k;               // [n_seqs, n_heads, d_head]
+    const void* v;
+    const int32_t* tail_chunk;   // [n_seqs]
+    const int32_t* tail_tokens;  // [n_seqs]
+    int n_seqs;
+    int delta_tokens;
+};
+// vec16: rows are whole 16-byte granules and k, v are 16-byte aligned
+cudaError_t launch_append_kv(const AppendParams& p, bool vec16, cudaStream_t stream);
+
+constexpr int SCATTER_MAX_CHUNKS = 512;
+struct ScatterParams {
+    void* pool;
+    Geometry geo;
+    const void* k;
+    const void* v;
+    int64_t stride_token, stride_head;  // in elements
+    int n_tokens;
+    int32_t chunk_ids[SCATTER_MAX_CHUNKS];
+};
+cudaError_t launch_scatter_prefill(const ScatterParams& p, bool vec16, cudaStream_t stream);
+
+constexpr int COPY_MAX_PAIRS = 256;
+struct CopyParams {
+    void* pool;
+    int64_t chunk_bytes;
+    int n;
+    int32_t src[COPY_MAX_PAIRS];
+    int32_t dst[COPY_MAX_PAIRS];
+};
+cudaError_t launch_copy_chunks(const CopyParams& p, cudaStream_t stream);
+
+struct ReadChunkParams {
+    const void* pool;
+    Geometry geo;
+    int chunk_id;
+    int n_tokens;
+    void* k_out;                 // [n_heads, n_tokens, d_head]
+    void* v_out;
+};
+cudaError_t launch_read_chunk(const ReadChunkParams& p, cudaStream_t stream);
+
+}  // namespace ca

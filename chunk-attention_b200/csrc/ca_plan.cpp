@@ -1,0 +1,257 @@
+// Host-side work-list builder; see ca_plan.h for what it produces and why.
+#include "ca_plan.h"
+
+#include <algorithm>
+#include <cstdio>
+#include <unordered_map>
+
+namespace ca {
+namespace {
+
+struct Unit {
+    int32_t tile_begin, n_tiles, head, row_begin, n_rows, splits, last_tokens;
+    bool tail;     // last tile is a sequence's tail chunk
+    double w;      // relative cost of one full tile of this unit
+};
+
+// Relative cost of streaming one tile through a chunk-first item.  Up to 32 rows the tile is
+// paid for by its HBM bytes alone (weight 1); wider row blocks issue proportionally more MMAs
+// per byte and become tensor-pipe bound.
+double chunk_first_tile_weight(int splits) {
+    return splits == 4 ? 1.0 : (splits == 2 ? 1.4 : 2.8);
+}
+constexpr double kTailTileWeight = 0.5;  // a tail holds between 0 and chunk_size - 1 tokens
+
+std::string fmt(const char* f, long a = 0, long b = 0, long c = 0) {
+    char buf[256];
+    snprintf(buf, sizeof(buf), f, a, b, c);
+    return buf;
+}
+
+// Lay the units [ubegin, uend) end to end, cut the stream into at most n_ctas equal-weight
+// parts and append the resulting items.  A tile belongs to the part its midpoint falls in.
+void cut_units(Plan& plan, const std::vector<Unit>& units, size_t ubegin, size_t uend, int n_ctas,
+               std::vector<int32_t>& cta_item_begin, int32_t& n_slots) {
+    double total = 0;
+    for (size_t u = ubegin; u < uend; u++) {
+        const Unit& un = units[u];
+        total += un.w * un.n_tiles - (un.tail ? un.w - kTailTileWeight : 0.0);
+    }
+    int eff = (int)std::min<double>(n_ctas, std::max(1.0, total / 1.5));
+    const size_t first_item = plan.items.size();
+    std::vector<int32_t> item_cta;
+    double acc = 0;
+    auto cta_of = [&](double x) {
+        int c = total > 0 ? (int)(x * eff / total) : 0;
+        return std::min(eff - 1, std::max(0, c));
+    };
+    for (size_t u = ubegin; u < uend; u++) {
+        const Unit& un = units[u];
+        int piece_start = 0, cur = -1;
+        auto emit = [&](int j_end) {
+            PlanItem it;
+            it.tile_begin = un.tile_begin + piece_start;
+            it.n_tiles = j_end - piece_start;
+            it.head = un.head;
+            it.row_begin = un.row_begin;
+            it.n_rows = un.n_rows;
+            it.slot_base = n_slots;
+            const bool has_last = (j_end == un.n_tiles);
+            it.flags = ((un.tail && has_last) ? ITEM_FLAG_TAIL : 0) | (un.splits << ITEM_SPLITS_SHIFT);
+            it.last_tokens = has_last ? un.last_tokens : plan.chunk_size;
+            n_slots += un.n_rows * std::max(1, (int)un.splits);
+            plan.items.push_back(it);
+            item_cta.push_back(cur);
+        };
+        for (int j = 0; j < un.n_tiles; j++) {
+            const double w = (un.tail && j == un.n_tiles - 1) ? kTailTileWeight : un.w;
+            const int c = cta_of(acc + 0.5 * w);
+            if (cur < 0) cur = c;
+            if (c != cur) {
+                emit(j);
+                piece_start = j;
+                cur = c;
+            }
+            acc += w;
+        }
+        if (un.n_tiles > 0) emit(un.n_tiles);
+    }
+    cta_item_begin.assign(eff + 1, (int32_t)plan.items.size());
+    // items are in non-decreasing CTA order: the first item of CTA c is the first with cta >= c
+    size_t i = 0;
+    for (int c = 0; c <= eff; c++) {
+        while (i < item_cta.size() && item_cta[i] < c) i++;
+        cta_item_begin[c] = (int32_t)(first_item + i);
+    }
+}
+
+}  // namespace
+
+std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int n_seqs, int n_heads,
+                       int chunk_size, int tpp_threshold, int n_ctas, int64_t max_chunks,
+                       bool split_phases, int d_head, int esize, bool fast_path) {
+    plan = Plan();
+    if (n_infos < 0 || n_seqs < 0 || n_heads <= 0 || chunk_size <= 0 || n_ctas <= 0)
+        return "negative or zero size";
+    if (n_infos > 0 && infos == nullptr) return "infos is null";
+    if (tpp_threshold < 1) tpp_threshold = 1;
+    plan.n_seqs = n_seqs;
+    plan.n_heads = n_heads;
+    plan.chunk_size = chunk_size;
+    plan.tpp_threshold = tpp_threshold;
+    plan.split_phases = split_phases;
+
+    // ---- validate, count path lengths ---------------------------------------------------------
+    plan.path_off.assign(n_seqs + 1, 0);
+    int64_t unique_tokens = 0;
+    for (int i = 0; i < n_infos; i++) {
+        const ca_chunk_info& ci = infos[i];
+        if (ci.chunk_id < 0 || ci.chunk_id >= max_chunks)
+            return fmt("chunk_id %ld of entry %ld outside the pool (%ld chunks)", ci.chunk_id, i, (long)max_chunks);
+        if (ci.n_tokens < 0 || ci.n_tokens > chunk_size)
+            return fmt("n_tokens %ld of entry %ld outside [0, %ld]", ci.n_tokens, i, chunk_size);
+        if (ci.seq_begin < 0 || ci.seq_begin >= ci.seq_end || ci.seq_end > n_seqs)
+            return fmt("row range [%ld, %ld) of entry %ld is empty or outside the batch", ci.seq_begin, ci.seq_end, i);
+        for (int s = ci.seq_begin; s < ci.seq_end; s++) plan.path_off[s + 1]++;
+        unique_tokens += ci.n_tokens;
+    }
+    for (int s = 0; s < n_seqs; s++) {
+        if (plan.path_off[s + 1] == 0) return fmt("row %ld is served by no chunk", s);
+        plan.path_off[s + 1] += plan.path_off[s];
+    }
+    const int64_t path_total = plan.path_off[n_seqs];
+    plan.path_chunks.resize(path_total);
+    plan.path_tokens.resize(path_total);
+    std::vector<int32_t> path_info(path_total);  // index into infos
+    {
+        std::vector<int32_t> cursor(plan.path_off.begin(), plan.path_off.end() - 1);
+        for (int i = 0; i < n_infos; i++) {
+            for (int s = infos[i].seq_begin; s < infos[i].seq_end; s++) {
+                int32_t p = cursor[s]++;
+                plan.path_chunks[p] = infos[i].chunk_id;
+                plan.path_tokens[p] = infos[i].n_tokens;
+                path_info[p] = i;
+            }
+        }
+    }
+    // the leaf of every row must be private to it: new tokens are appended there
+    plan.tail_chunk.resize(n_seqs);
+    plan.tail_tokens.resize(n_seqs);
+    for (int s = 0; s < n_seqs; s++) {
+        const ca_chunk_info& leaf = infos[path_info[plan.path_off[s + 1] - 1]];
+        if (leaf.seq_end - leaf.seq_begin != 1)
+            return fmt("last chunk of row %ld is shared by %ld rows; every row needs its own tail", s,
+                       leaf.seq_end - leaf.seq_begin);
+        plan.tail_chunk[s] = leaf.chunk_id;
+        plan.tail_tokens[s] = leaf.n_tokens;
+    }
+
+    plan.stats.unique_kv_bytes = unique_tokens * (int64_t)n_heads * d_head * 2 * esize;
+    plan.stats.n_chunks = n_infos;
+    plan.stats.fast_path = fast_path ? 1 : 0;
+    plan.stats.kernels_per_step = 1;
+    plan.merge_off.assign((size_t)n_seqs * n_heads + 1, 0);
+    if (!fast_path) {
+        plan.n_ctas = 0;
+        plan.cta_item_begin.assign(1, 0);
+        return "";
+    }
+
+    // ---- classify chunks, group shared ones into runs ----------------------------------------------
+    struct Run { int32_t b, e, tile_begin; std::vector<int32_t> chunks; };
+    std::vector<Run> runs;
+    std::unordered_map<uint64_t, int> run_of;
+    std::vector<char> shared(n_infos, 0);
+    for (int i = 0; i < n_infos; i++) {
+        const ca_chunk_info& ci = infos[i];
+        const int n = ci.seq_end - ci.seq_begin;
+        if (n > tpp_threshold && ci.n_tokens == chunk_size) {
+            shared[i] = 1;
+            plan.stats.n_shared_chunks++;
+            const uint64_t key = ((uint64_t)(uint32_t)ci.seq_begin << 32) | (uint32_t)ci.seq_end;
+            auto f = run_of.find(key);
+            int r;
+            if (f == run_of.end()) {
+                r = (int)runs.size();
+                run_of.emplace(key, r);
+                runs.push_back(Run{ci.seq_begin, ci.seq_end, 0, {}});
+            } else {
+                r = f->second;
+            }
+            runs[r].chunks.push_back(ci.chunk_id);
+        }
+    }
+    plan.stats.n_runs = (int)runs.size();
+
+    // ---- tile table and units ---------------------------------------------------------------------------
+    std::vector<Unit> units;
+    for (Run& r : runs) {
+        r.tile_begin = (int32_t)plan.tile_chunks.size();
+        plan.tile_chunks.insert(plan.tile_chunks.end(), r.chunks.begin(), r.chunks.end());
+        const int n = r.e - r.b;
+        const int n_blocks = (n + MAX_ROWS_PER_ITEM - 1) / MAX_ROWS_PER_ITEM;
+        const int rows_per_block = (n + n_blocks - 1) / n_blocks;
+        for (int blk = 0; blk < n_blocks; blk++) {
+            const int rb = r.b + blk * rows_per_block;
+            const int rows = std::min(rows_per_block, r.e - rb);
+            if (rows <= 0) continue;
+            const int splits = rows <= 32 ? 4 : (rows <= 64 ? 2 : 1);
+            for (int h = 0; h < n_heads; h++)
+                units.push_back(Unit{r.tile_begin, (int32_t)r.chunks.size(), h, rb, rows, splits,
+                                     chunk_size, false, chunk_first_tile_weight(splits)});
+        }
+    }
+    const size_t n_units_cf = units.size();
+    for (int s = 0; s < n_seqs; s++) {
+        const int32_t tb = (int32_t)plan.tile_chunks.size();
+        for (int32_t p = plan.path_off[s]; p < plan.path_off[s + 1]; p++)
+            if (!shared[path_info[p]]) plan.tile_chunks.push_back(plan.path_chunks[p]);
+        const int32_t nt = (int32_t)plan.tile_chunks.size() - tb;
+        // a non-final private tile must be full: only the tail may be partially filled
+        for (int32_t p = plan.path_off[s]; p + 1 < plan.path_off[s + 1]; p++)
+            if (!shared[path_info[p]] && plan.path_tokens[p] != chunk_size)
+                return fmt("row %ld has a partially filled chunk that is not its tail", s);
+        for (int h = 0; h < n_heads; h++)
+            units.push_back(Unit{tb, nt, h, s, 1, 0, plan.tail_tokens[s], true, 1.0});
+    }
+
+    // ---- cut into items, schedules ----------------------------------------------------------------------
+    int32_t n_slots = 0;
+    if (!split_phases) {
+        cut_units(plan, units, 0, units.size(), n_ctas, plan.cta_item_begin, n_slots);
+        plan.n_items_cf = 0;
+        plan.n_ctas = (int)plan.cta_item_begin.size() - 1;
+        plan.stats.kernels_per_step = 2;
+    } else {
+        cut_units(plan, units, 0, n_units_cf, n_ctas, plan.cta_item_begin_cf, n_slots);
+        plan.n_items_cf = (int)plan.items.size();
+        cut_units(plan, units, n_units_cf, units.size(), n_ctas, plan.cta_item_begin_sf, n_slots);
+        plan.n_ctas = std::max((int)plan.cta_item_begin_cf.size(), (int)plan.cta_item_begin_sf.size()) - 1;
+        plan.stats.kernels_per_step = (plan.n_items_cf > 0 ? 1 : 0) + 2;
+    }
+
+    // ---- merge lists -------------------------------------------------------------------------------------
+    for (const PlanItem& it : plan.items) {
+        const int splits = std::max(1, it.flags >> ITEM_SPLITS_SHIFT);
+        for (int r = 0; r < it.n_rows; r++)
+            plan.merge_off[(size_t)(it.row_begin + r) * n_heads + it.head + 1] += splits;
+    }
+    for (size_t i = 1; i < plan.merge_off.size(); i++) plan.merge_off[i] += plan.merge_off[i - 1];
+    plan.merge_slots.resize(plan.merge_off.back());
+    {
+        std::vector<int32_t> cursor(plan.merge_off.begin(), plan.merge_off.end() - 1);
+        for (const PlanItem& it : plan.items) {
+            const int splits = std::max(1, it.flags >> ITEM_SPLITS_SHIFT);
+            for (int sp = 0; sp < splits; sp++)
+                for (int r = 0; r < it.n_rows; r++)
+                    plan.merge_slots[cursor[(size_t)(it.row_begin + r) * n_heads + it.head]++] =
+                        it.slot_base + sp * it.n_rows + r;
+        }
+    }
+    plan.stats.n_items = (int)plan.items.size();
+    plan.stats.n_slots = n_slots;
+    plan.stats.n_ctas = plan.n_ctas;
+    return "";
+}
+
+}  // namespace ca

@@ -1,0 +1,70 @@
+// ca_host::Attention — the C++ object behind chunk_attn.Attention.
+//
+// Same constructor arguments, methods, row-order contract and error messages as the reference's
+// GPT::Attention (cpp/chunk_attn/attention.h:16-75, cpp/chunk_attn/attention.cpp), so that the
+// reference's llama_hf model and ModelHost drive it unchanged.  Differences in substance:
+// K/V live in ONE device allocation in the library's private tile layout and every data-path
+// operation (prefill scatter, token append, copy-on-write, attention) is a CUDA kernel behind
+// the C ABI of include/chunk_attn_b200.h, launched on torch's current stream.  There is no CPU
+// implementation: constructing it on a non-CUDA device throws.
+#pragma once
+#include <torch/torch.h>
+
+#include <future>
+#include <memory>
+#include <vector>
+
+#include "../../../include/chunk_attn_b200.h"
+#include "prefix_tree.h"
+
+namespace ca_host {
+
+class Attention {
+  public:
+    Attention(int n_heads, int d_head, int chunk_size, int memory_mb = 2048, bool share_prefix = true,
+              int tpp_threshold = 1, torch::Dtype dtype = torch::kFloat16,
+              torch::Device device = torch::Device(torch::kCUDA));
+    // same configuration, fresh empty cache (one per transformer layer in the reference's model)
+    Attention(Attention& other);
+    ~Attention();
+    Attention& operator=(const Attention&) = delete;
+
+    int add_seq(const std::vector<int>& tokens, torch::Tensor k, torch::Tensor v);
+    std::shared_ptr<std::future<int>> add_seq_async(const std::vector<int>& tokens, torch::Tensor k, torch::Tensor v);
+    void remove_seq(int seq_idx);
+    std::vector<Chunk*> append_token(const std::vector<int>& tokens, torch::Tensor k, torch::Tensor v, bool fused = true);
+    void refresh_kernel_context(bool force = false);
+    std::vector<Chunk*> reserve();
+    void clear();
+    int64_t peak_memory_allocated() const { return tree_->pool().peak_memory_allocated(); }
+    void duplicate(int seq_idx, int copies);
+    torch::Tensor forward(torch::Tensor q, int partition = 0);
+
+    Chunk* get_trie() { return tree_->root(); }
+    std::vector<Chunk*> tails() { return tree_->tails(); }
+    void print(Chunk* root = nullptr, int level = 0);
+    std::vector<ca_chunk_info> get_chunks() { return tree_->get_chunks(); }
+
+    // introspection used by the benchmark and the tests
+    ca_plan_stats plan_stats();
+    void set_option(int option, int64_t value);
+    int device_status();
+
+  private:
+    void init();
+    void* stream() const;
+    torch::Tensor to_cache(torch::Tensor t) const;  // dtype/device of the cache, last dim contiguous
+
+    int n_heads_, d_head_, chunk_size_, memory_mb_, tpp_threshold_;
+    bool share_prefix_;
+    torch::TensorOptions options_;
+    int ca_dtype_ = 0;
+    int64_t max_chunks_ = 0;
+    int64_t chunk_bytes_ = 0;
+    torch::Tensor pool_;  // one uint8 tensor: [max_chunks][n_heads][K|V][chunk_size][d_head]
+    std::unique_ptr<PrefixTree> tree_;
+    ca_context* ctx_ = nullptr;
+    bool valid_ = false;
+};
+
+}  // namespace ca_host

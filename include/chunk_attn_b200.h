@@ -1,0 +1,189 @@
+/*
+ * chunk_attn_b200.h — C ABI of the B200 (sm_100a) ChunkAttention decode kernels.
+ *
+ * This is the boundary between the C++ host (prefix tree, chunk pool bookkeeping, the
+ * `Attention` class and its pybind11 surface) and the hand-written CUDA underneath.  It
+ * replaces, function for function, the free functions the reference's host calls in
+ * cpp/chunk_attn/kernel_cuda.h:57-69 and the `KernelContext` they share (kernel_cuda.h:9-55).
+ * Only plain pointers, integers and a CUDA stream cross it: no torch types, no C++ types,
+ * no exceptions.  Every function returns CA_OK (0) or a negative CA_ERR_* code;
+ * ca_last_error() gives the message of the calling thread's last failure.
+ *
+ * There is no CPU implementation behind this ABI.  A function that needs the GPU fails with
+ * CA_ERR_CUDA when no device is usable; nothing falls back to the host.
+ *
+ * Threading: a context is driven by one thread at a time (the reference's `Attention` has the
+ * same contract, src/chunk_attn/models/model_host.py:82-123).  All device work is ordered on
+ * the stream passed to each call.
+ */
+#ifndef CHUNK_ATTN_B200_H_
+#define CHUNK_ATTN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CA_API __attribute__((visibility("default")))
+
+/* ---- status codes ------------------------------------------------------------------------ */
+#define CA_OK 0
+#define CA_ERR_INVALID (-1)      /* bad argument (null pointer, range, unsupported shape)      */
+#define CA_ERR_CUDA (-2)         /* a CUDA runtime call failed; see ca_last_error()            */
+#define CA_ERR_STATE (-3)        /* call order: work list not refreshed, tail slot overflow    */
+#define CA_ERR_DEVICE_STATUS (-4) /* a kernel reported a bounded wait that ran out            */
+
+/* element types of q/k/v/out and of the chunk pool */
+#define CA_DTYPE_F16 0
+#define CA_DTYPE_F32 1
+
+/* `partition` of ca_attention, the reference's meaning (cpp/chunk_attn/attention.h:46):
+ * 0 auto, 1 chunk-first then sequence-first, 2 sequence-first only. */
+#define CA_PARTITION_AUTO 0
+#define CA_PARTITION_CHUNK_FIRST 1
+#define CA_PARTITION_SEQ_FIRST 2
+
+typedef struct ca_context ca_context;
+typedef struct ca_plan ca_plan;
+typedef void* ca_stream; /* cudaStream_t */
+
+/* One entry of the per-step work list the host hands down: a live, non-root chunk of the
+ * prefix tree and the contiguous range of sequence rows whose context contains it.
+ * Replaces GPT::ChunkInfo (cpp/chunk_attn/chunk_info.h:7-15); the chunk is named by its
+ * slot in the pool instead of by pointer, and carries its token count. */
+typedef struct ca_chunk_info {
+    int32_t chunk_id;  /* slot in the pool, 0 <= chunk_id < max_chunks */
+    int32_t n_tokens;  /* tokens currently stored, 0..chunk_size        */
+    int32_t seq_begin; /* first row (inclusive)                         */
+    int32_t seq_end;   /* last row (exclusive)                          */
+} ca_chunk_info;
+
+/* ---- library ------------------------------------------------------------------------------ */
+CA_API const char* ca_last_error(void);
+CA_API int ca_version(void);
+
+/* ---- pool geometry -------------------------------------------------------------------------
+ * The pool is ONE device allocation made by the caller:
+ *     [max_chunks][n_heads][2 (K then V)][chunk_size][d_head] elements.
+ * A (chunk, head) pair therefore owns one contiguous K tile immediately followed by its V tile,
+ * which is what one bulk copy into shared memory fetches.  Inside a tile the 16-byte granules
+ * of token row t are XOR-swizzled with (t & 7) when a row holds a multiple of 8 granules, so
+ * that tensor-core fragment loads from the staged tile are bank-conflict free.  The layout is
+ * private to this library (the reference exposes no K/V tensors to Python either,
+ * cpp/chunk_attn/python_exports.cpp:16-21); ca_tile_elem_offset() is its definition.
+ * Replaces the [n_heads, chunk_size, d_head] views of cpp/chunk_attn/chunk_allocator.cpp:43-55. */
+CA_API int64_t ca_chunk_bytes(int n_heads, int d_head, int chunk_size, int dtype);
+CA_API int64_t ca_tile_elem_offset(int d_head, int dtype, int token, int elem);
+
+/* ---- context --------------------------------------------------------------------------------
+ * Replaces GPT::KernelContext (cpp/chunk_attn/kernel_cuda.h:9-55).  Owns the device work lists
+ * and the partial-result scratch; borrows the pool.  `pool` must be 256-byte aligned. */
+CA_API int ca_context_create(ca_context** out, int device, int n_heads, int d_head, int chunk_size,
+                             int dtype, void* pool, int64_t max_chunks, int tpp_threshold);
+CA_API void ca_context_destroy(ca_context* ctx);
+
+/* 0: one launch walks shared runs and private tails together (default);
+ * 1: the chunk-first items and the sequence-first items are launched as two kernels. */
+#define CA_OPT_SPLIT_PHASES 1
+/* number of persistent CTAs; 0 = one per SM */
+#define CA_OPT_NUM_CTAS 2
+CA_API int ca_context_set_option(ca_context* ctx, int option, int64_t value);
+
+/* Rebuild and upload the work lists after the tree changed.
+ * Replaces GPT::refresh_kernel_context (cpp/chunk_attn/kernel_cuda.h:67-69,
+ * kernel_cuda.cu:1331-1445).  `infos` is a host array in the order the host's depth-first walk
+ * produced it (parents before children); resets the appended-token counter to 0. */
+CA_API int ca_refresh_kernel_context(ca_context* ctx, const ca_chunk_info* infos, int n_infos,
+                                     int n_seqs, ca_stream stream);
+
+/* Write one new K row and one new V row per sequence into that sequence's tail chunk, at slot
+ * (tokens at last refresh + tokens appended since), then count the append.
+ * k, v: device, [n_seqs, n_heads, d_head] contiguous.
+ * Replaces GPT::append_kv (cpp/chunk_attn/kernel_cuda.h:65, kernel_cuda.cu:1273-1318) and the
+ * `delta_tokens += 1` of cpp/chunk_attn/attention.cpp:112. */
+CA_API int ca_append_kv(ca_context* ctx, const void* k, const void* v, int n_seqs, ca_stream stream);
+CA_API int ca_context_delta_tokens(const ca_context* ctx);
+
+/* Decode attention for the current batch: out[s, h, :] = softmax(q[s, h, :] K_s^T / sqrt(d)) V_s
+ * over the context of row s.  q, out: device, [n_seqs, n_heads, d_head] contiguous.
+ * Replaces GPT::attention (cpp/chunk_attn/kernel_cuda.h:57-61, kernel_cuda.cu:1320-1329). */
+CA_API int ca_attention(ca_context* ctx, const void* q, void* out, int n_seqs, int partition,
+                        ca_stream stream);
+
+/* The two halves of ca_attention, separately launchable (profiling, tests):
+ * ca_attn_partials = chunk-first over shared runs + sequence-first over private tails, emitting
+ * per-piece partial outputs with their running max and sum-of-exponentials
+ * (replaces attn_chunks_first / attn_seqs_first, cpp/chunk_attn/kernel_cuda.h:63-64);
+ * ca_attn_merge = online-softmax combination of the partials of every (row, head)
+ * (replaces the merge inlined in kernel_cuda.cu:962-984,1042-1085).
+ * `phases`: 1 chunk-first items only, 2 sequence-first items only, 3 both. */
+CA_API int ca_attn_partials(ca_context* ctx, const void* q, int n_seqs, int phases, ca_stream stream);
+CA_API int ca_attn_merge(ca_context* ctx, void* out, int n_seqs, ca_stream stream);
+
+/* Prefill ingestion: copy tokens [first_token, first_token + n_tokens) of a sequence's K and V
+ * into freshly allocated chunks; token first_token + i goes to chunk_ids[i / chunk_size], row
+ * i % chunk_size.  k, v: device, element strides (stride_token, stride_head, 1).
+ * chunk_ids: HOST array of ceil(n_tokens / chunk_size) pool slots.
+ * Replaces Chunk::append_tokens (cpp/chunk_attn/chunk.cpp:63-81) as driven by
+ * Attention::add_seq (cpp/chunk_attn/attention.cpp:176-180). */
+CA_API int ca_scatter_prefill(ca_context* ctx, const void* k, const void* v, int64_t stride_token,
+                              int64_t stride_head, int first_token, int n_tokens,
+                              const int32_t* chunk_ids, ca_stream stream);
+
+/* Copy-on-write: clone whole chunks (all heads, K and V) src_ids[i] -> dst_ids[i].
+ * src_ids, dst_ids: HOST arrays.  Replaces Chunk::deep_copy (cpp/chunk_attn/chunk.cpp:93-107). */
+CA_API int ca_copy_chunks(ca_context* ctx, const int32_t* src_ids, const int32_t* dst_ids, int n,
+                          ca_stream stream);
+
+/* Read back chunk rows in the logical [n_heads][n_tokens][d_head] order (tests, debugging). */
+CA_API int ca_read_chunk(ca_context* ctx, int chunk_id, int n_tokens, void* k_out, void* v_out,
+                         ca_stream stream);
+
+/* Device status word written by kernels whose bounded waits ran out (0 = clean).  Synchronises
+ * the stream. */
+CA_API int ca_status_read(ca_context* ctx, ca_stream stream, int32_t* status);
+
+/* Per-step counters of the current work list (the roofline metric is computed from them). */
+typedef struct ca_plan_stats {
+    int64_t unique_kv_bytes;   /* sum over live chunks of n_tokens * n_heads * d_head * 2 * sizeof */
+    int32_t n_chunks;          /* live non-root chunks, empty tails included                      */
+    int32_t n_shared_chunks;   /* chunks walked by the chunk-first phase                          */
+    int32_t n_runs;            /* maximal chains of shared chunks with identical sharers          */
+    int32_t n_items;           /* pieces of work after cutting to CTAs                            */
+    int32_t n_slots;           /* partial rows                                                    */
+    int32_t n_ctas;            /* persistent CTAs launched                                        */
+    int32_t fast_path;         /* 1 when the tensor-core/TMA kernels serve this geometry          */
+    int32_t kernels_per_step;  /* launches one ca_attention call makes                            */
+} ca_plan_stats;
+CA_API int ca_context_stats(const ca_context* ctx, ca_plan_stats* out);
+
+/* ---- host-only planner (no GPU needed) -------------------------------------------------------
+ * The work-list builder used by ca_refresh_kernel_context, exposed so that it can be checked on
+ * a machine without a GPU.  Arrays are owned by the plan. */
+#define CA_PLAN_ITEMS 0          /* int32[n_items][8]: tile_begin, n_tiles, head, row_begin,
+                                    n_rows, slot_base, flags(bit0 last tile is a tail; bits 8..:
+                                    token splits), last_tokens                                   */
+#define CA_PLAN_TILE_CHUNKS 1    /* int32[]: pool slots, indexed by tile_begin + j               */
+#define CA_PLAN_CTA_ITEM_BEGIN 2 /* int32[n_ctas + 1]                                            */
+#define CA_PLAN_MERGE_OFF 3      /* int32[n_seqs * n_heads + 1]                                  */
+#define CA_PLAN_MERGE_SLOTS 4    /* int32[]                                                      */
+#define CA_PLAN_PATH_OFF 5       /* int32[n_seqs + 1]   (sequence-first-only path lists)         */
+#define CA_PLAN_PATH_CHUNKS 6    /* int32[]: pool slots root -> leaf                             */
+#define CA_PLAN_PATH_TOKENS 7    /* int32[]: tokens in that chunk at refresh                     */
+#define CA_PLAN_TAIL_CHUNK 8     /* int32[n_seqs]                                                */
+#define CA_PLAN_TAIL_TOKENS 9    /* int32[n_seqs]                                                */
+#define CA_PLAN_CTA_ITEM_BEGIN_CF 10 /* split-phase schedules: chunk-first items                 */
+#define CA_PLAN_CTA_ITEM_BEGIN_SF 11 /* split-phase schedules: sequence-first items              */
+CA_API int ca_plan_build(ca_plan** out, const ca_chunk_info* infos, int n_infos, int n_seqs,
+                         int n_heads, int chunk_size, int tpp_threshold, int n_ctas,
+                         int64_t max_chunks, int split_phases);
+CA_API int ca_plan_array(const ca_plan* plan, int which, const int32_t** data, int64_t* count);
+CA_API int ca_plan_stats_get(const ca_plan* plan, ca_plan_stats* out);
+CA_API void ca_plan_destroy(ca_plan* plan);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CHUNK_ATTN_B200_H_ */

@@ -1,0 +1,91 @@
+"""numpy emulation of what the kernels do with a work list (plan): every item produces partial
+(max, sum, O) rows exactly as the persistent kernel's warps would, and the merge lists combine
+them.  It lets the planner be checked end to end against dense attention on a machine without a
+GPU: any tile that is dropped, duplicated, mis-assigned to a row or mis-merged shows up as a
+numerical mismatch."""
+import math
+
+import numpy as np
+
+from chunk_attn import cabi
+
+
+def emulate(plan, kv_of_chunk, q, chunk_size, delta=0, schedule="fused"):
+    """plan: cabi.Plan; kv_of_chunk: chunk_id -> (K [H, C, d], V [H, C, d]) float arrays;
+    q: [n_seqs, H, d].  Returns out [n_seqs, H, d] float64 and the list of (cta, item) visits."""
+    items = plan.items()
+    tiles = plan.array(cabi.PLAN_TILE_CHUNKS)
+    st = plan.stats()
+    n_seqs, H, d = q.shape
+    scale = 1.0 / math.sqrt(d)
+    part_o = np.full((st["n_slots"], d), np.nan)
+    part_m = np.full(st["n_slots"], np.nan)
+    part_l = np.full(st["n_slots"], np.nan)
+
+    if schedule == "fused":
+        begins = [plan.array(cabi.PLAN_CTA_ITEM_BEGIN)]
+    else:
+        begins = [plan.array(cabi.PLAN_CTA_ITEM_BEGIN_CF), plan.array(cabi.PLAN_CTA_ITEM_BEGIN_SF)]
+    visited = np.zeros(len(items), np.int32)
+    loads = []
+    for cta_begin in begins:
+        for c in range(len(cta_begin) - 1):
+            w = 0
+            for i in range(cta_begin[c], cta_begin[c + 1]):
+                visited[i] += 1
+                w += items[i][1]
+            loads.append(w)
+    assert (visited == 1).all(), "every item must be walked by exactly one CTA"
+
+    for (tile_begin, n_tiles, head, row_begin, n_rows, slot_base, flags, last_tokens) in items:
+        splits = flags >> 8
+        tail = flags & 1
+        ks, vs = [], []
+        for j in range(n_tiles):
+            nt = chunk_size
+            if j == n_tiles - 1:
+                nt = min(chunk_size, last_tokens + (delta if tail else 0))
+            K, V = kv_of_chunk[int(tiles[tile_begin + j])]
+            ks.append((K[head], nt))
+            vs.append(V[head])
+        if splits == 0:
+            assert n_rows == 1
+            groups = [(slot_base, [(0, chunk_size)])]  # one slot, all tokens
+        else:
+            tw = chunk_size // splits
+            groups = [(slot_base + sp * n_rows, [(sp * tw, (sp + 1) * tw)]) for sp in range(splits)]
+        qr = q[row_begin:row_begin + n_rows, head, :].astype(np.float64)
+        for slot0, ranges in groups:
+            lo, hi = ranges[0]
+            kk = [k[lo:min(hi, nt)] for (k, nt) in ks]
+            vv = [v[lo:min(hi, nt)] for v, (k, nt) in zip(vs, ks)]
+            Kc = np.concatenate(kk, axis=0).astype(np.float64) if kk else np.zeros((0, d))
+            Vc = np.concatenate(vv, axis=0).astype(np.float64) if vv else np.zeros((0, d))
+            if Kc.shape[0] == 0:
+                part_m[slot0:slot0 + n_rows] = -1e30
+                part_l[slot0:slot0 + n_rows] = 0
+                part_o[slot0:slot0 + n_rows] = 0
+                continue
+            s = qr @ Kc.T * scale
+            m = s.max(axis=1)
+            p = np.exp(s - m[:, None])
+            part_m[slot0:slot0 + n_rows] = m
+            part_l[slot0:slot0 + n_rows] = p.sum(axis=1)
+            part_o[slot0:slot0 + n_rows] = p @ Vc
+
+    merge_off = plan.array(cabi.PLAN_MERGE_OFF)
+    merge_slots = plan.array(cabi.PLAN_MERGE_SLOTS)
+    used = np.zeros(st["n_slots"], np.int32)
+    out = np.zeros((n_seqs, H, d))
+    for s_ in range(n_seqs):
+        for h in range(H):
+            sl = merge_slots[merge_off[s_ * H + h]:merge_off[s_ * H + h + 1]]
+            used[sl] += 1
+            m = part_m[sl]
+            assert not np.isnan(m).any(), "merge list names a slot nobody wrote"
+            M = m.max()
+            w = np.exp(m - M)
+            L = (w * part_l[sl]).sum()
+            out[s_, h] = (w[:, None] * part_o[sl]).sum(axis=0) / L if L > 0 else 0.0
+    assert (used == 1).all(), "every partial slot must be merged exactly once"
+    return out, loads
