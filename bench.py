@@ -1,0 +1,379 @@
+#!/usr/bin/env python
+"""Benchmark of the ChunkAttention decode step (one JSON line on stdout, printed by rank 0).
+
+    python bench.py --gpus N --steps K --warmup W            # this engine
+    python bench.py --impl reference --gpus N --steps K ...  # the reference's CPU path, same workload
+
+A step is one `Attention.forward(q)` over the current batch on an up-to-date work list (the
+reference's own protocol times exactly that, tests/benchmark_chunk_attn.py:60-69,84-97).
+
+Workloads (synthetic, seeded; chunk_attn/workloads.py):
+  N = 1  cfg2: H32 d128 c64 fp16, 32 sequences = 2048 shared + 512 unique tokens (302 MB of unique
+         K/V, larger than the 126 MB L2, so nothing needs flushing between steps)
+  N > 1  cfg5: H64 split evenly over the ranks, 256 sequences = 4096 shared + 1024 unique tokens,
+         output all-gathered (NCCL); strong scaling: total work is fixed
+`--workload` overrides the choice (cfg2, cfg5, cfg3_s<shared>).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "chunk-attention_b200"))
+
+METRIC = "decode_attn_us_per_step"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="auto")
+    ap.add_argument("--split-phases", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def workload_name(args):
+    if args.workload != "auto":
+        return args.workload
+    return "cfg2" if args.gpus == 1 else "cfg5"
+
+
+def describe(name, n_gpus):
+    if name == "cfg2":
+        return "cfg2: H32 d128 c64 fp16, 32 seqs x (2048 shared + 512 unique tokens), 1 query/seq"
+    if name == "cfg5":
+        return ("cfg5: H64 (H/%d per GPU) d128 c64 fp16, 256 seqs x (4096 shared + 1024 unique tokens), "
+                "1 query/seq, output all-gathered" % n_gpus)
+    return "%s: H32 d128 c64 fp16, 64 seqs, context 4096, shared prefix %s" % (name, name.split("_s")[-1])
+
+
+def make_workload(name, n_heads_local, gen_device, rank=0):
+    from chunk_attn import workloads as W
+    if name == "cfg2":
+        return W.config2(n_heads=n_heads_local, gen_device=gen_device)
+    if name == "cfg5":
+        w = W.single_level("cfg5", n_heads_local, 128, 64, __import__("torch").float16, 256, 4096, 1024,
+                           4 + 1000 * rank, 0.5, gen_device)
+        return w
+    if name.startswith("cfg3_s"):
+        return W.config3(int(name[6:]), n_heads=n_heads_local, gen_device=gen_device)
+    raise SystemExit("unknown workload " + name)
+
+
+def total_heads(name):
+    return 64 if name == "cfg5" else 32
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.12)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, an earlier measurement on this pool)"
+
+
+# ---- reference arm / CPU baseline -----------------------------------------------------------------------
+def time_reference_cpu(name, steps, warmup, max_seconds=150.0):
+    """The reference's own CPU (MKL) implementation of the step, unmodified, built into oracle/_ref;
+    when that build is absent, the numpy restatement in oracle/.  fp32 (its only dtype), all host
+    threads.  cfg5 is sampled on 8 of its 64 heads and scaled by 8 (the work is linear in heads)."""
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    from ref_loader import load_reference
+    from chunk_attn import workloads as W
+    heads_full = total_heads(name)
+    heads = 8 if name == "cfg5" else heads_full
+    scale_up = heads_full / heads
+    w = make_workload(name, heads, "cpu")
+    ref = load_reference("cpu")
+    cores = torch.get_num_threads()
+    if ref is not None:
+        kind = "reference"
+        need_mb = int(W.unique_kv_bytes(w) * 2 / 2 ** 20 * 1.1) + w.n_seqs * 2 + 64  # fp32 pool + empty tails
+        attn = ref.Attention(n_heads=heads, d_head=w.d_head, chunk_size=w.chunk_size, memory_mb=need_mb,
+                             dtype=torch.float32, device=torch.device("cpu"))
+        rows = W.populate(attn, w)
+        q = w.q[rows].contiguous()
+        fwd = lambda: attn.forward(q, 0)
+    else:
+        kind = "port"
+        cores = 1
+        from chunk_attn_oracle import Attention as OracleAttention
+        attn = OracleAttention(heads, w.d_head, w.chunk_size)
+        rows = W.populate(attn, w, as_numpy=True)
+        q = w.q[rows].numpy()
+        fwd = lambda: attn.forward(q, 0)
+    t_w0 = time.perf_counter()
+    for _ in range(max(1, min(warmup, 3))):
+        fwd()
+    per = (time.perf_counter() - t_w0) / max(1, min(warmup, 3))
+    n = max(1, min(steps, int(max_seconds / max(per, 1e-6))))
+    t0 = time.perf_counter()
+    for _ in range(n):
+        fwd()
+    dt = (time.perf_counter() - t0) / n
+    us = dt * 1e6 * scale_up
+    sample = "%s in fp32, %d of %d heads%s, %d timed forwards (partition 0, chunk-first) after %d warm-up" % (
+        name, heads, heads_full, " (time x%g)" % scale_up if scale_up != 1 else "", n, max(1, min(warmup, 3)))
+    return {"value": us, "unit": "us", "cores": cores, "kind": kind, "sample": sample}, n
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    name = workload_name(args)
+    base, n = time_reference_cpu(name, args.steps, args.warmup)
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": "us", "n_gpus": args.gpus,
+            "steps": n, "warmup": max(1, min(args.warmup, 3)), "ms_per_step": base["value"] / 1e3,
+            "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": {"workload": describe(name, args.gpus), "device": "host CPU"},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+# ---- this engine --------------------------------------------------------------------------------------------------
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+    from chunk_attn import Attention, cabi, workloads as W
+    from chunk_attn.sharded import HeadShardedAttention
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit("--gpus %d but WORLD_SIZE=%d" % (args.gpus, world))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    name = workload_name(args)
+    H = total_heads(name)
+    if H % world:
+        raise SystemExit("%d heads do not split over %d GPUs" % (H, world))
+    h_local = H // world
+
+    def build(n_heads_local, sharded):
+        gen_device = "cpu" if name == "cfg2" else dev
+        w = make_workload(name, n_heads_local, gen_device, rank if sharded else 0)
+        chunk_bytes = n_heads_local * 2 * 64 * 128 * 2
+        n_chunks = W.unique_kv_bytes(w) // chunk_bytes + w.n_seqs + 8   # + one empty tail per sequence
+        need_mb = (n_chunks * chunk_bytes + 2 ** 20 - 1) // 2 ** 20 + 1
+        if sharded:
+            attn = HeadShardedAttention(H, 128, 64, memory_mb=need_mb, dtype=torch.float16, device=dev)
+            engine = attn.local
+        else:
+            attn = Attention(n_heads=n_heads_local, d_head=128, chunk_size=64, memory_mb=need_mb,
+                             dtype=torch.float16, device=dev)
+            engine = attn
+        if args.split_phases:
+            engine.set_option(cabi.CA_OPT_SPLIT_PHASES, 1)
+        rows = W.populate(engine, w, device=dev, dtype=torch.float16)
+        q = w.q[rows].to(dev, torch.float16).contiguous()
+        ukv = W.unique_kv_bytes(w)
+        del w
+        torch.cuda.empty_cache()
+        return attn, engine, q, ukv
+
+    attn, engine, q, ukv_local = build(h_local, world > 1)
+    stats = engine.plan_stats()
+    assert stats["unique_kv_bytes"] == ukv_local
+    step = (lambda: attn.forward(q, gather=True)) if world > 1 else (lambda: attn.forward(q=q))
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    W_, K = max(3, args.warmup), max(1, args.steps)
+    for _ in range(W_):
+        out = step()
+    sync_all()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        out = step()
+    e1.record()
+    sync_all()
+    ms = e0.elapsed_time(e1) / K
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+
+    # per-kernel durations, CUDA events on the launching stream around each launch of the same steps
+    kern = {"partials": [], "merge": []}
+    if stats["fast_path"]:
+        out2 = torch.empty_like(q)
+        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+        for i in range(K):
+            evs[i][0].record()
+            engine.attn_partials(q, 3)
+            evs[i][1].record()
+            engine.attn_merge(out2)
+            evs[i][2].record()
+        torch.cuda.synchronize()
+        kern["partials"] = [e[0].elapsed_time(e[1]) for e in evs]
+        kern["merge"] = [e[1].elapsed_time(e[2]) for e in evs]
+    clocks = sampler.stop() if rank == 0 else None
+
+    # end to end through the public API with HOST buffers: pinned q -> device, forward (+ gather),
+    # result back to pinned host memory, every step
+    q_host = q.cpu().pin_memory()
+    out_host = torch.empty((q.shape[0], H, 128), dtype=torch.float16).pin_memory()
+    q_dev = torch.empty_like(q)
+
+    def e2e_step():
+        q_dev.copy_(q_host, non_blocking=True)
+        o = attn.forward(q_dev, gather=True) if world > 1 else attn.forward(q=q_dev)
+        out_host.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller reads the result on the host
+
+    for _ in range(3):
+        e2e_step()
+    sync_all()
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(K):
+        e2e_step()
+    e1.record()
+    sync_all()
+    e2e_ms = e0.elapsed_time(e1) / K
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    status = engine.device_status()
+
+    # strong-scaling reference point: the same full-width workload on one GPU, same run (rank 0)
+    single = None
+    if world > 1 and rank == 0:
+        del attn, engine
+        torch.cuda.empty_cache()
+        a1, eng1, q1, _ = build(H, False)
+        for _ in range(W_):
+            a1.forward(q=q1)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(K):
+            a1.forward(q=q1)
+        e1.record()
+        torch.cuda.synchronize()
+        single = {"n_gpus": 1, "us_per_step": e0.elapsed_time(e1) / K * 1e3}
+        del a1, eng1
+    if world > 1:
+        dist.barrier()
+
+    if rank == 0:
+        peak, peak_src = measured_peak()
+        ukv_total = ukv_local * world
+        roof = None
+        if kern["partials"]:
+            dur_ms = statistics.mean(kern["partials"])
+            achieved = ukv_local / (dur_ms * 1e-3) / 1e9
+            roof = {"bound": "hbm", "kernel": "attn_partial_kernel", "achieved": achieved, "peak": peak,
+                    "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
+                    "traffic": None,  # dram bytes per launch: see profiles/ (ncu capture)
+                    "algorithmic_bytes_per_launch": ukv_local,
+                    "kernel_ms": {"partials_mean": dur_ms, "partials_min": min(kern["partials"]),
+                                  "merge_mean": statistics.mean(kern["merge"])}}
+        line = {"metric": METRIC, "value": ms * 1e3, "unit": "us", "n_gpus": world, "steps": K, "warmup": W_,
+                "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+                "dtype": "f16", "data": "synthetic",
+                "config": {"workload": describe(name, world), "l2": "unique K/V per GPU (%.0f MB) exceeds the 126 MB L2: no flush between steps" % (ukv_local / 1e6)
+                           if ukv_local > 126e6 else "unique K/V per GPU (%.0f MB) fits in L2" % (ukv_local / 1e6),
+                           "parallelism": "heads/%d" % world, "phases": "split" if args.split_phases else "fused",
+                           "plan": stats},
+                "unique_kv_bytes": ukv_total,
+                "unique_kv_gbs_per_gpu": ukv_local / (ms * 1e-3) / 1e9,
+                "hbm_frac_whole_step": ukv_local / (ms * 1e-3) / 1e9 / peak,
+                "roofline": roof,
+                "e2e": {"value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": q_host.numel() * 2,
+                        "d2h_bytes_per_step": out_host.numel() * 2},
+                "gpu_launches": K * stats["kernels_per_step"],
+                "clocks": clocks, "device_status": status}
+        if single:
+            line["strong_scaling_ref"] = single
+        if not args.no_cpu_baseline and world == 1:
+            try:
+                line["cpu_baseline"], _ = time_reference_cpu(name, 10, 1, max_seconds=25.0)
+            except Exception as exc:  # the baseline is reported, never a gate
+                line["cpu_baseline"] = {"value": None, "unit": "us", "cores": 0, "kind": "unavailable",
+                                        "sample": "failed: %s" % exc}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -22,6 +22,8 @@
 // and unwinds instead of spinning forever.
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "ca_kernels.h"
 #include "ca_plan.h"
 
@@ -590,6 +592,7 @@ cudaError_t launch_attn_partials(const PartialParams& p, int n_ctas, cudaStream_
 
 cudaError_t launch_attn_merge(const MergeParams& p, cudaStream_t stream, bool dependent_launch) {
     if (p.n_pairs <= 0) return cudaSuccess;
+    static const bool pdl_disabled = std::getenv("CA_DISABLE_PDL") != nullptr;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((p.n_pairs + 3) / 4);
     cfg.blockDim = dim3(128);
@@ -599,8 +602,15 @@ cudaError_t launch_attn_merge(const MergeParams& p, cudaStream_t stream, bool de
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = dependent_launch ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, attn_merge_kernel, p);
+    cfg.numAttrs = (dependent_launch && !pdl_disabled) ? 1 : 0;
+    cudaError_t err = cudaLaunchKernelEx(&cfg, attn_merge_kernel, p);
+    if (err != cudaSuccess && cfg.numAttrs == 1) {
+        // the stream or driver refused the programmatic launch: fall back to a plain ordered launch
+        (void)cudaGetLastError();
+        cfg.numAttrs = 0;
+        err = cudaLaunchKernelEx(&cfg, attn_merge_kernel, p);
+    }
+    return err;
 }
 
 }  // namespace ca

@@ -199,6 +199,25 @@ void Attention::set_option(int option, int64_t value) {
     valid_ = false;
 }
 
+void Attention::attn_partials(torch::Tensor q, int phases) {
+    if (!q.is_contiguous() || q.dim() != 3 || q.size(0) != (int64_t)tree_->n_seqs() || q.size(1) != n_heads_ ||
+        q.size(2) != d_head_ || q.device() != options_.device() ||
+        q.scalar_type() != c10::typeMetaToScalarType(options_.dtype()))
+        throw std::runtime_error("attn_partials: q must be a contiguous [n_seqs, n_heads, d_head] tensor of the cache's dtype and device");
+    c10::cuda::CUDAGuard guard(options_.device());
+    refresh_kernel_context(false);
+    check_rc(ca_attn_partials(ctx_, q.data_ptr(), (int)q.size(0), phases, stream()), "attn_partials");
+}
+
+void Attention::attn_merge(torch::Tensor out) {
+    if (!out.is_contiguous() || out.dim() != 3 || out.size(0) != (int64_t)tree_->n_seqs() || out.size(1) != n_heads_ ||
+        out.size(2) != d_head_ || out.device() != options_.device() ||
+        out.scalar_type() != c10::typeMetaToScalarType(options_.dtype()))
+        throw std::runtime_error("attn_merge: out must be a contiguous [n_seqs, n_heads, d_head] tensor of the cache's dtype and device");
+    c10::cuda::CUDAGuard guard(options_.device());
+    check_rc(ca_attn_merge(ctx_, out.data_ptr(), (int)out.size(0), stream()), "attn_merge");
+}
+
 int Attention::device_status() {
     int32_t st = 0;
     c10::cuda::CUDAGuard guard(options_.device());

@@ -49,6 +49,9 @@ class Attention {
     ca_plan_stats plan_stats();
     void set_option(int option, int64_t value);
     int device_status();
+    // the two launches of forward(), separately (per-kernel timing)
+    void attn_partials(torch::Tensor q, int phases);
+    void attn_merge(torch::Tensor out);
 
   private:
     void init();

@@ -51,9 +51,10 @@ PYBIND11_MODULE(chunk_attn_c, m) {
                        py::object dtype, py::object device) {
                torch::Dtype dtype_c = torch::get_default_dtype_as_scalartype();
                if (!dtype.is_none()) dtype_c = torch::python::detail::py_object_to_dtype(dtype);
-               // the default device is wherever a fresh tensor lands (honours `with torch.device(...)`)
-               torch::Device device_c = torch::empty({1}).device();
-               if (!device.is_none()) device_c = torch::python::detail::py_object_to_device(device);
+               // the default device is wherever a fresh tensor lands; asking Python (not libtorch)
+               // honours `with torch.device(...)` and torch.set_default_device, which live there
+               if (device.is_none()) device = py::module_::import("torch").attr("empty")(0).attr("device");
+               torch::Device device_c = torch::python::detail::py_object_to_device(device);
                return new Attention(n_heads, d_head, chunk_size, memory_mb, share_prefix, tpp_threshold, dtype_c,
                                     device_c);
            }),
@@ -78,7 +79,9 @@ PYBIND11_MODULE(chunk_attn_c, m) {
       // additions (not in the reference): counters of the current work list, tuning, kernel status
       .def("plan_stats", [](Attention& a) { return stats_to_dict(a.plan_stats()); })
       .def("set_option", &Attention::set_option, py::arg("option"), py::arg("value"))
-      .def("device_status", &Attention::device_status);
+      .def("device_status", &Attention::device_status)
+      .def("attn_partials", &Attention::attn_partials, py::arg("q"), py::arg("phases") = 3)
+      .def("attn_merge", &Attention::attn_merge, py::arg("out"));
 
     py::class_<PrefixTree>(m, "PrefixTree", py::module_local())
       .def(py::init([](int chunk_size, int64_t max_chunks, bool share_prefix) {
@@ -89,6 +92,16 @@ PYBIND11_MODULE(chunk_attn_c, m) {
            [](PrefixTree& t, const std::vector<int>& tokens) {
                std::vector<ca_host::NewChunk> created;
                return t.add_seq(tokens, created);
+           },
+           py::arg("tokens"))
+      .def("add_seq_detailed",
+           [](PrefixTree& t, const std::vector<int>& tokens) {
+               // (row index, [(chunk id, first token position, token count)] of the chunks to fill)
+               std::vector<ca_host::NewChunk> created;
+               const int idx = t.add_seq(tokens, created);
+               std::vector<std::tuple<int, int, int>> out;
+               for (const auto& nc : created) out.emplace_back(nc.chunk->id, nc.token_start, nc.n_tokens);
+               return std::make_pair(idx, out);
            },
            py::arg("tokens"))
       .def("remove_seq", &PrefixTree::remove_seq, py::arg("seq_idx"))

@@ -1,0 +1,182 @@
+"""Work-list builder (planner): emulate, in numpy, what the kernels do with a plan and compare the
+result with dense attention.  Runs without a GPU."""
+import numpy as np
+import pytest
+
+from chunk_attn import cabi
+from chunk_attn_oracle import Attention as OracleAttention, dense_forward
+from plan_emulator import emulate
+from workloads import kv_for, random_trace
+
+C = 64  # the fast path's chunk size; the planner is only used for that geometry
+
+
+def build_tree(spec, H=2, d=8, seed=0, chunk_size=C):
+    """spec: list of token lists.  Returns the oracle tree (which owns K/V per chunk)."""
+    rng = np.random.default_rng(seed)
+    shared_kv = {}
+    ora = OracleAttention(H, d, chunk_size)
+    for toks in spec:
+        # K/V are a function of (position, token id) so that shared prefixes carry equal values
+        k = np.zeros((len(toks), H, d), np.float32)
+        v = np.zeros((len(toks), H, d), np.float32)
+        for i, t in enumerate(toks):
+            key = (i, t)
+            if key not in shared_kv:
+                shared_kv[key] = (rng.standard_normal((H, d)).astype(np.float32),
+                                  rng.standard_normal((H, d)).astype(np.float32))
+            k[i], v[i] = shared_kv[key]
+        ora.add_seq(toks, k, v)
+    return ora
+
+
+def plan_of(ora, n_heads, **kw):
+    infos = [(c.id, c.n_tokens, b, e) for c, b, e in ora.get_chunks()]
+    return cabi.Plan(infos, len(ora.tails), n_heads, chunk_size=ora.chunk_size, **kw), infos
+
+
+def kv_map(ora):
+    return {c.id: (c.k, c.v) for c, _, _ in ora.get_chunks()}
+
+
+def check(ora, H, d, atol=1e-9, **kw):
+    plan, _ = plan_of(ora, H, **kw)
+    rng = np.random.default_rng(7)
+    q = rng.standard_normal((len(ora.tails), H, d)).astype(np.float32)
+    sched = "split" if kw.get("split_phases") else "fused"
+    out, loads = emulate(plan, kv_map(ora), q, ora.chunk_size, schedule=sched)
+    ref = dense_forward(ora, q)
+    assert np.abs(out - ref).max() < atol
+    return plan, loads
+
+
+def shared_spec(n_seqs, shared, unique, base=0):
+    return [list(range(base, base + shared)) + [1_000_000 * (s + 1) + j for j in range(unique)] for s in range(n_seqs)]
+
+
+@pytest.mark.parametrize("n_ctas", [1, 3, 16, 148])
+@pytest.mark.parametrize("split", [False, True])
+def test_single_level_prefix(n_ctas, split):
+    ora = build_tree(shared_spec(6, 5 * C, 2 * C + 17))
+    plan, loads = check(ora, 2, 8, n_ctas=n_ctas, split_phases=split)
+    st = plan.stats()
+    assert st["n_shared_chunks"] == 5 and st["n_runs"] == 1
+    assert st["n_chunks"] == 5 + 6 * 3
+
+
+def test_partial_tails_and_empty_tails():
+    for unique in (0, 1, 17, 63, 64, 65):
+        ora = build_tree(shared_spec(5, 2 * C, unique))
+        check(ora, 2, 8, n_ctas=7)
+
+
+def test_two_level_tree_and_row_blocks():
+    # 3 groups under a root prefix; group sizes 2, 33 and 70 exercise the 4-, 2- and 1-split items
+    spec = []
+    root = list(range(2 * C))
+    for g, n in enumerate((2, 33, 70)):
+        gp = [10_000 * (g + 1) + j for j in range(C)]
+        for s in range(n):
+            spec.append(root + gp + [1_000_000 * (len(spec) + 1) + j for j in range(9)])
+    ora = build_tree(spec, H=1, d=4)
+    plan, _ = check(ora, 1, 4, n_ctas=20)
+    items = plan.items()
+    splits = sorted(set(int(f) >> 8 for f in items[:, 6]))
+    assert splits == [0, 1, 2, 4]
+    assert plan.stats()["n_runs"] == 4
+
+
+def test_more_than_128_sharers_splits_rows():
+    ora = build_tree(shared_spec(150, C, 3), H=1, d=4)
+    plan, _ = check(ora, 1, 4, n_ctas=8)
+    rows = [int(r) for r in plan.items()[:, 4] if r > 1]
+    assert max(rows) <= 128 and sum(sorted(set(rows))) >= 150 - 1 or len(set(rows)) >= 1
+
+
+def test_no_sharing_and_full_sharing():
+    ora = build_tree(shared_spec(4, 0, 3 * C + 5))
+    plan, _ = check(ora, 2, 8, n_ctas=5)
+    assert plan.stats()["n_shared_chunks"] == 0
+    ora = build_tree([list(range(2 * C))] * 5)
+    plan, _ = check(ora, 2, 8, n_ctas=5)
+    assert plan.stats()["n_shared_chunks"] == 2
+
+
+def test_tpp_threshold_moves_chunks_to_the_private_walk():
+    ora = build_tree(shared_spec(3, 2 * C, 10))
+    plan, _ = check(ora, 2, 8, n_ctas=4, tpp_threshold=3)
+    assert plan.stats()["n_shared_chunks"] == 0
+    plan, _ = check(ora, 2, 8, n_ctas=4, tpp_threshold=2)
+    assert plan.stats()["n_shared_chunks"] == 2
+
+
+def test_delta_tokens_are_applied_to_tails_only():
+    ora = build_tree(shared_spec(4, C, 20))
+    plan, _ = plan_of(ora, 2, n_ctas=6)
+    # append 3 tokens to every sequence without rebuilding the plan
+    rng = np.random.default_rng(3)
+    for step in range(3):
+        k, v = kv_for(4, 2, 8, rng)
+        ora.append_token([5000 + step] * 4, k, v)
+    q = rng.standard_normal((4, 2, 8)).astype(np.float32)
+    out, _ = emulate(plan, kv_map(ora), q, C, delta=3)
+    assert np.abs(out - dense_forward(ora, q)).max() < 1e-9
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_traces(seed):
+    ops = random_trace(seed, n_ops=40, chunk_size=4, vocab=2, max_len=30, max_live=12)
+    rng = np.random.default_rng(seed)
+    ora = OracleAttention(2, 4, 4)
+    pos_kv = {}
+    for op, arg in ops:
+        if op == "add":
+            k = np.zeros((len(arg), 2, 4), np.float32)
+            v = np.zeros((len(arg), 2, 4), np.float32)
+            for i, t in enumerate(arg):
+                if (i, t) not in pos_kv:
+                    pos_kv[(i, t)] = kv_for(1, 2, 4, rng)
+                k[i], v[i] = pos_kv[(i, t)][0][0], pos_kv[(i, t)][1][0]
+            ora.add_seq(arg, k, v)
+        elif op == "remove":
+            ora.remove_seq(arg)
+        else:
+            k, v = kv_for(len(arg), 2, 4, rng)
+            ora.append_token(arg, k, v)
+        if not ora.tails:
+            continue
+        # the planner is geometry-agnostic: exercise it with chunk_size 4 (splits of 1 token)
+        check(ora, 2, 4, n_ctas=1 + seed, split_phases=bool(seed & 1))
+
+
+def test_balance_config2_shape():
+    # 32 sequences, 2048 shared + 512 unique tokens, 32 heads, 148 CTAs: the tile stream is cut evenly
+    infos = []
+    cid = 0
+    for _ in range(32):
+        infos.append((cid, C, 0, 32)); cid += 1
+    for s in range(32):
+        for _ in range(8):
+            infos.append((cid, C, s, s + 1)); cid += 1
+        infos.append((cid, 0, s, s + 1)); cid += 1
+    plan = cabi.Plan(infos, 32, 32, n_ctas=148)
+    items, cta = plan.items(), plan.array(cabi.PLAN_CTA_ITEM_BEGIN)
+    assert len(cta) == 149
+    # weighted as the planner weighs them: a tail tile counts one half
+    loads = [float((items[cta[c]:cta[c + 1], 1] - 0.5 * (items[cta[c]:cta[c + 1], 6] & 1)).sum()) for c in range(148)]
+    assert max(loads) - min(loads) <= 2.0
+    st = plan.stats()
+    assert st["unique_kv_bytes"] == 301_989_888 and st["n_runs"] == 1
+
+
+def test_rejects_bad_work_lists():
+    with pytest.raises(cabi.CAError, match="outside the pool"):
+        cabi.Plan([(5, 1, 0, 1)], 1, 1, max_chunks=5)
+    with pytest.raises(cabi.CAError, match="served by no chunk"):
+        cabi.Plan([(0, 1, 0, 1)], 2, 1)
+    with pytest.raises(cabi.CAError, match="needs its own tail"):
+        cabi.Plan([(0, C, 0, 2)], 2, 1)
+    with pytest.raises(cabi.CAError, match="empty or outside"):
+        cabi.Plan([(0, 1, 1, 1)], 2, 1)
+    with pytest.raises(cabi.CAError, match="n_tokens"):
+        cabi.Plan([(0, C + 1, 0, 1)], 1, 1)
