@@ -1,0 +1,65 @@
+"""The C-ABI library loads without a GPU, exports every symbol the public header declares, and its
+GPU entry points fail loudly (never fall back) when no device is usable."""
+import ctypes as C
+import os
+import re
+
+import pytest
+import torch
+
+from chunk_attn import cabi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "chunk_attn_b200.h")).read()
+    return sorted(set(re.findall(r"CA_API\s+[\w\s\*]+?\b(ca_\w+)\s*\(", text)))
+
+
+def test_header_and_library_agree():
+    declared = declared_symbols()
+    assert len(declared) >= 22
+    assert declared == sorted(cabi.EXPORTED)
+    for name in declared:
+        assert hasattr(cabi.lib, name), name
+
+
+def test_host_only_entry_points():
+    assert cabi.lib.ca_version() >= 100
+    assert cabi.lib.ca_chunk_bytes(32, 128, 64, cabi.CA_DTYPE_F16) == 1 << 20
+    assert cabi.lib.ca_chunk_bytes(32, 128, 64, 7) == -1
+    # the tile layout: a permutation of the row's granules, identity when rows are short
+    for d, dt, es in ((128, cabi.CA_DTYPE_F16, 2), (64, cabi.CA_DTYPE_F32, 4), (4, cabi.CA_DTYPE_F32, 4),
+                      (20, cabi.CA_DTYPE_F16, 2)):
+        for t in (0, 1, 7, 9):
+            offs = [cabi.lib.ca_tile_elem_offset(d, dt, t, e) for e in range(d)]
+            assert sorted(offs) == list(range(t * d, (t + 1) * d))
+            per16 = 16 // es
+            if d % per16 == 0 and (d // per16) % 8 == 0:
+                assert offs[0] == t * d + ((0 ^ (t & 7)) * per16)
+            else:
+                assert offs == list(range(t * d, (t + 1) * d))
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the behaviour without a device")
+def test_gpu_entry_points_fail_loudly_without_a_device():
+    h = C.c_void_p()
+    rc = cabi.lib.ca_context_create(C.byref(h), 0, 2, 128, 64, cabi.CA_DTYPE_F16, None, 0, 1)
+    assert rc == cabi.CA_ERR_CUDA and not h.value
+    assert len(cabi.lib.ca_last_error()) > 0
+    from chunk_attn import Attention
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        Attention(n_heads=2, d_head=4, chunk_size=2, memory_mb=1, dtype=torch.float32, device=torch.device("cpu"))
+
+
+def test_null_and_bad_arguments():
+    assert cabi.lib.ca_context_create(None, 0, 2, 128, 64, 0, None, 0, 1) == cabi.CA_ERR_INVALID
+    h = C.c_void_p()
+    assert cabi.lib.ca_context_create(C.byref(h), 0, 2, 128, 64, 9, None, 0, 1) == cabi.CA_ERR_INVALID
+    assert cabi.lib.ca_context_create(C.byref(h), 0, 2, 512, 64, 0, None, 0, 1) == cabi.CA_ERR_INVALID
+    assert cabi.lib.ca_attention(None, None, None, 0, 0, None) == cabi.CA_ERR_INVALID
+    assert cabi.lib.ca_append_kv(None, None, None, 0, None) == cabi.CA_ERR_INVALID
+    assert cabi.lib.ca_context_delta_tokens(None) == -1
+    cabi.lib.ca_context_destroy(None)
+    cabi.lib.ca_plan_destroy(None)
