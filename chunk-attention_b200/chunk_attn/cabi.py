@@ -26,8 +26,9 @@ EXPORTED = [
     "ca_context_destroy", "ca_context_set_option", "ca_refresh_kernel_context", "ca_append_kv",
     "ca_context_delta_tokens", "ca_attention", "ca_attn_partials", "ca_attn_merge",
     "ca_scatter_prefill", "ca_copy_chunks", "ca_read_chunk", "ca_status_read", "ca_context_stats",
-    "ca_plan_build", "ca_plan_array", "ca_plan_stats_get", "ca_plan_destroy",
+    "ca_plan_build", "ca_plan_array", "ca_plan_stats_get", "ca_plan_destroy", "ca_attention_static",
 ]
+CA_STATIC_MAX_SLOTS = 16384
 
 
 class ChunkInfo(C.Structure):
@@ -78,6 +79,7 @@ def _load():
         "ca_plan_array": (i32, [vp, i32, C.POINTER(C.POINTER(C.c_int32)), C.POINTER(i64)]),
         "ca_plan_stats_get": (i32, [vp, C.POINTER(PlanStats)]),
         "ca_plan_destroy": (None, [vp]),
+        "ca_attention_static": (i32, [vp, i32, vp, vp, i32, vp, i32, vp, vp, i32, vp, vp, i32, i32, vp, vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

@@ -53,6 +53,11 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 }  // namespace
 
+namespace ca {
+// lets the other translation units of the library leave a message for ca_last_error()
+void set_last_error(const std::string& msg) { g_last_error = msg; }
+}  // namespace ca
+
 struct ca_plan {
     ca::Plan plan;
 };

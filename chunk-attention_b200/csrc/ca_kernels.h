@@ -3,9 +3,13 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <string>
+
 #include "ca_layout.h"
 
 namespace ca {
+
+void set_last_error(const std::string& msg);  // message returned by ca_last_error() on this thread
 
 // Device status word values (first failure wins).
 constexpr int STATUS_OK = 0;

@@ -159,6 +159,44 @@ typedef struct ca_plan_stats {
 } ca_plan_stats;
 CA_API int ca_context_stats(const ca_context* ctx, ca_plan_stats* out);
 
+/* ---- allocation-free decode step ---------------------------------------------------------------
+ * No counterpart in the reference: this entry point exists for callers that cannot allocate device
+ * memory when they reach the decode step, for instance a plugin inside a serving process whose
+ * framework reserved the whole GPU for its own arena at start-up (a raw cudaMalloc then fails or
+ * is forbidden), or a latency-critical loop that cannot take the device-wide synchronisation that
+ * cudaMalloc / cudaFree imply.  ca_attention keeps its partial results in scratch that
+ * ca_refresh_kernel_context grows with cudaMalloc; ca_attention_static keeps them in a fixed
+ * __device__ array inside the library (CA_STATIC_MAX_SLOTS partial rows of 520 bytes, about
+ * 8.1 MiB, resident on every GPU that loads the library until the process exits) and allocates
+ * nothing: no cudaMalloc, no cudaFree, no allocating library routine.
+ *
+ * Same computation and geometry as the tensor-core path of ca_attention (fp16, d_head 128,
+ * chunk_size 64).  The caller passes inputs and outputs only, all in device memory it owns, on the
+ * calling thread's current device:
+ *   pool            the chunk pool (layout above), 256-byte aligned
+ *   q, out          [n_seqs, n_heads, 128] fp16, contiguous
+ *   items .. merge_slots   the work list: the arrays ca_plan_build produces (CA_PLAN_ITEMS,
+ *                   CA_PLAN_TILE_CHUNKS, CA_PLAN_CTA_ITEM_BEGIN with n_ctas + 1 entries,
+ *                   CA_PLAN_MERGE_OFF, CA_PLAN_MERGE_SLOTS), copied to the device by the caller
+ *   n_slots         ca_plan_stats.n_slots of that plan; above CA_STATIC_MAX_SLOTS the call is refused
+ *                   with CA_ERR_INVALID and a message naming both numbers
+ *   delta_tokens    tokens appended to every tail since the plan was built
+ *   status          optional device word for the kernels' bounded-wait status (0 = clean); NULL
+ *                   selects a word inside the library.  It is cleared at the start of each call.
+ *
+ * The first call on a device looks up the device address of the scratch (cudaGetSymbolAddress)
+ * and sets the kernel's shared-memory attribute; make that first call before any stream capture.
+ * All calls on a device share the one scratch array, which still holds the previous call's
+ * partial rows when the next call starts (none of them needs clearing: every row a merge list names
+ * is rewritten first).  Two calls that overlap on the GPU (different streams, or different threads)
+ * therefore race on it: keep calls on one device stream-ordered. */
+#define CA_STATIC_MAX_SLOTS 16384
+CA_API int ca_attention_static(const void* pool, int n_heads, const void* q, void* out, int n_seqs,
+                               const int32_t* items, int n_items, const int32_t* tile_chunks,
+                               const int32_t* cta_item_begin, int n_ctas, const int32_t* merge_off,
+                               const int32_t* merge_slots, int n_slots, int delta_tokens,
+                               int32_t* status, ca_stream stream);
+
 /* ---- host-only planner (no GPU needed) -------------------------------------------------------
  * The work-list builder used by ca_refresh_kernel_context, exposed so that it can be checked on
  * a machine without a GPU.  Arrays are owned by the plan. */
