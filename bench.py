@@ -36,6 +36,7 @@ def parse():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="auto")
     ap.add_argument("--split-phases", type=int, default=0)
+    ap.add_argument("--ctas", type=int, default=0, help="persistent CTAs (0 = one per SM)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
 
@@ -227,6 +228,8 @@ def run_b200(args):
             engine = attn
         if args.split_phases:
             engine.set_option(cabi.CA_OPT_SPLIT_PHASES, 1)
+        if args.ctas:
+            engine.set_option(cabi.CA_OPT_NUM_CTAS, args.ctas)
         rows = W.populate(engine, w, device=dev, dtype=torch.float16)
         q = w.q[rows].to(dev, torch.float16).contiguous()
         ukv = W.unique_kv_bytes(w)
@@ -264,19 +267,27 @@ def run_b200(args):
         ms = float(t.item())
 
     # per-kernel durations, CUDA events on the launching stream around each launch of the same steps
-    kern = {"partials": [], "merge": []}
+    kern = {"partials": [], "merge": [], "chunk_first": [], "seq_first": []}
     if stats["fast_path"]:
         out2 = torch.empty_like(q)
-        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(K)]
         for i in range(K):
             evs[i][0].record()
-            engine.attn_partials(q, 3)
+            if args.split_phases:
+                engine.attn_partials(q, 1)
+                evs[i][3].record()
+                engine.attn_partials(q, 2)
+            else:
+                engine.attn_partials(q, 3)
             evs[i][1].record()
             engine.attn_merge(out2)
             evs[i][2].record()
         torch.cuda.synchronize()
         kern["partials"] = [e[0].elapsed_time(e[1]) for e in evs]
         kern["merge"] = [e[1].elapsed_time(e[2]) for e in evs]
+        if args.split_phases:
+            kern["chunk_first"] = [e[0].elapsed_time(e[3]) for e in evs]
+            kern["seq_first"] = [e[3].elapsed_time(e[1]) for e in evs]
     clocks = sampler.stop() if rank == 0 else None
 
     # end to end through the public API with HOST buffers: pinned q -> device, forward (+ gather),
@@ -339,6 +350,9 @@ def run_b200(args):
                     "algorithmic_bytes_per_launch": ukv_local,
                     "kernel_ms": {"partials_mean": dur_ms, "partials_min": min(kern["partials"]),
                                   "merge_mean": statistics.mean(kern["merge"])}}
+            if kern["chunk_first"]:
+                roof["kernel_ms"]["chunk_first_mean"] = statistics.mean(kern["chunk_first"])
+                roof["kernel_ms"]["seq_first_mean"] = statistics.mean(kern["seq_first"])
         line = {"metric": METRIC, "value": ms * 1e3, "unit": "us", "n_gpus": world, "steps": K, "warmup": W_,
                 "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
                 "dtype": "f16", "data": "synthetic",
