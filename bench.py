@@ -37,6 +37,8 @@ def parse():
     ap.add_argument("--workload", default="auto")
     ap.add_argument("--split-phases", type=int, default=0)
     ap.add_argument("--ctas", type=int, default=0, help="persistent CTAs (0 = one per SM)")
+    ap.add_argument("--tails", default="tensor", choices=["tensor", "simt"],
+                    help="private tails on tensor cores (default) or on CUDA cores")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
 
@@ -230,6 +232,8 @@ def run_b200(args):
             engine.set_option(cabi.CA_OPT_SPLIT_PHASES, 1)
         if args.ctas:
             engine.set_option(cabi.CA_OPT_NUM_CTAS, args.ctas)
+        if args.tails == "simt":
+            engine.set_option(cabi.CA_OPT_SEQ_FIRST_TENSOR, 0)
         rows = W.populate(engine, w, device=dev, dtype=torch.float16)
         q = w.q[rows].to(dev, torch.float16).contiguous()
         ukv = W.unique_kv_bytes(w)
@@ -358,7 +362,7 @@ def run_b200(args):
                 "dtype": "f16", "data": "synthetic",
                 "config": {"workload": describe(name, world), "l2": "unique K/V per GPU (%.0f MB) exceeds the 126 MB L2: no flush between steps" % (ukv_local / 1e6)
                            if ukv_local > 126e6 else "unique K/V per GPU (%.0f MB) fits in L2" % (ukv_local / 1e6),
-                           "parallelism": "heads/%d" % world, "phases": "split" if args.split_phases else "fused",
+                           "parallelism": "heads/%d" % world, "phases": "split" if args.split_phases else "fused", "tails": args.tails,
                            "plan": stats},
                 "unique_kv_bytes": ukv_total,
                 "unique_kv_gbs_per_gpu": ukv_local / (ms * 1e-3) / 1e9,

@@ -15,7 +15,7 @@ _LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "lib
 CA_OK = 0
 CA_ERR_INVALID, CA_ERR_CUDA, CA_ERR_STATE, CA_ERR_DEVICE_STATUS = -1, -2, -3, -4
 CA_DTYPE_F16, CA_DTYPE_F32 = 0, 1
-CA_OPT_SPLIT_PHASES, CA_OPT_NUM_CTAS = 1, 2
+CA_OPT_SPLIT_PHASES, CA_OPT_NUM_CTAS, CA_OPT_SEQ_FIRST_TENSOR, CA_OPT_TRACE = 1, 2, 3, 4
 (PLAN_ITEMS, PLAN_TILE_CHUNKS, PLAN_CTA_ITEM_BEGIN, PLAN_MERGE_OFF, PLAN_MERGE_SLOTS, PLAN_PATH_OFF,
  PLAN_PATH_CHUNKS, PLAN_PATH_TOKENS, PLAN_TAIL_CHUNK, PLAN_TAIL_TOKENS, PLAN_CTA_ITEM_BEGIN_CF,
  PLAN_CTA_ITEM_BEGIN_SF) = range(12)
@@ -26,6 +26,7 @@ EXPORTED = [
     "ca_context_destroy", "ca_context_set_option", "ca_refresh_kernel_context", "ca_append_kv",
     "ca_context_delta_tokens", "ca_attention", "ca_attn_partials", "ca_attn_merge",
     "ca_scatter_prefill", "ca_copy_chunks", "ca_read_chunk", "ca_status_read", "ca_context_stats",
+    "ca_context_read_trace",
     "ca_plan_build", "ca_plan_array", "ca_plan_stats_get", "ca_plan_destroy", "ca_attention_static",
 ]
 CA_STATIC_MAX_SLOTS = 16384
@@ -75,7 +76,8 @@ def _load():
         "ca_read_chunk": (i32, [vp, i32, i32, vp, vp, vp]),
         "ca_status_read": (i32, [vp, vp, C.POINTER(C.c_int32)]),
         "ca_context_stats": (i32, [vp, C.POINTER(PlanStats)]),
-        "ca_plan_build": (i32, [C.POINTER(vp), C.POINTER(ChunkInfo), i32, i32, i32, i32, i32, i32, i64, i32]),
+        "ca_context_read_trace": (i32, [vp, C.POINTER(C.c_uint64), i32, C.POINTER(i32), vp]),
+        "ca_plan_build": (i32, [C.POINTER(vp), C.POINTER(ChunkInfo), i32, i32, i32, i32, i32, i32, i64, i32, i32]),
         "ca_plan_array": (i32, [vp, i32, C.POINTER(C.POINTER(C.c_int32)), C.POINTER(i64)]),
         "ca_plan_stats_get": (i32, [vp, C.POINTER(PlanStats)]),
         "ca_plan_destroy": (None, [vp]),
@@ -109,11 +111,11 @@ class Plan:
     """Host-only work-list builder (no GPU needed)."""
 
     def __init__(self, infos, n_seqs, n_heads, chunk_size=64, tpp_threshold=1, n_ctas=148,
-                 max_chunks=1 << 30, split_phases=False):
+                 max_chunks=1 << 30, split_phases=False, seq_first_tensor=True):
         arr, n = make_infos(infos)
         self._h = C.c_void_p()
         check(lib.ca_plan_build(C.byref(self._h), arr, n, n_seqs, n_heads, chunk_size, tpp_threshold,
-                                n_ctas, max_chunks, int(split_phases)))
+                                n_ctas, max_chunks, int(split_phases), int(seq_first_tensor)))
 
     def array(self, which):
         ptr, cnt = C.POINTER(C.c_int32)(), C.c_int64()
@@ -195,6 +197,13 @@ class Context:
         st = PlanStats()
         check(lib.ca_context_stats(self._h, C.byref(st)))
         return st.as_dict()
+
+    def read_trace(self, max_ctas=4096):
+        """[n_ctas, 4] uint64 ns: start, producer end, first / last consumer warp end."""
+        buf = (C.c_uint64 * (4 * max_ctas))()
+        n = C.c_int()
+        check(lib.ca_context_read_trace(self._h, buf, max_ctas, C.byref(n), self._stream()))
+        return np.ctypeslib.as_array(buf)[:4 * n.value].reshape(-1, 4).copy()
 
     def delta_tokens(self):
         return lib.ca_context_delta_tokens(self._h)

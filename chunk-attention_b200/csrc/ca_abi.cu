@@ -62,6 +62,10 @@ struct ca_plan {
     ca::Plan plan;
 };
 
+namespace {
+constexpr int kTraceCtas = 4096;
+}
+
 struct ca_context {
     int device = 0;
     int dtype = 0;
@@ -73,6 +77,9 @@ struct ca_context {
     int num_sms = 1;
     bool opt_split = false;
     int opt_ctas = 0;
+    bool opt_sf_tensor = true;
+    unsigned long long* trace = nullptr;  // [kTraceCtas][4], allocated when tracing is switched on
+    int trace_ctas = 0;                   // CTAs of the last traced launch
 
     ca::Plan plan;
     bool valid = false;
@@ -170,6 +177,7 @@ void ca_context_destroy(ca_context* c) {
     if (c->dev_blob) cudaFree(c->dev_blob);
     if (c->part_o) cudaFree(c->part_o);
     if (c->part_ml) cudaFree(c->part_ml);
+    if (c->trace) cudaFree(c->trace);
     if (c->status) cudaFree(c->status);
     delete c;
 }
@@ -181,6 +189,19 @@ int ca_context_set_option(ca_context* c, int option, int64_t value) {
     } else if (option == CA_OPT_NUM_CTAS) {
         if (value < 0 || value > 4096) return fail(CA_ERR_INVALID, "CTA count out of range");
         c->opt_ctas = (int)value;
+    } else if (option == CA_OPT_SEQ_FIRST_TENSOR) {
+        c->opt_sf_tensor = value != 0;
+    } else if (option == CA_OPT_TRACE) {
+        DeviceGuard guard(c->device);
+        if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+        if (value && !c->trace) {
+            CA_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->trace), (size_t)kTraceCtas * 4 * sizeof(unsigned long long)));
+            CA_CUDA(cudaMemset(c->trace, 0, (size_t)kTraceCtas * 4 * sizeof(unsigned long long)));
+        } else if (!value && c->trace) {
+            CA_CUDA(cudaFree(c->trace));
+            c->trace = nullptr;
+        }
+        return CA_OK;
     } else {
         return fail(CA_ERR_INVALID, "unknown option");
     }
@@ -197,7 +218,7 @@ int ca_refresh_kernel_context(ca_context* c, const ca_chunk_info* infos, int n_i
     const int n_ctas = c->opt_ctas > 0 ? c->opt_ctas : c->num_sms;
     std::string err = ca::build_plan(c->plan, infos, n_infos, n_seqs, c->geo.n_heads, c->geo.chunk_size,
                                      c->tpp_threshold, n_ctas, c->max_chunks, c->opt_split, c->geo.d_head,
-                                     c->geo.esize, c->fast);
+                                     c->geo.esize, c->fast, c->opt_sf_tensor);
     if (!err.empty()) return fail(CA_ERR_INVALID, "work list rejected: " + err);
     const ca::Plan& pl = c->plan;
 
@@ -338,8 +359,10 @@ int ca_attn_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_st
     p.delta_tokens = c->delta_tokens;
     p.scale_log2 = 1.4426950408889634f / std::sqrt((float)c->geo.d_head);
     p.status = c->status;
+    p.trace = c->trace;
     if (!c->plan.split_phases) {
         p.cta_item_begin = c->d_cta;
+        c->trace_ctas = (int)c->plan.cta_item_begin.size() - 1;
         CA_CUDA(ca::launch_attn_partials(p, (int)c->plan.cta_item_begin.size() - 1, stream));
     } else {
         if ((phases & 1) && c->plan.n_items_cf > 0) {
@@ -492,6 +515,19 @@ int ca_status_read(ca_context* c, ca_stream stream_, int32_t* status) {
     return CA_OK;
 }
 
+int ca_context_read_trace(ca_context* c, uint64_t* out, int max_ctas, int* n_ctas, ca_stream stream_) {
+    if (!c || !out || !n_ctas || max_ctas < 0) return fail(CA_ERR_INVALID, "null argument");
+    if (!c->trace) return fail(CA_ERR_STATE, "tracing is off: set CA_OPT_TRACE first");
+    DeviceGuard guard(c->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const int n = c->trace_ctas < max_ctas ? c->trace_ctas : max_ctas;
+    CA_CUDA(cudaStreamSynchronize(stream));
+    if (n > 0) CA_CUDA(cudaMemcpy(out, c->trace, (size_t)n * 4 * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+    *n_ctas = n;
+    return CA_OK;
+}
+
 int ca_context_stats(const ca_context* c, ca_plan_stats* out) {
     if (!c || !out) return fail(CA_ERR_INVALID, "null argument");
     if (!c->valid) return fail(CA_ERR_STATE, "work list is stale");
@@ -501,13 +537,14 @@ int ca_context_stats(const ca_context* c, ca_plan_stats* out) {
 
 // ---- host-only planner ---------------------------------------------------------------------------------
 int ca_plan_build(ca_plan** out, const ca_chunk_info* infos, int n_infos, int n_seqs, int n_heads,
-                  int chunk_size, int tpp_threshold, int n_ctas, int64_t max_chunks, int split_phases) {
+                  int chunk_size, int tpp_threshold, int n_ctas, int64_t max_chunks, int split_phases,
+                  int seq_first_tensor) {
     if (!out) return fail(CA_ERR_INVALID, "out is null");
     *out = nullptr;
     ca_plan* p = new (std::nothrow) ca_plan();
     if (!p) return fail(CA_ERR_INVALID, "out of host memory");
     std::string err = ca::build_plan(p->plan, infos, n_infos, n_seqs, n_heads, chunk_size, tpp_threshold, n_ctas,
-                                     max_chunks, split_phases != 0, ca::FAST_D, 2, true);
+                                     max_chunks, split_phases != 0, ca::FAST_D, 2, true, seq_first_tensor != 0);
     if (!err.empty()) {
         delete p;
         return fail(CA_ERR_INVALID, "work list rejected: " + err);

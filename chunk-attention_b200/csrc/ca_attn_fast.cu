@@ -116,6 +116,25 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// D(16x8, f32) += A(16x8, f16, row) * B(8x8, f16, col)
+__device__ __forceinline__ void mma_1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(b0));
+}
+__device__ __forceinline__ void sts128_zero(uint32_t addr) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(addr), "r"(0u) : "memory");
+}
+// order this thread's generic-proxy shared-memory writes before later async-proxy (TMA) writes
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -355,6 +374,182 @@ __device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView&
     return true;
 }
 
+// Combine the 8 warps' (max, sum, O[128]) of a ONE-row item and write its single partial.  Every
+// warp has stored its state in its slot of the double-buffered scratch (buffer = item parity);
+// one mbarrier phase per such item orders the stores before the loads, and because every warp
+// waits for the phase, a warp can be at most one item ahead, so two buffers suffice.
+__device__ __forceinline__ bool combine_row_and_store(const PartialParams& p, const ItemView& it, float* scratch,
+                                                      uint32_t merge_bar, uint32_t& simt_count, int warp, int lane) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(merge_bar);
+    bool ok = mbar_wait_bounded(merge_bar, simt_count & 1);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) return false;
+    if (warp < 4) {
+        const float* base = scratch + (simt_count & 1) * NUM_CONSUMER_WARPS * SCRATCH_FLOATS_PER_WARP;
+        const int d = warp * 32 + lane;
+        float mm = NEG_BIG;
+#pragma unroll
+        for (int w = 0; w < NUM_CONSUMER_WARPS; w++) mm = fmaxf(mm, base[w * SCRATCH_FLOATS_PER_WARP]);
+        float ll = 0.f, od = 0.f;
+#pragma unroll
+        for (int w = 0; w < NUM_CONSUMER_WARPS; w++) {
+            const float wl = base[w * SCRATCH_FLOATS_PER_WARP + 1];
+            // a warp that saw no token keeps l = 0 and contributes nothing whatever its weight
+            const float wgt = fast_exp2(base[w * SCRATCH_FLOATS_PER_WARP] - mm);
+            ll = fmaf(wgt, wl, ll);
+            od = fmaf(wgt, base[w * SCRATCH_FLOATS_PER_WARP + 4 + d], od);
+        }
+        p.part_o[(size_t)it.slot_base * FAST_D + d] = od;
+        if (d == 0) p.part_ml[it.slot_base] = make_float2(mm, ll);
+    }
+    simt_count++;
+    return true;
+}
+
+// Tensor-core item of up to 16 rows, 8 token splits: warp w owns tokens 8w..8w+7 of every tile (one
+// 8-wide column tile of S, one k = 8 step of P V).  This is how a sequence's private tail (ONE row)
+// is walked when the tensor-core sequence-first mode is selected: 15 of the 16 MMA rows are idle, but
+// the walk needs about a third of the instructions of the CUDA-core version, which matters because
+// with one 200 KiB CTA per SM only 8 warps are there to hide latency.  A partially filled tail tile
+// is handled by masking the scores of absent tokens and zeroing their V rows in the staged copy.
+// A one-row item combines its 8 warps through shared memory and writes one partial; wider items
+// write one partial per warp.
+__device__ __forceinline__ bool mma8_item(const PartialParams& p, const ItemView& it, Ring& rg, float* scratch,
+                                          uint32_t merge_bar, uint32_t& simt_count, int warp, int lane) {
+    const int tok0 = warp * 8;
+    const int quad = lane & 3;
+    const int r_lo = lane >> 2;
+    const int r_hi = r_lo + 8;
+    const bool v_lo = r_lo < it.n_rows;
+    const bool v_hi = r_hi < it.n_rows;
+
+    uint32_t qa[8][4];
+    {
+        const __half* q = reinterpret_cast<const __half*>(p.q);
+        const size_t row_stride = (size_t)p.n_heads * FAST_D;
+        const __half* q_lo = q + (size_t)(it.row_begin + r_lo) * row_stride + (size_t)it.head * FAST_D;
+        const __half* q_hi = q + (size_t)(it.row_begin + r_hi) * row_stride + (size_t)it.head * FAST_D;
+#pragma unroll
+        for (int ks = 0; ks < 8; ks++) {
+            const int col = ks * 16 + 2 * quad;
+            qa[ks][0] = v_lo ? __ldg(reinterpret_cast<const uint32_t*>(q_lo + col)) : 0u;
+            qa[ks][1] = v_hi ? __ldg(reinterpret_cast<const uint32_t*>(q_hi + col)) : 0u;
+            qa[ks][2] = v_lo ? __ldg(reinterpret_cast<const uint32_t*>(q_lo + col + 8)) : 0u;
+            qa[ks][3] = v_hi ? __ldg(reinterpret_cast<const uint32_t*>(q_hi + col + 8)) : 0u;
+        }
+    }
+    float o[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; n++) {
+        o[n][0] = 0.f; o[n][1] = 0.f; o[n][2] = 0.f; o[n][3] = 0.f;
+    }
+    float m_lo = NEG_BIG, m_hi = NEG_BIG, l_lo = 0.f, l_hi = 0.f;
+
+    // ldmatrix x4: the four 8x8 matrices are four consecutive granules of this warp's 8 token rows
+    const int row_t = tok0 + (lane & 7);
+    const uint32_t row_off = row_t * (FAST_D * 2);
+    const int sw = row_t & 7;
+    const int gsel = lane >> 3;
+    const int t0 = tok0 + 2 * quad;  // token of accumulator columns c0/c2; c1/c3 are the next token
+
+    for (int j = 0; j < it.n_tiles; j++) {
+        const int nt = tile_tokens(it, j, p.delta_tokens);
+        if (nt == 0) continue;
+        if (!consumer_wait_full(rg)) return false;
+        if (tok0 < nt) {
+            const uint32_t kbase = rg.ring + rg.stage * FAST_STAGE_BYTES;
+            const uint32_t vbase = kbase + FAST_TILE_BYTES;
+            const bool partial = tok0 + 8 > nt;
+            if (partial) {
+                // absent tokens: the bulk copy did not fill their rows, so they hold stale bytes;
+                // zero the V rows (their P is forced to 0 below, and 0 * NaN would still be NaN)
+                for (int idx = lane; idx < (tok0 + 8 - nt) * 16; idx += 32)
+                    sts128_zero(vbase + (nt + (idx >> 4)) * (FAST_D * 2) + ((idx & 15) << 4));
+                __syncwarp();
+            }
+            float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int k2 = 0; k2 < 4; k2++) {
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(b0, b1, b2, b3, kbase + row_off + (((4 * k2 + gsel) ^ sw) << 4));
+                mma_16816(sa, qa[2 * k2], b0, b1);
+                mma_16816(sb, qa[2 * k2 + 1], b2, b3);
+            }
+            float s0 = sa[0] + sb[0], s1 = sa[1] + sb[1], s2 = sa[2] + sb[2], s3 = sa[3] + sb[3];
+            const bool in0 = t0 < nt, in1 = t0 + 1 < nt;
+            if (!in0) { s0 = NEG_BIG; s2 = NEG_BIG; }
+            if (!in1) { s1 = NEG_BIG; s3 = NEG_BIG; }
+            float mx_lo = fmaxf(s0, s1), mx_hi = fmaxf(s2, s3);
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+            const float mn_lo = fmaxf(m_lo, mx_lo * p.scale_log2);
+            const float mn_hi = fmaxf(m_hi, mx_hi * p.scale_log2);
+            const float a_lo = fast_exp2(m_lo - mn_lo);
+            const float a_hi = fast_exp2(m_hi - mn_hi);
+            m_lo = mn_lo;
+            m_hi = mn_hi;
+            const float p0 = in0 ? fast_exp2(fmaf(s0, p.scale_log2, -mn_lo)) : 0.f;
+            const float p1 = in1 ? fast_exp2(fmaf(s1, p.scale_log2, -mn_lo)) : 0.f;
+            const float p2 = in0 ? fast_exp2(fmaf(s2, p.scale_log2, -mn_hi)) : 0.f;
+            const float p3 = in1 ? fast_exp2(fmaf(s3, p.scale_log2, -mn_hi)) : 0.f;
+            l_lo = l_lo * a_lo + (p0 + p1);
+            l_hi = l_hi * a_hi + (p2 + p3);
+#pragma unroll
+            for (int n = 0; n < 16; n++) {
+                o[n][0] *= a_lo; o[n][1] *= a_lo; o[n][2] *= a_hi; o[n][3] *= a_hi;
+            }
+            const uint32_t pa0 = pack_half2(p0, p1), pa1 = pack_half2(p2, p3);
+#pragma unroll
+            for (int dq = 0; dq < 4; dq++) {
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4_trans(b0, b1, b2, b3, vbase + row_off + (((4 * dq + gsel) ^ sw) << 4));
+                mma_1688(o[4 * dq + 0], pa0, pa1, b0);
+                mma_1688(o[4 * dq + 1], pa0, pa1, b1);
+                mma_1688(o[4 * dq + 2], pa0, pa1, b2);
+                mma_1688(o[4 * dq + 3], pa0, pa1, b3);
+            }
+            if (partial) fence_proxy_async();
+        }
+        consumer_release(rg, lane);
+    }
+
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    if (it.n_rows == 1) {
+        // row 0 lives in the first quad: lane q holds outputs 8n + 2q, 8n + 2q + 1
+        float* mine = scratch + ((simt_count & 1) * NUM_CONSUMER_WARPS + warp) * SCRATCH_FLOATS_PER_WARP;
+        if (lane == 0) {
+            mine[0] = m_lo;
+            mine[1] = l_lo;
+        }
+        if (lane < 4) {
+#pragma unroll
+            for (int n = 0; n < 16; n++)
+                *reinterpret_cast<float2*>(mine + 4 + 8 * n + 2 * quad) = make_float2(o[n][0], o[n][1]);
+        }
+        return combine_row_and_store(p, it, scratch, merge_bar, simt_count, warp, lane);
+    }
+    const int slot0 = it.slot_base + warp * it.n_rows;
+    if (v_lo) {
+        float* dst = p.part_o + (size_t)(slot0 + r_lo) * FAST_D + 2 * quad;
+#pragma unroll
+        for (int n = 0; n < 16; n++) *reinterpret_cast<float2*>(dst + 8 * n) = make_float2(o[n][0], o[n][1]);
+        if (quad == 0) p.part_ml[slot0 + r_lo] = make_float2(m_lo, l_lo);
+    }
+    if (v_hi) {
+        float* dst = p.part_o + (size_t)(slot0 + r_hi) * FAST_D + 2 * quad;
+#pragma unroll
+        for (int n = 0; n < 16; n++) *reinterpret_cast<float2*>(dst + 8 * n) = make_float2(o[n][2], o[n][3]);
+        if (quad == 0) p.part_ml[slot0 + r_hi] = make_float2(m_hi, l_hi);
+    }
+    return true;
+}
+
 // Sequence-first item on CUDA cores.  Warp w owns tokens 8w..8w+7 of every tile; a half-warp reads
 // one 256-byte token row per 128-bit load (lane = granule), so K rows are dotted against q held in
 // registers and V rows are accumulated into 8 output elements per lane.  The 8 warps' states are
@@ -449,7 +644,7 @@ __device__ __forceinline__ bool simt_item(const PartialParams& p, const ItemView
 #pragma unroll
     for (int i = 0; i < 8; i++) o[i] += __shfl_xor_sync(0xffffffffu, o[i], 16);
 
-    // combine the 8 warps: double-buffered scratch, one mbarrier phase per sequence-first item
+    // lanes 0..15 of a warp hold the warp's 128 outputs, 8 each
     float* mine = scratch + ((simt_count & 1) * NUM_CONSUMER_WARPS + warp) * SCRATCH_FLOATS_PER_WARP;
     if (lane == 0) {
         mine[0] = m;
@@ -459,31 +654,7 @@ __device__ __forceinline__ bool simt_item(const PartialParams& p, const ItemView
         *reinterpret_cast<float4*>(mine + 4 + 8 * g) = make_float4(o[0], o[1], o[2], o[3]);
         *reinterpret_cast<float4*>(mine + 8 + 8 * g) = make_float4(o[4], o[5], o[6], o[7]);
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(merge_bar);
-    bool ok = mbar_wait_bounded(merge_bar, simt_count & 1);
-    ok = __all_sync(0xffffffffu, ok);
-    if (!ok) return false;
-    if (warp < 4) {
-        const float* base = scratch + (simt_count & 1) * NUM_CONSUMER_WARPS * SCRATCH_FLOATS_PER_WARP;
-        const int d = warp * 32 + lane;
-        float mm = NEG_BIG;
-#pragma unroll
-        for (int w = 0; w < NUM_CONSUMER_WARPS; w++) mm = fmaxf(mm, base[w * SCRATCH_FLOATS_PER_WARP]);
-        float ll = 0.f, od = 0.f;
-#pragma unroll
-        for (int w = 0; w < NUM_CONSUMER_WARPS; w++) {
-            const float wl = base[w * SCRATCH_FLOATS_PER_WARP + 1];
-            // a warp that saw no token keeps l = 0 and contributes nothing whatever its weight
-            const float wgt = fast_exp2(base[w * SCRATCH_FLOATS_PER_WARP] - mm);
-            ll = fmaf(wgt, wl, ll);
-            od = fmaf(wgt, base[w * SCRATCH_FLOATS_PER_WARP + 4 + d], od);
-        }
-        p.part_o[(size_t)it.slot_base * FAST_D + d] = od;
-        if (d == 0) p.part_ml[it.slot_base] = make_float2(mm, ll);
-    }
-    simt_count++;
-    return true;
+    return combine_row_and_store(p, it, scratch, merge_bar, simt_count, warp, lane);
 }
 
 __global__ void __launch_bounds__(NUM_THREADS, 1) attn_partial_kernel(const PartialParams p) {
@@ -518,8 +689,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_partial_kernel(const Part
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
+    if (p.trace && threadIdx.x == 0) p.trace[4 * blockIdx.x + 0] = global_timer_ns();
     if (warp == NUM_CONSUMER_WARPS) {
         producer_loop(p, rg, item_begin, item_end, lane);
+        if (p.trace && lane == 0) p.trace[4 * blockIdx.x + 1] = global_timer_ns();
         return;
     }
 
@@ -530,6 +703,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_partial_kernel(const Part
         bool ok;
         if (splits == 0) {
             ok = simt_item(p, it, rg, scratch, merge_bar, simt_count, warp, lane);
+        } else if (splits == 8) {
+            ok = mma8_item(p, it, rg, scratch, merge_bar, simt_count, warp, lane);
         } else if (splits == 4) {
             ok = mma_item<4>(p, it, rg, warp, lane);
         } else if (splits == 2) {
@@ -542,6 +717,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_partial_kernel(const Part
             break;
         }
     }
+    if (p.trace && lane == 0 && (warp == 0 || warp == NUM_CONSUMER_WARPS - 1))
+        p.trace[4 * blockIdx.x + (warp == 0 ? 2 : 3)] = global_timer_ns();
 }
 
 // One warp per (row, head): out = sum_i 2^(m_i - M) O_i / sum_i 2^(m_i - M) l_i.

@@ -35,6 +35,8 @@ struct PartialParams {
     int delta_tokens;            // tokens appended to every tail since the plan was built
     float scale_log2;            // log2(e) / sqrt(d_head)
     int* status;
+    unsigned long long* trace = nullptr;  // optional [n_ctas][4] ns timestamps: start, producer end, first and
+                                 // last consumer warp end; null = off
 };
 
 // Persistent kernel: chunk-first items on tensor cores and sequence-first items on CUDA cores,

@@ -18,8 +18,11 @@ struct Unit {
 // paid for by its HBM bytes alone (weight 1); wider row blocks issue proportionally more MMAs
 // per byte and become tensor-pipe bound.
 double chunk_first_tile_weight(int splits) {
-    return splits == 4 ? 1.0 : (splits == 2 ? 1.4 : 2.8);
+    return splits >= 4 ? 1.0 : (splits == 2 ? 1.4 : 2.8);
 }
+// partial rows an item emits: a one-row item combines its warps on chip and writes one row, a
+// wider item writes one row per (token split, query row)
+int item_slots(int n_rows, int splits) { return n_rows == 1 ? 1 : n_rows * std::max(1, splits); }
 constexpr double kTailTileWeight = 0.5;  // a tail holds between 0 and chunk_size - 1 tokens
 
 std::string fmt(const char* f, long a = 0, long b = 0, long c = 0) {
@@ -59,7 +62,7 @@ void cut_units(Plan& plan, const std::vector<Unit>& units, size_t ubegin, size_t
             const bool has_last = (j_end == un.n_tiles);
             it.flags = ((un.tail && has_last) ? ITEM_FLAG_TAIL : 0) | (un.splits << ITEM_SPLITS_SHIFT);
             it.last_tokens = has_last ? un.last_tokens : plan.chunk_size;
-            n_slots += un.n_rows * std::max(1, (int)un.splits);
+            n_slots += item_slots(un.n_rows, un.splits);
             plan.items.push_back(it);
             item_cta.push_back(cur);
         };
@@ -89,7 +92,7 @@ void cut_units(Plan& plan, const std::vector<Unit>& units, size_t ubegin, size_t
 
 std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int n_seqs, int n_heads,
                        int chunk_size, int tpp_threshold, int n_ctas, int64_t max_chunks,
-                       bool split_phases, int d_head, int esize, bool fast_path) {
+                       bool split_phases, int d_head, int esize, bool fast_path, bool seq_first_tensor) {
     plan = Plan();
     if (n_infos < 0 || n_seqs < 0 || n_heads <= 0 || chunk_size <= 0 || n_ctas <= 0)
         return "negative or zero size";
@@ -195,7 +198,7 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
             const int rb = r.b + blk * rows_per_block;
             const int rows = std::min(rows_per_block, r.e - rb);
             if (rows <= 0) continue;
-            const int splits = rows <= 32 ? 4 : (rows <= 64 ? 2 : 1);
+            const int splits = rows <= 16 ? 8 : (rows <= 32 ? 4 : (rows <= 64 ? 2 : 1));
             for (int h = 0; h < n_heads; h++)
                 units.push_back(Unit{r.tile_begin, (int32_t)r.chunks.size(), h, rb, rows, splits,
                                      chunk_size, false, chunk_first_tile_weight(splits)});
@@ -212,7 +215,7 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
             if (!shared[path_info[p]] && plan.path_tokens[p] != chunk_size)
                 return fmt("row %ld has a partially filled chunk that is not its tail", s);
         for (int h = 0; h < n_heads; h++)
-            units.push_back(Unit{tb, nt, h, s, 1, 0, plan.tail_tokens[s], true, 1.0});
+            units.push_back(Unit{tb, nt, h, s, 1, seq_first_tensor ? 8 : 0, plan.tail_tokens[s], true, 1.0});
     }
 
     // ---- cut into items, schedules ----------------------------------------------------------------------
@@ -232,7 +235,7 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
 
     // ---- merge lists -------------------------------------------------------------------------------------
     for (const PlanItem& it : plan.items) {
-        const int splits = std::max(1, it.flags >> ITEM_SPLITS_SHIFT);
+        const int splits = it.n_rows == 1 ? 1 : std::max(1, it.flags >> ITEM_SPLITS_SHIFT);
         for (int r = 0; r < it.n_rows; r++)
             plan.merge_off[(size_t)(it.row_begin + r) * n_heads + it.head + 1] += splits;
     }
@@ -241,7 +244,7 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
     {
         std::vector<int32_t> cursor(plan.merge_off.begin(), plan.merge_off.end() - 1);
         for (const PlanItem& it : plan.items) {
-            const int splits = std::max(1, it.flags >> ITEM_SPLITS_SHIFT);
+            const int splits = it.n_rows == 1 ? 1 : std::max(1, it.flags >> ITEM_SPLITS_SHIFT);
             for (int sp = 0; sp < splits; sp++)
                 for (int r = 0; r < it.n_rows; r++)
                     plan.merge_slots[cursor[(size_t)(it.row_begin + r) * n_heads + it.head]++] =

@@ -27,7 +27,8 @@
 namespace ca {
 
 constexpr int ITEM_FLAG_TAIL = 1;     // last tile of the item is the sequence's tail chunk
-constexpr int ITEM_SPLITS_SHIFT = 8;  // flags >> 8: token splits (4, 2, 1) of a chunk-first item
+constexpr int ITEM_SPLITS_SHIFT = 8;  // flags >> 8: token splits of a tensor-core item (8, 4, 2, 1);
+                                      // 0 = one-row item walked on CUDA cores
 constexpr int MAX_ROWS_PER_ITEM = 128;
 
 struct PlanItem {
@@ -60,6 +61,6 @@ struct Plan {
 // Returns an empty string on success, else the reason the input was rejected.
 std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int n_seqs, int n_heads,
                        int chunk_size, int tpp_threshold, int n_ctas, int64_t max_chunks,
-                       bool split_phases, int d_head, int esize, bool fast_path);
+                       bool split_phases, int d_head, int esize, bool fast_path, bool seq_first_tensor);
 
 }  // namespace ca

@@ -89,6 +89,11 @@ CA_API void ca_context_destroy(ca_context* ctx);
 #define CA_OPT_SPLIT_PHASES 1
 /* number of persistent CTAs; 0 = one per SM */
 #define CA_OPT_NUM_CTAS 2
+/* how a sequence's private tail (one query row) is walked: 1 (default) on tensor cores, 8 tokens
+ * per warp; 0 on CUDA cores with 128-bit shared-memory loads and warp-shuffle reductions */
+#define CA_OPT_SEQ_FIRST_TENSOR 3
+/* 1: the attention kernel records per-CTA nanosecond timestamps, read with ca_context_read_trace */
+#define CA_OPT_TRACE 4
 CA_API int ca_context_set_option(ca_context* ctx, int option, int64_t value);
 
 /* Rebuild and upload the work lists after the tree changed.
@@ -144,6 +149,12 @@ CA_API int ca_read_chunk(ca_context* ctx, int chunk_id, int n_tokens, void* k_ou
 /* Device status word written by kernels whose bounded waits ran out (0 = clean).  Synchronises
  * the stream. */
 CA_API int ca_status_read(ca_context* ctx, ca_stream stream, int32_t* status);
+
+/* Per-CTA timestamps of the last attention launch when CA_OPT_TRACE is on (diagnostics): for CTA i,
+ * out[4i..4i+3] = start, producer warp end, first consumer warp end, last consumer warp end, in ns
+ * of the GPU's global timer.  `out` is a HOST array of 4 * max_ctas; returns the CTA count through
+ * n_ctas.  Synchronises the stream. */
+CA_API int ca_context_read_trace(ca_context* ctx, uint64_t* out, int max_ctas, int* n_ctas, ca_stream stream);
 
 /* Per-step counters of the current work list (the roofline metric is computed from them). */
 typedef struct ca_plan_stats {
@@ -202,7 +213,7 @@ CA_API int ca_attention_static(const void* pool, int n_heads, const void* q, voi
  * a machine without a GPU.  Arrays are owned by the plan. */
 #define CA_PLAN_ITEMS 0          /* int32[n_items][8]: tile_begin, n_tiles, head, row_begin,
                                     n_rows, slot_base, flags(bit0 last tile is a tail; bits 8..:
-                                    token splits), last_tokens                                   */
+                                    token splits, 0 = CUDA-core walk), last_tokens               */
 #define CA_PLAN_TILE_CHUNKS 1    /* int32[]: pool slots, indexed by tile_begin + j               */
 #define CA_PLAN_CTA_ITEM_BEGIN 2 /* int32[n_ctas + 1]                                            */
 #define CA_PLAN_MERGE_OFF 3      /* int32[n_seqs * n_heads + 1]                                  */
@@ -216,7 +227,7 @@ CA_API int ca_attention_static(const void* pool, int n_heads, const void* q, voi
 #define CA_PLAN_CTA_ITEM_BEGIN_SF 11 /* split-phase schedules: sequence-first items              */
 CA_API int ca_plan_build(ca_plan** out, const ca_chunk_info* infos, int n_infos, int n_seqs,
                          int n_heads, int chunk_size, int tpp_threshold, int n_ctas,
-                         int64_t max_chunks, int split_phases);
+                         int64_t max_chunks, int split_phases, int seq_first_tensor);
 CA_API int ca_plan_array(const ca_plan* plan, int which, const int32_t** data, int64_t* count);
 CA_API int ca_plan_stats_get(const ca_plan* plan, ca_plan_stats* out);
 CA_API void ca_plan_destroy(ca_plan* plan);

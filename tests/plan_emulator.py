@@ -48,9 +48,9 @@ def emulate(plan, kv_of_chunk, q, chunk_size, delta=0, schedule="fused"):
             K, V = kv_of_chunk[int(tiles[tile_begin + j])]
             ks.append((K[head], nt))
             vs.append(V[head])
-        if splits == 0:
-            assert n_rows == 1
-            groups = [(slot_base, [(0, chunk_size)])]  # one slot, all tokens
+        if n_rows == 1:
+            assert splits in (0, 8)
+            groups = [(slot_base, [(0, chunk_size)])]  # warps combined on chip: one slot, all tokens
         else:
             tw = chunk_size // splits
             groups = [(slot_base + sp * n_rows, [(sp * tw, (sp + 1) * tw)]) for sp in range(splits)]

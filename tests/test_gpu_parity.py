@@ -161,10 +161,13 @@ def test_sharer_counts(n_seqs):
     check_against_oracle(w, eng, TOL_F16)
 
 
-@pytest.mark.parametrize("unique", [0, 1, 17, 63, 64, 65])
-def test_partial_and_empty_tails(unique):
+@pytest.mark.parametrize("tensor_tails", [1, 0])
+@pytest.mark.parametrize("unique", [0, 1, 7, 8, 9, 17, 63, 64, 65])
+def test_partial_and_empty_tails(unique, tensor_tails):
+    # both ways of walking a private tail: tensor cores (default) and CUDA cores
     w = W.single_level("u%d" % unique, 3, 128, 64, torch.float16, 5, 2 * 64, unique, 40 + unique, 0.5)
     eng = fast_engine(H=3)
+    eng.ctx.set_option(cabi.CA_OPT_SEQ_FIRST_TENSOR, tensor_tails)
     check_against_oracle(w, eng, TOL_F16)
 
 
@@ -181,10 +184,11 @@ def test_peaky_scores_and_many_pieces():
     w = W.single_level("peaky", 4, 128, 64, torch.float16, 9, 6 * 64, 3 * 64 + 5, 60, 0.5)
     w.q = w.q * 8
     for n_ctas in (1, 5, 148):
-        for split in (0, 1):
+        for split, tensor_tails in ((0, 1), (1, 1), (0, 0), (1, 0)):
             eng = fast_engine(H=4)
             eng.ctx.set_option(cabi.CA_OPT_NUM_CTAS, n_ctas)
             eng.ctx.set_option(cabi.CA_OPT_SPLIT_PHASES, split)
+            eng.ctx.set_option(cabi.CA_OPT_SEQ_FIRST_TENSOR, tensor_tails)
             check_against_oracle(w, eng, TOL_F16, partitions=(0,))
 
 
@@ -195,13 +199,15 @@ def test_tpp_threshold_semantics():
     assert eng.ctx.stats()["n_shared_chunks"] == 0
 
 
-def test_decode_trace_with_churn():
+@pytest.mark.parametrize("tensor_tails", [1, 0])
+def test_decode_trace_with_churn(tensor_tails):
     # scaled-down two-level tree with incremental decode: append every step, churn every 4 steps,
     # the oracle mirrors every operation; tails cross chunk boundaries during the trace
     cfg = W.Config4(n_heads=2, n_groups=3, per_group=4, root_len=128, group_len=64, unique_len=60, steps=14,
                     churn_every=4, churn=2)
     from chunk_attn_oracle import Attention as OracleAttention
     eng = fast_engine(H=2, max_chunks=256)
+    eng.ctx.set_option(cabi.CA_OPT_SEQ_FIRST_TENSOR, tensor_tails)
     ora = OracleAttention(2, 128, 64)
     seqs = []
 

@@ -56,9 +56,11 @@ def shared_spec(n_seqs, shared, unique, base=0):
 
 @pytest.mark.parametrize("n_ctas", [1, 3, 16, 148])
 @pytest.mark.parametrize("split", [False, True])
-def test_single_level_prefix(n_ctas, split):
+@pytest.mark.parametrize("tensor_tails", [True, False])
+def test_single_level_prefix(n_ctas, split, tensor_tails):
     ora = build_tree(shared_spec(6, 5 * C, 2 * C + 17))
-    plan, loads = check(ora, 2, 8, n_ctas=n_ctas, split_phases=split)
+    plan, loads = check(ora, 2, 8, n_ctas=n_ctas, split_phases=split, seq_first_tensor=tensor_tails)
+    assert sorted(set(int(f) >> 8 for f in plan.items()[:, 6])) == ([8] if tensor_tails else [0, 8])
     st = plan.stats()
     assert st["n_shared_chunks"] == 5 and st["n_runs"] == 1
     assert st["n_chunks"] == 5 + 6 * 3
@@ -82,7 +84,7 @@ def test_two_level_tree_and_row_blocks():
     plan, _ = check(ora, 1, 4, n_ctas=20)
     items = plan.items()
     splits = sorted(set(int(f) >> 8 for f in items[:, 6]))
-    assert splits == [0, 1, 2, 4]
+    assert splits == [1, 2, 8]  # 70 rows -> 1 split, 33 -> 2, 2 rows and every private tail -> 8
     assert plan.stats()["n_runs"] == 4
 
 
@@ -125,9 +127,9 @@ def test_delta_tokens_are_applied_to_tails_only():
 
 @pytest.mark.parametrize("seed", range(8))
 def test_random_traces(seed):
-    ops = random_trace(seed, n_ops=40, chunk_size=4, vocab=2, max_len=30, max_live=12)
+    ops = random_trace(seed, n_ops=40, chunk_size=8, vocab=2, max_len=50, max_live=12)
     rng = np.random.default_rng(seed)
-    ora = OracleAttention(2, 4, 4)
+    ora = OracleAttention(2, 4, 8)
     pos_kv = {}
     for op, arg in ops:
         if op == "add":
@@ -145,7 +147,7 @@ def test_random_traces(seed):
             ora.append_token(arg, k, v)
         if not ora.tails:
             continue
-        # the planner is geometry-agnostic: exercise it with chunk_size 4 (splits of 1 token)
+        # the planner is geometry-agnostic: exercise it with chunk_size 8 (8 splits of 1 token)
         check(ora, 2, 4, n_ctas=1 + seed, split_phases=bool(seed & 1))
 
 
