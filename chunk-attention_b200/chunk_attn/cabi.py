@@ -199,11 +199,12 @@ class Context:
         return st.as_dict()
 
     def read_trace(self, max_ctas=4096):
-        """[n_ctas, 4] uint64 ns: start, producer end, first / last consumer warp end."""
-        buf = (C.c_uint64 * (4 * max_ctas))()
+        """[n_ctas, 8] uint64: ns of start, producer end, first / last consumer warp end; cycles of
+        consumer warp 0 waiting for tiles, combining, producer waiting for free stages, warp 0 total."""
+        buf = (C.c_uint64 * (16 * max_ctas))()
         n = C.c_int()
         check(lib.ca_context_read_trace(self._h, buf, max_ctas, C.byref(n), self._stream()))
-        return np.ctypeslib.as_array(buf)[:4 * n.value].reshape(-1, 4).copy()
+        return np.ctypeslib.as_array(buf)[:16 * n.value].reshape(-1, 16).copy()
 
     def delta_tokens(self):
         return lib.ca_context_delta_tokens(self._h)

@@ -195,8 +195,8 @@ int ca_context_set_option(ca_context* c, int option, int64_t value) {
         DeviceGuard guard(c->device);
         if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
         if (value && !c->trace) {
-            CA_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->trace), (size_t)kTraceCtas * 4 * sizeof(unsigned long long)));
-            CA_CUDA(cudaMemset(c->trace, 0, (size_t)kTraceCtas * 4 * sizeof(unsigned long long)));
+            CA_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->trace), (size_t)kTraceCtas * 16 * sizeof(unsigned long long)));
+            CA_CUDA(cudaMemset(c->trace, 0, (size_t)kTraceCtas * 16 * sizeof(unsigned long long)));
         } else if (!value && c->trace) {
             CA_CUDA(cudaFree(c->trace));
             c->trace = nullptr;
@@ -523,7 +523,7 @@ int ca_context_read_trace(ca_context* c, uint64_t* out, int max_ctas, int* n_cta
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     const int n = c->trace_ctas < max_ctas ? c->trace_ctas : max_ctas;
     CA_CUDA(cudaStreamSynchronize(stream));
-    if (n > 0) CA_CUDA(cudaMemcpy(out, c->trace, (size_t)n * 4 * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+    if (n > 0) CA_CUDA(cudaMemcpy(out, c->trace, (size_t)n * 16 * sizeof(uint64_t), cudaMemcpyDeviceToHost));
     *n_ctas = n;
     return CA_OK;
 }

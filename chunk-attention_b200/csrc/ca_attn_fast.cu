@@ -32,11 +32,27 @@ namespace {
 
 constexpr int NUM_STAGES = 6;
 constexpr int NUM_CONSUMER_WARPS = 8;
-constexpr int NUM_THREADS = (NUM_CONSUMER_WARPS + 1) * 32;
+// 8 consumer warps (two warpgroups) + one producer warpgroup of which a single warp works.  The
+// register file is re-split at run time: the producer group shrinks to 40 registers per thread and
+// the consumers grow to 232 (128 * 40 + 256 * 232 = 64512 <= 65536).
+constexpr int NUM_THREADS = (NUM_CONSUMER_WARPS + 4) * 32;
+constexpr int PRODUCER_REGS = 40;
+constexpr int CONSUMER_REGS = 232;
 constexpr int SCRATCH_FLOATS_PER_WARP = 132;  // m, l, 2 pad, o[128]
 constexpr int SCRATCH_BYTES = 2 * NUM_CONSUMER_WARPS * SCRATCH_FLOATS_PER_WARP * 4;
 constexpr int NUM_BARRIERS = 2 * NUM_STAGES + 1;
-constexpr int SMEM_BYTES = NUM_STAGES * FAST_STAGE_BYTES + SCRATCH_BYTES + NUM_BARRIERS * 8 + 16;
+// query rows of items of up to 16 rows travel with the item's first tile: one slot per ring stage
+// Rows are pitched 16 bytes past their 256 so that the 8 rows an ldmatrix reads fall in 8 different
+// bank groups.
+constexpr int QSLOT_ROWS = 16;
+constexpr int QSLOT_PITCH = FAST_D * 2 + 16;
+constexpr int QSLOT_BYTES = QSLOT_ROWS * QSLOT_PITCH;
+constexpr int SMEM_RING_BYTES = NUM_STAGES * FAST_STAGE_BYTES;
+constexpr int SMEM_Q_OFFSET = SMEM_RING_BYTES;
+constexpr int SMEM_SCRATCH_OFFSET = SMEM_Q_OFFSET + NUM_STAGES * QSLOT_BYTES;
+constexpr int SMEM_BAR_OFFSET = SMEM_SCRATCH_OFFSET + SCRATCH_BYTES;
+constexpr int SMEM_BYTES = SMEM_BAR_OFFSET + NUM_BARRIERS * 8 + 16;
+static_assert(SMEM_BYTES <= 232448, "more than the 227 KiB a CTA can have");
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // about two seconds
 constexpr float NEG_BIG = -1.0e30f;
 
@@ -116,13 +132,6 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// D(16x8, f32) += A(16x8, f16, row) * B(8x8, f16, col)
-__device__ __forceinline__ void mma_1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(a1), "r"(b0));
-}
 __device__ __forceinline__ void sts128_zero(uint32_t addr) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(addr), "r"(0u) : "memory");
 }
@@ -153,10 +162,16 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
 // ---- pipeline bookkeeping shared by producer and consumers ----------------------------------------
 struct Ring {
     uint32_t ring;        // shared address of stage 0
+    uint32_t qslots;      // shared address of query slot 0 (slot s belongs to stage s)
     uint32_t full_bar;    // NUM_STAGES barriers, producer -> consumers (count 1 + tx bytes)
     uint32_t empty_bar;   // NUM_STAGES barriers, consumers -> producer (count NUM_CONSUMER_WARPS)
     uint32_t stage;
     uint32_t phase;
+    bool timed;               // tracing on: accumulate stall cycles
+    long long wait_cycles;    // cycles spent waiting on ring barriers
+    long long tail_cycles;    // consumers: cycles spent combining warps and storing partials
+    long long seg[6];         // consumers, 8-split items: prologue, scores+softmax, P V+release, epilogue,
+                              // query fragments, time between items
     __device__ __forceinline__ void advance() {
         if (++stage == NUM_STAGES) {
             stage = 0;
@@ -168,11 +183,15 @@ struct Ring {
 __device__ __forceinline__ void report(int* status, int code) { atomicCAS(status, STATUS_OK, code); }
 
 // ---- producer: one warp, lane 0 issues --------------------------------------------------------------
-__device__ __forceinline__ void producer_loop(const PartialParams& p, Ring rg, int item_begin, int item_end, int lane) {
+__device__ __forceinline__ void producer_loop(const PartialParams& p, Ring& rg, int item_begin, int item_end, int lane) {
     uint32_t issued = 0;
     bool ok = true;
+    ItemView next = item_begin < item_end ? load_item(p.items, item_begin) : ItemView{};
     for (int i = item_begin; i < item_end && ok; i++) {
-        const ItemView it = load_item(p.items, i);
+        const ItemView it = next;
+        if (i + 1 < item_end) next = load_item(p.items, i + 1);  // in flight while this item streams
+        // items of up to 16 rows get their query rows staged next to their first tile
+        bool q_pending = (it.flags >> ITEM_SPLITS_SHIFT) == 8;
         for (int j0 = 0; j0 < it.n_tiles && ok; j0 += 32) {
             // each lane fetches the pool slot of one upcoming tile, lane 0 reads them by shuffle
             const int jl = j0 + lane;
@@ -183,18 +202,30 @@ __device__ __forceinline__ void producer_loop(const PartialParams& p, Ring rg, i
                 const int nt = tile_tokens(it, j0 + jj, p.delta_tokens);
                 if (nt == 0) continue;
                 if (lane == 0) {
+                    const long long t0 = rg.timed ? clock64() : 0;
                     ok = mbar_wait_bounded(rg.empty_bar + 8 * rg.stage, rg.phase ^ 1);
+                    if (rg.timed) rg.wait_cycles += clock64() - t0;
                     if (ok) {
                         const uint8_t* src =
                             p.pool + ((size_t)chunk * p.n_heads + it.head) * (size_t)FAST_STAGE_BYTES;
                         const uint32_t bytes = (uint32_t)nt * (FAST_D * 2);
                         const uint32_t bar = rg.full_bar + 8 * rg.stage;
                         const uint32_t dst = rg.ring + rg.stage * FAST_STAGE_BYTES;
-                        mbar_arrive_expect_tx(bar, 2 * bytes);
+                        const uint32_t q_bytes = q_pending ? (uint32_t)it.n_rows * (FAST_D * 2) : 0u;
+                        mbar_arrive_expect_tx(bar, 2 * bytes + q_bytes);
                         bulk_copy_g2s(dst, src, bytes, bar);
                         bulk_copy_g2s(dst + FAST_TILE_BYTES, src + FAST_TILE_BYTES, bytes, bar);
+                        if (q_pending) {
+                            const uint8_t* q = reinterpret_cast<const uint8_t*>(p.q) +
+                                               ((size_t)it.row_begin * p.n_heads + it.head) * (FAST_D * 2);
+                            const uint32_t qdst = rg.qslots + rg.stage * QSLOT_BYTES;
+                            for (int r = 0; r < it.n_rows; r++)
+                                bulk_copy_g2s(qdst + r * QSLOT_PITCH, q + (size_t)r * p.n_heads * (FAST_D * 2),
+                                              FAST_D * 2, bar);
+                        }
                     }
                 }
+                q_pending = false;
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (!ok) break;
                 issued++;
@@ -217,8 +248,10 @@ __device__ __forceinline__ void producer_loop(const PartialParams& p, Ring rg, i
 }
 
 // ---- consumers ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ bool consumer_wait_full(const Ring& rg) {
+__device__ __forceinline__ bool consumer_wait_full(Ring& rg) {
+    const long long t0 = rg.timed ? clock64() : 0;
     const bool ok = mbar_wait_bounded(rg.full_bar + 8 * rg.stage, rg.phase);
+    if (rg.timed) rg.wait_cycles += clock64() - t0;
     return __all_sync(0xffffffffu, ok);
 }
 __device__ __forceinline__ void consumer_release(Ring& rg, int lane) {
@@ -280,12 +313,17 @@ __device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView&
         const uint32_t kbase = rg.ring + rg.stage * FAST_STAGE_BYTES;
         const uint32_t vbase = kbase + FAST_TILE_BYTES;
 
-        // S = Q K^T for this warp's TW tokens
-        float s[NT_S][4];
+        // S = Q K^T for this warp's TW tokens.  The 8 k-steps over d_head are spread over KG
+        // independent accumulator sets (summed afterwards) so that narrow warp slices do not
+        // serialise on the latency of 8 dependent MMAs.
+        constexpr int KG = NT_S >= 8 ? 1 : (NT_S >= 4 ? 2 : 4);
+        float sg[KG][NT_S][4];
 #pragma unroll
-        for (int n = 0; n < NT_S; n++) {
-            s[n][0] = 0.f; s[n][1] = 0.f; s[n][2] = 0.f; s[n][3] = 0.f;
-        }
+        for (int kg = 0; kg < KG; kg++)
+#pragma unroll
+            for (int n = 0; n < NT_S; n++) {
+                sg[kg][n][0] = 0.f; sg[kg][n][1] = 0.f; sg[kg][n][2] = 0.f; sg[kg][n][3] = 0.f;
+            }
 #pragma unroll
         for (int ks = 0; ks < 8; ks++) {
 #pragma unroll
@@ -294,10 +332,20 @@ __device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView&
                 const int g = 2 * ks + k_gsel;
                 uint32_t b0, b1, b2, b3;
                 ldsm_x4(b0, b1, b2, b3, kbase + t * (FAST_D * 2) + ((g ^ (t & 7)) << 4));
-                mma_16816(s[2 * np], qa[ks], b0, b1);
-                mma_16816(s[2 * np + 1], qa[ks], b2, b3);
+                mma_16816(sg[ks % KG][2 * np], qa[ks], b0, b1);
+                mma_16816(sg[ks % KG][2 * np + 1], qa[ks], b2, b3);
             }
         }
+        float s[NT_S][4];
+#pragma unroll
+        for (int n = 0; n < NT_S; n++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                float acc = sg[0][n][c];
+#pragma unroll
+                for (int kg = 1; kg < KG; kg++) acc += sg[kg][n][c];
+                s[n][c] = acc;
+            }
 
         // online softmax in log2 units; a thread holds rows r_lo (c0, c1) and r_hi (c2, c3)
         float mx_lo = NEG_BIG, mx_hi = NEG_BIG;
@@ -332,9 +380,12 @@ __device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView&
         }
         l_lo = l_lo * a_lo + sum_lo;
         l_hi = l_hi * a_hi + sum_hi;
+        // once the running maxima have settled the factors are exactly 1: skip the 64 multiplies
+        if (__any_sync(0xffffffffu, a_lo != 1.f || a_hi != 1.f)) {
 #pragma unroll
-        for (int n = 0; n < 16; n++) {
-            o[n][0] *= a_lo; o[n][1] *= a_lo; o[n][2] *= a_hi; o[n][3] *= a_hi;
+            for (int n = 0; n < 16; n++) {
+                o[n][0] *= a_lo; o[n][1] *= a_lo; o[n][2] *= a_hi; o[n][3] *= a_hi;
+            }
         }
 
         // O += P V
@@ -379,7 +430,9 @@ __device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView&
 // one mbarrier phase per such item orders the stores before the loads, and because every warp
 // waits for the phase, a warp can be at most one item ahead, so two buffers suffice.
 __device__ __forceinline__ bool combine_row_and_store(const PartialParams& p, const ItemView& it, float* scratch,
-                                                      uint32_t merge_bar, uint32_t& simt_count, int warp, int lane) {
+                                                      uint32_t merge_bar, uint32_t& simt_count, int warp, int lane,
+                                                      Ring& rg) {
+    const long long t0 = rg.timed ? clock64() : 0;
     __syncwarp();
     if (lane == 0) mbar_arrive(merge_bar);
     bool ok = mbar_wait_bounded(merge_bar, simt_count & 1);
@@ -404,11 +457,12 @@ __device__ __forceinline__ bool combine_row_and_store(const PartialParams& p, co
         if (d == 0) p.part_ml[it.slot_base] = make_float2(mm, ll);
     }
     simt_count++;
+    if (rg.timed) rg.tail_cycles += clock64() - t0;
     return true;
 }
 
-// Tensor-core item of up to 16 rows, 8 token splits: warp w owns tokens 8w..8w+7 of every tile (one
-// 8-wide column tile of S, one k = 8 step of P V).  This is how a sequence's private tail (ONE row)
+// Tensor-core item of up to 16 rows, 8 token splits: warp w owns tokens 8w..8w+7 of every tile, and
+// walks the tiles two at a time (see the loop).  This is how a sequence's private tail (ONE row)
 // is walked when the tensor-core sequence-first mode is selected: 15 of the 16 MMA rows are idle, but
 // the walk needs about a third of the instructions of the CUDA-core version, which matters because
 // with one 200 KiB CTA per SM only 8 warps are there to hide latency.  A partially filled tail tile
@@ -417,6 +471,7 @@ __device__ __forceinline__ bool combine_row_and_store(const PartialParams& p, co
 // write one partial per warp.
 __device__ __forceinline__ bool mma8_item(const PartialParams& p, const ItemView& it, Ring& rg, float* scratch,
                                           uint32_t merge_bar, uint32_t& simt_count, int warp, int lane) {
+    long long tseg = rg.timed ? clock64() : 0;
     const int tok0 = warp * 8;
     const int quad = lane & 3;
     const int r_lo = lane >> 2;
@@ -425,20 +480,7 @@ __device__ __forceinline__ bool mma8_item(const PartialParams& p, const ItemView
     const bool v_hi = r_hi < it.n_rows;
 
     uint32_t qa[8][4];
-    {
-        const __half* q = reinterpret_cast<const __half*>(p.q);
-        const size_t row_stride = (size_t)p.n_heads * FAST_D;
-        const __half* q_lo = q + (size_t)(it.row_begin + r_lo) * row_stride + (size_t)it.head * FAST_D;
-        const __half* q_hi = q + (size_t)(it.row_begin + r_hi) * row_stride + (size_t)it.head * FAST_D;
-#pragma unroll
-        for (int ks = 0; ks < 8; ks++) {
-            const int col = ks * 16 + 2 * quad;
-            qa[ks][0] = v_lo ? __ldg(reinterpret_cast<const uint32_t*>(q_lo + col)) : 0u;
-            qa[ks][1] = v_hi ? __ldg(reinterpret_cast<const uint32_t*>(q_hi + col)) : 0u;
-            qa[ks][2] = v_lo ? __ldg(reinterpret_cast<const uint32_t*>(q_lo + col + 8)) : 0u;
-            qa[ks][3] = v_hi ? __ldg(reinterpret_cast<const uint32_t*>(q_hi + col + 8)) : 0u;
-        }
-    }
+    bool have_q = false;
     float o[16][4];
 #pragma unroll
     for (int n = 0; n < 16; n++) {
@@ -446,80 +488,169 @@ __device__ __forceinline__ bool mma8_item(const PartialParams& p, const ItemView
     }
     float m_lo = NEG_BIG, m_hi = NEG_BIG, l_lo = 0.f, l_hi = 0.f;
 
-    // ldmatrix x4: the four 8x8 matrices are four consecutive granules of this warp's 8 token rows
+    // This warp's 8 token rows of a tile; ldmatrix lane roles are set per use below.
     const int row_t = tok0 + (lane & 7);
     const uint32_t row_off = row_t * (FAST_D * 2);
     const int sw = row_t & 7;
-    const int gsel = lane >> 3;
+    const int mi = lane >> 3;        // which of the four 8x8 matrices of an ldmatrix.x4 this lane addresses
     const int t0 = tok0 + 2 * quad;  // token of accumulator columns c0/c2; c1/c3 are the next token
 
-    for (int j = 0; j < it.n_tiles; j++) {
-        const int nt = tile_tokens(it, j, p.delta_tokens);
-        if (nt == 0) continue;
+    // Tiles are walked in PAIRS (A, B): the warp's 8 tokens of A and its 8 tokens of B form one
+    // 16-token block, so the softmax runs once per pair and P V uses full k = 16 MMAs whose B
+    // operand takes its first 8 token rows from A's stage and the other 8 from B's stage.  Two
+    // tiles per latency chain is what lets 8 warps keep up with the copy engine.
+    int j = 0;
+    while (j < it.n_tiles) {
+        const int nt_a = tile_tokens(it, j, p.delta_tokens);
+        if (nt_a == 0) {  // an empty tail (always the last tile): it occupies no stage
+            j++;
+            continue;
+        }
+        int nt_b = (j + 1 < it.n_tiles) ? tile_tokens(it, j + 1, p.delta_tokens) : 0;
+        const bool two = nt_b > 0;
+        j += 2;  // a second tile that is an empty tail is skipped with the pair
+
+        if (rg.timed) { const long long t = clock64(); rg.seg[0] += t - tseg; tseg = t; }
         if (!consumer_wait_full(rg)) return false;
-        if (tok0 < nt) {
-            const uint32_t kbase = rg.ring + rg.stage * FAST_STAGE_BYTES;
-            const uint32_t vbase = kbase + FAST_TILE_BYTES;
-            const bool partial = tok0 + 8 > nt;
-            if (partial) {
-                // absent tokens: the bulk copy did not fill their rows, so they hold stale bytes;
-                // zero the V rows (their P is forced to 0 below, and 0 * NaN would still be NaN)
-                for (int idx = lane; idx < (tok0 + 8 - nt) * 16; idx += 32)
-                    sts128_zero(vbase + (nt + (idx >> 4)) * (FAST_D * 2) + ((idx & 15) << 4));
-                __syncwarp();
-            }
-            float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint32_t stage_a = rg.stage;
+        const uint32_t ka = rg.ring + stage_a * FAST_STAGE_BYTES;
+        const uint32_t va = ka + FAST_TILE_BYTES;
+        if (!have_q) {
+            const long long tq = rg.timed ? clock64() : 0;
+            // The producer staged this item's query rows next to its first non-empty tile, in the
+            // slot of that tile's stage; they arrived with it.  Copy them to registers as the A
+            // fragments of the 8 k-steps before this stage is released.
+            const uint32_t qrow = rg.qslots + stage_a * QSLOT_BYTES + ((lane & 7) + (mi & 1) * 8) * QSLOT_PITCH + (mi >> 1) * 16;
 #pragma unroll
-            for (int k2 = 0; k2 < 4; k2++) {
-                uint32_t b0, b1, b2, b3;
-                ldsm_x4(b0, b1, b2, b3, kbase + row_off + (((4 * k2 + gsel) ^ sw) << 4));
-                mma_16816(sa, qa[2 * k2], b0, b1);
-                mma_16816(sb, qa[2 * k2 + 1], b2, b3);
+            for (int ks = 0; ks < 8; ks++) {
+                ldsm_x4(qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], qrow + ks * 32);
+                // rows past the item hold stale bytes: make them exact zeros
+                if (!v_lo) { qa[ks][0] = 0u; qa[ks][2] = 0u; }
+                if (!v_hi) { qa[ks][1] = 0u; qa[ks][3] = 0u; }
             }
-            float s0 = sa[0] + sb[0], s1 = sa[1] + sb[1], s2 = sa[2] + sb[2], s3 = sa[3] + sb[3];
-            const bool in0 = t0 < nt, in1 = t0 + 1 < nt;
-            if (!in0) { s0 = NEG_BIG; s2 = NEG_BIG; }
-            if (!in1) { s1 = NEG_BIG; s3 = NEG_BIG; }
-            float mx_lo = fmaxf(s0, s1), mx_hi = fmaxf(s2, s3);
-            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
-            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
-            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
-            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-            const float mn_lo = fmaxf(m_lo, mx_lo * p.scale_log2);
-            const float mn_hi = fmaxf(m_hi, mx_hi * p.scale_log2);
-            const float a_lo = fast_exp2(m_lo - mn_lo);
-            const float a_hi = fast_exp2(m_hi - mn_hi);
-            m_lo = mn_lo;
-            m_hi = mn_hi;
-            const float p0 = in0 ? fast_exp2(fmaf(s0, p.scale_log2, -mn_lo)) : 0.f;
-            const float p1 = in1 ? fast_exp2(fmaf(s1, p.scale_log2, -mn_lo)) : 0.f;
-            const float p2 = in0 ? fast_exp2(fmaf(s2, p.scale_log2, -mn_hi)) : 0.f;
-            const float p3 = in1 ? fast_exp2(fmaf(s3, p.scale_log2, -mn_hi)) : 0.f;
-            l_lo = l_lo * a_lo + (p0 + p1);
-            l_hi = l_hi * a_hi + (p2 + p3);
+            have_q = true;
+            if (rg.timed) rg.seg[4] += clock64() + (long long)(qa[7][3] & 0u) - tq;
+        }
+        uint32_t stage_b = stage_a, kb = ka, vb = va;  // without a second tile B aliases A (and is masked)
+        if (two) {
+            rg.advance();
+            if (!consumer_wait_full(rg)) return false;
+            stage_b = rg.stage;
+            kb = rg.ring + stage_b * FAST_STAGE_BYTES;
+            vb = kb + FAST_TILE_BYTES;
+        }
+        if (rg.timed) tseg = clock64();
+        // only the last tile of an item can be partially filled: A when it stands alone, else B
+        const int nt_last = two ? nt_b : nt_a;
+        const uint32_t v_last = two ? vb : va;
+        const bool partial = tok0 + 8 > nt_last;
+        if (partial) {
+            // Absent tokens: the bulk copy did not fill their rows, so they hold stale bytes.  Their
+            // scores are masked below; their V rows are zeroed here because 0 * NaN is NaN.
+            const int first_absent = nt_last > tok0 ? nt_last : tok0;
+            for (int idx = lane; idx < (tok0 + 8 - first_absent) * 16; idx += 32)
+                sts128_zero(v_last + (first_absent + (idx >> 4)) * (FAST_D * 2) + ((idx & 15) << 4));
+            __syncwarp();
+        }
+
+        // S for the 8 tokens of A and the 8 tokens of B: two accumulators each (even / odd k-steps)
+        float sa[2][4], sb[2][4];
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            sa[e][0] = 0.f; sa[e][1] = 0.f; sa[e][2] = 0.f; sa[e][3] = 0.f;
+            sb[e][0] = 0.f; sb[e][1] = 0.f; sb[e][2] = 0.f; sb[e][3] = 0.f;
+        }
+#pragma unroll
+        for (int k2 = 0; k2 < 4; k2++) {
+            // four consecutive granules of the 8 token rows = the B fragments of two k-steps
+            const uint32_t goff = row_off + (((4 * k2 + mi) ^ sw) << 4);
+            uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+            ldsm_x4(a0, a1, a2, a3, ka + goff);
+            ldsm_x4(b0, b1, b2, b3, kb + goff);
+            mma_16816(sa[0], qa[2 * k2], a0, a1);
+            mma_16816(sb[0], qa[2 * k2], b0, b1);
+            mma_16816(sa[1], qa[2 * k2 + 1], a2, a3);
+            mma_16816(sb[1], qa[2 * k2 + 1], b2, b3);
+        }
+        float s[8];  // [0..3] tile A (c0..c3), [4..7] tile B
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            s[c] = sa[0][c] + sa[1][c];
+            s[4 + c] = sb[0][c] + sb[1][c];
+        }
+        const bool in_a0 = t0 < nt_a, in_a1 = t0 + 1 < nt_a;
+        const bool in_b0 = two && t0 < nt_b, in_b1 = two && t0 + 1 < nt_b;
+        if (!in_a0) { s[0] = NEG_BIG; s[2] = NEG_BIG; }
+        if (!in_a1) { s[1] = NEG_BIG; s[3] = NEG_BIG; }
+        if (!in_b0) { s[4] = NEG_BIG; s[6] = NEG_BIG; }
+        if (!in_b1) { s[5] = NEG_BIG; s[7] = NEG_BIG; }
+        float mx_lo = fmaxf(fmaxf(s[0], s[1]), fmaxf(s[4], s[5]));
+        float mx_hi = fmaxf(fmaxf(s[2], s[3]), fmaxf(s[6], s[7]));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        // a warp whose 16 tokens are all absent keeps its state: NEG_BIG scores would otherwise win
+        const float mn_lo = fmaxf(m_lo, mx_lo > 0.5f * NEG_BIG ? mx_lo * p.scale_log2 : NEG_BIG);
+        const float mn_hi = fmaxf(m_hi, mx_hi > 0.5f * NEG_BIG ? mx_hi * p.scale_log2 : NEG_BIG);
+        const float a_lo = fast_exp2(m_lo - mn_lo);
+        const float a_hi = fast_exp2(m_hi - mn_hi);
+        m_lo = mn_lo;
+        m_hi = mn_hi;
+        float pr[8];
+        pr[0] = in_a0 ? fast_exp2(fmaf(s[0], p.scale_log2, -mn_lo)) : 0.f;
+        pr[1] = in_a1 ? fast_exp2(fmaf(s[1], p.scale_log2, -mn_lo)) : 0.f;
+        pr[2] = in_a0 ? fast_exp2(fmaf(s[2], p.scale_log2, -mn_hi)) : 0.f;
+        pr[3] = in_a1 ? fast_exp2(fmaf(s[3], p.scale_log2, -mn_hi)) : 0.f;
+        pr[4] = in_b0 ? fast_exp2(fmaf(s[4], p.scale_log2, -mn_lo)) : 0.f;
+        pr[5] = in_b1 ? fast_exp2(fmaf(s[5], p.scale_log2, -mn_lo)) : 0.f;
+        pr[6] = in_b0 ? fast_exp2(fmaf(s[6], p.scale_log2, -mn_hi)) : 0.f;
+        pr[7] = in_b1 ? fast_exp2(fmaf(s[7], p.scale_log2, -mn_hi)) : 0.f;
+        l_lo = l_lo * a_lo + ((pr[0] + pr[1]) + (pr[4] + pr[5]));
+        l_hi = l_hi * a_hi + ((pr[2] + pr[3]) + (pr[6] + pr[7]));
+        // once the running maxima have settled the factors are exactly 1: skip the 64 multiplies
+        if (__any_sync(0xffffffffu, a_lo != 1.f || a_hi != 1.f)) {
 #pragma unroll
             for (int n = 0; n < 16; n++) {
                 o[n][0] *= a_lo; o[n][1] *= a_lo; o[n][2] *= a_hi; o[n][3] *= a_hi;
             }
-            const uint32_t pa0 = pack_half2(p0, p1), pa1 = pack_half2(p2, p3);
-#pragma unroll
-            for (int dq = 0; dq < 4; dq++) {
-                uint32_t b0, b1, b2, b3;
-                ldsm_x4_trans(b0, b1, b2, b3, vbase + row_off + (((4 * dq + gsel) ^ sw) << 4));
-                mma_1688(o[4 * dq + 0], pa0, pa1, b0);
-                mma_1688(o[4 * dq + 1], pa0, pa1, b1);
-                mma_1688(o[4 * dq + 2], pa0, pa1, b2);
-                mma_1688(o[4 * dq + 3], pa0, pa1, b3);
-            }
-            if (partial) fence_proxy_async();
         }
-        consumer_release(rg, lane);
+        // P as the A operand of a k = 16 step: k 0..7 are A's tokens, k 8..15 are B's tokens
+        uint32_t pa[4];
+        pa[0] = pack_half2(pr[0], pr[1]);
+        pa[1] = pack_half2(pr[2], pr[3]);
+        pa[2] = pack_half2(pr[4], pr[5]);
+        pa[3] = pack_half2(pr[6], pr[7]);
+        if (rg.timed) { const long long t = clock64() + (long long)(pa[0] & 0u); rg.seg[1] += t - tseg; tseg = t; }
+        // V: matrices 0 / 2 come from A's stage, 1 / 3 from B's stage; 0 / 1 are granule 2dp, 2 / 3 the next
+        const uint32_t vrow = ((mi & 1) ? vb : va) + row_off;
+#pragma unroll
+        for (int dp = 0; dp < 8; dp++) {
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4_trans(b0, b1, b2, b3, vrow + (((2 * dp + (mi >> 1)) ^ sw) << 4));
+            mma_16816(o[2 * dp], pa, b0, b1);
+            mma_16816(o[2 * dp + 1], pa, b2, b3);
+        }
+        if (partial) fence_proxy_async();
+        // hand both stages back
+        __syncwarp();
+        if (lane == 0) {
+            mbar_arrive(rg.empty_bar + 8 * stage_a);
+            if (two) mbar_arrive(rg.empty_bar + 8 * stage_b);
+        }
+        rg.advance();
+        if (rg.timed) { const long long t = clock64(); rg.seg[2] += t - tseg; tseg = t; }
     }
 
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    if (it.n_rows == 1 && !have_q) {
+        // the item held no token at all (an empty reserved tail): mark its partial as empty
+        if (warp == 0 && lane == 0) p.part_ml[it.slot_base] = make_float2(NEG_BIG, 0.f);
+        return true;
+    }
     if (it.n_rows == 1) {
         // row 0 lives in the first quad: lane q holds outputs 8n + 2q, 8n + 2q + 1
         float* mine = scratch + ((simt_count & 1) * NUM_CONSUMER_WARPS + warp) * SCRATCH_FLOATS_PER_WARP;
@@ -532,7 +663,8 @@ __device__ __forceinline__ bool mma8_item(const PartialParams& p, const ItemView
             for (int n = 0; n < 16; n++)
                 *reinterpret_cast<float2*>(mine + 4 + 8 * n + 2 * quad) = make_float2(o[n][0], o[n][1]);
         }
-        return combine_row_and_store(p, it, scratch, merge_bar, simt_count, warp, lane);
+        if (rg.timed) rg.seg[3] += clock64() - tseg;
+        return combine_row_and_store(p, it, scratch, merge_bar, simt_count, warp, lane, rg);
     }
     const int slot0 = it.slot_base + warp * it.n_rows;
     if (v_lo) {
@@ -654,20 +786,26 @@ __device__ __forceinline__ bool simt_item(const PartialParams& p, const ItemView
         *reinterpret_cast<float4*>(mine + 4 + 8 * g) = make_float4(o[0], o[1], o[2], o[3]);
         *reinterpret_cast<float4*>(mine + 8 + 8 * g) = make_float4(o[4], o[5], o[6], o[7]);
     }
-    return combine_row_and_store(p, it, scratch, merge_bar, simt_count, warp, lane);
+    return combine_row_and_store(p, it, scratch, merge_bar, simt_count, warp, lane, rg);
 }
 
 __global__ void __launch_bounds__(NUM_THREADS, 1) attn_partial_kernel(const PartialParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
-    float* scratch = reinterpret_cast<float*>(smem + NUM_STAGES * FAST_STAGE_BYTES);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NUM_STAGES * FAST_STAGE_BYTES + SCRATCH_BYTES);
+    float* scratch = reinterpret_cast<float*>(smem + SMEM_SCRATCH_OFFSET);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_BAR_OFFSET);
 
     Ring rg;
     rg.ring = smem_u32(smem);
+    rg.qslots = smem_u32(smem + SMEM_Q_OFFSET);
     rg.full_bar = smem_u32(bars);
     rg.empty_bar = smem_u32(bars + NUM_STAGES);
     rg.stage = 0;
     rg.phase = 0;
+    rg.timed = p.trace != nullptr;
+    rg.wait_cycles = 0;
+    rg.tail_cycles = 0;
+    rg.seg[0] = rg.seg[1] = rg.seg[2] = rg.seg[3] = rg.seg[4] = rg.seg[5] = 0;
+    const long long t_begin = rg.timed ? clock64() : 0;
     const uint32_t merge_bar = smem_u32(bars + 2 * NUM_STAGES);
 
     if (threadIdx.x == 0) {
@@ -689,17 +827,28 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_partial_kernel(const Part
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
-    if (p.trace && threadIdx.x == 0) p.trace[4 * blockIdx.x + 0] = global_timer_ns();
-    if (warp == NUM_CONSUMER_WARPS) {
-        producer_loop(p, rg, item_begin, item_end, lane);
-        if (p.trace && lane == 0) p.trace[4 * blockIdx.x + 1] = global_timer_ns();
+    if (p.trace && threadIdx.x == 0) p.trace[16 * blockIdx.x + 0] = global_timer_ns();
+    if (warp >= NUM_CONSUMER_WARPS) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PRODUCER_REGS));
+        if (warp == NUM_CONSUMER_WARPS) {
+            producer_loop(p, rg, item_begin, item_end, lane);
+            if (p.trace && lane == 0) {
+                p.trace[16 * blockIdx.x + 1] = global_timer_ns();
+                p.trace[16 * blockIdx.x + 6] = (unsigned long long)rg.wait_cycles;
+            }
+        }
         return;
     }
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(CONSUMER_REGS));
 
     uint32_t simt_count = 0;
+    ItemView next = item_begin < item_end ? load_item(p.items, item_begin) : ItemView{};
+    long long t_between = rg.timed ? clock64() : 0;
     for (int i = item_begin; i < item_end; i++) {
-        const ItemView it = load_item(p.items, i);
+        const ItemView it = next;
+        if (i + 1 < item_end) next = load_item(p.items, i + 1);  // in flight while this item is walked
         const int splits = it.flags >> ITEM_SPLITS_SHIFT;
+        if (rg.timed) rg.seg[5] += clock64() - t_between;
         bool ok;
         if (splits == 0) {
             ok = simt_item(p, it, rg, scratch, merge_bar, simt_count, warp, lane);
@@ -716,9 +865,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_partial_kernel(const Part
             if (lane == 0) report(p.status, STATUS_FULL_WAIT_TIMEOUT);
             break;
         }
+        if (rg.timed) t_between = clock64();
     }
-    if (p.trace && lane == 0 && (warp == 0 || warp == NUM_CONSUMER_WARPS - 1))
-        p.trace[4 * blockIdx.x + (warp == 0 ? 2 : 3)] = global_timer_ns();
+    if (p.trace && lane == 0 && (warp == 0 || warp == NUM_CONSUMER_WARPS - 1)) {
+        p.trace[16 * blockIdx.x + (warp == 0 ? 2 : 3)] = global_timer_ns();
+        if (warp == 0) {
+            p.trace[16 * blockIdx.x + 4] = (unsigned long long)rg.wait_cycles;
+            p.trace[16 * blockIdx.x + 5] = (unsigned long long)rg.tail_cycles;
+            p.trace[16 * blockIdx.x + 7] = (unsigned long long)(clock64() - t_begin);
+            for (int k = 0; k < 6; k++) p.trace[16 * blockIdx.x + 8 + k] = (unsigned long long)rg.seg[k];
+        }
+    }
 }
 
 // One warp per (row, head): out = sum_i 2^(m_i - M) O_i / sum_i 2^(m_i - M) l_i.
@@ -737,6 +894,7 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeParams p) {
     for (int i = b; i < e; i++) {
         const int slot = __ldg(p.merge_slots + i);
         const float2 ml = p.part_ml[slot];
+        if (!(ml.y > 0.f)) continue;  // an empty piece: its O row was not written
         const float w = fast_exp2(ml.x - mm);
         ll = fmaf(w, ml.y, ll);
         const float4 v = *reinterpret_cast<const float4*>(p.part_o + (size_t)slot * FAST_D + 4 * lane);

@@ -35,8 +35,9 @@ struct PartialParams {
     int delta_tokens;            // tokens appended to every tail since the plan was built
     float scale_log2;            // log2(e) / sqrt(d_head)
     int* status;
-    unsigned long long* trace = nullptr;  // optional [n_ctas][4] ns timestamps: start, producer end, first and
-                                 // last consumer warp end; null = off
+    unsigned long long* trace = nullptr;  // optional [n_ctas][8], null = off: ns timestamps of start,
+                                 // producer end, first and last consumer warp end; then cycles: warp 0 waiting for
+                                 // tiles, warp 0 combining/storing partials, producer waiting for free stages, warp 0 total
 };
 
 // Persistent kernel: chunk-first items on tensor cores and sequence-first items on CUDA cores,

@@ -18,12 +18,18 @@ struct Unit {
 // paid for by its HBM bytes alone (weight 1); wider row blocks issue proportionally more MMAs
 // per byte and become tensor-pipe bound.
 double chunk_first_tile_weight(int splits) {
-    return splits >= 4 ? 1.0 : (splits == 2 ? 1.4 : 2.8);
+    return splits >= 4 ? 1.08 : (splits == 2 ? 1.5 : 2.8);
 }
 // partial rows an item emits: a one-row item combines its warps on chip and writes one row, a
 // wider item writes one row per (token split, query row)
 int item_slots(int n_rows, int splits) { return n_rows == 1 ? 1 : n_rows * std::max(1, splits); }
-constexpr double kTailTileWeight = 0.5;  // a tail holds between 0 and chunk_size - 1 tokens
+// Fixed cost of starting and finishing an item (descriptor, queries, combining the warps, storing the
+// partial), in units of one full tile.
+constexpr double kItemOverhead = 0.25;
+// A tail tile costs what it holds now, plus a little for the tokens appended before the next rebuild.
+double tail_tile_weight(int tokens, int chunk_size) {
+    return std::min(1.0, std::max(0.05, (tokens + 4.0) / chunk_size));
+}
 
 std::string fmt(const char* f, long a = 0, long b = 0, long c = 0) {
     char buf[256];
@@ -38,7 +44,8 @@ void cut_units(Plan& plan, const std::vector<Unit>& units, size_t ubegin, size_t
     double total = 0;
     for (size_t u = ubegin; u < uend; u++) {
         const Unit& un = units[u];
-        total += un.w * un.n_tiles - (un.tail ? un.w - kTailTileWeight : 0.0);
+        total += kItemOverhead + un.w * un.n_tiles -
+                 (un.tail ? un.w - tail_tile_weight(un.last_tokens, plan.chunk_size) : 0.0);
     }
     int eff = (int)std::min<double>(n_ctas, std::max(1.0, total / 1.5));
     const size_t first_item = plan.items.size();
@@ -66,8 +73,9 @@ void cut_units(Plan& plan, const std::vector<Unit>& units, size_t ubegin, size_t
             plan.items.push_back(it);
             item_cta.push_back(cur);
         };
+        acc += kItemOverhead;
         for (int j = 0; j < un.n_tiles; j++) {
-            const double w = (un.tail && j == un.n_tiles - 1) ? kTailTileWeight : un.w;
+            const double w = (un.tail && j == un.n_tiles - 1) ? tail_tile_weight(un.last_tokens, plan.chunk_size) : un.w;
             const int c = cta_of(acc + 0.5 * w);
             if (cur < 0) cur = c;
             if (c != cur) {

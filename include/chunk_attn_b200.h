@@ -151,9 +151,11 @@ CA_API int ca_read_chunk(ca_context* ctx, int chunk_id, int n_tokens, void* k_ou
 CA_API int ca_status_read(ca_context* ctx, ca_stream stream, int32_t* status);
 
 /* Per-CTA timestamps of the last attention launch when CA_OPT_TRACE is on (diagnostics): for CTA i,
- * out[4i..4i+3] = start, producer warp end, first consumer warp end, last consumer warp end, in ns
- * of the GPU's global timer.  `out` is a HOST array of 4 * max_ctas; returns the CTA count through
- * n_ctas.  Synchronises the stream. */
+ * out[8i..8i+3] = start, producer warp end, first consumer warp end, last consumer warp end, in ns
+ * of the GPU's global timer; out[8i+4..8i+7] = SM cycles: first consumer warp waiting for tiles, the
+ * same warp combining warps / storing partials, producer waiting for free stages, first consumer
+ * warp in total.  `out` is a HOST array of 8 * max_ctas; returns the CTA count through n_ctas.
+ * Synchronises the stream. */
 CA_API int ca_context_read_trace(ca_context* ctx, uint64_t* out, int max_ctas, int* n_ctas, ca_stream stream);
 
 /* Per-step counters of the current work list (the roofline metric is computed from them). */

@@ -164,9 +164,9 @@ def test_balance_config2_shape():
     plan = cabi.Plan(infos, 32, 32, n_ctas=148)
     items, cta = plan.items(), plan.array(cabi.PLAN_CTA_ITEM_BEGIN)
     assert len(cta) == 149
-    # weighted as the planner weighs them: a tail tile counts one half
-    loads = [float((items[cta[c]:cta[c + 1], 1] - 0.5 * (items[cta[c]:cta[c + 1], 6] & 1)).sum()) for c in range(148)]
-    assert max(loads) - min(loads) <= 2.0
+    # empty tails cost (almost) nothing: count full tiles only
+    loads = [float((items[cta[c]:cta[c + 1], 1] - (items[cta[c]:cta[c + 1], 6] & 1)).sum()) for c in range(148)]
+    assert max(loads) - min(loads) <= 8.0   # chunk-first tiles weigh a little more than private ones
     st = plan.stats()
     assert st["unique_kv_bytes"] == 301_989_888 and st["n_runs"] == 1
 
