@@ -110,7 +110,7 @@ def make_infos(infos):
 class Plan:
     """Host-only work-list builder (no GPU needed)."""
 
-    def __init__(self, infos, n_seqs, n_heads, chunk_size=64, tpp_threshold=1, n_ctas=148,
+    def __init__(self, infos, n_seqs, n_heads, chunk_size=64, tpp_threshold=1, n_ctas=296,
                  max_chunks=1 << 30, split_phases=False, seq_first_tensor=True):
         arr, n = make_infos(infos)
         self._h = C.c_void_p()
@@ -201,10 +201,10 @@ class Context:
     def read_trace(self, max_ctas=4096):
         """[n_ctas, 8] uint64: ns of start, producer end, first / last consumer warp end; cycles of
         consumer warp 0 waiting for tiles, combining, producer waiting for free stages, warp 0 total."""
-        buf = (C.c_uint64 * (16 * max_ctas))()
+        buf = (C.c_uint64 * (8 * max_ctas))()
         n = C.c_int()
         check(lib.ca_context_read_trace(self._h, buf, max_ctas, C.byref(n), self._stream()))
-        return np.ctypeslib.as_array(buf)[:16 * n.value].reshape(-1, 16).copy()
+        return np.ctypeslib.as_array(buf)[:8 * n.value].reshape(-1, 8).copy()
 
     def delta_tokens(self):
         return lib.ca_context_delta_tokens(self._h)

@@ -195,8 +195,8 @@ int ca_context_set_option(ca_context* c, int option, int64_t value) {
         DeviceGuard guard(c->device);
         if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
         if (value && !c->trace) {
-            CA_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->trace), (size_t)kTraceCtas * 16 * sizeof(unsigned long long)));
-            CA_CUDA(cudaMemset(c->trace, 0, (size_t)kTraceCtas * 16 * sizeof(unsigned long long)));
+            CA_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->trace), (size_t)kTraceCtas * 8 * sizeof(unsigned long long)));
+            CA_CUDA(cudaMemset(c->trace, 0, (size_t)kTraceCtas * 8 * sizeof(unsigned long long)));
         } else if (!value && c->trace) {
             CA_CUDA(cudaFree(c->trace));
             c->trace = nullptr;
@@ -215,7 +215,7 @@ int ca_refresh_kernel_context(ca_context* c, const ca_chunk_info* infos, int n_i
     DeviceGuard guard(c->device);
     if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
     c->valid = false;
-    const int n_ctas = c->opt_ctas > 0 ? c->opt_ctas : c->num_sms;
+    const int n_ctas = c->opt_ctas > 0 ? c->opt_ctas : c->num_sms * ca::FAST_CTAS_PER_SM;
     std::string err = ca::build_plan(c->plan, infos, n_infos, n_seqs, c->geo.n_heads, c->geo.chunk_size,
                                      c->tpp_threshold, n_ctas, c->max_chunks, c->opt_split, c->geo.d_head,
                                      c->geo.esize, c->fast, c->opt_sf_tensor);
@@ -523,7 +523,7 @@ int ca_context_read_trace(ca_context* c, uint64_t* out, int max_ctas, int* n_cta
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     const int n = c->trace_ctas < max_ctas ? c->trace_ctas : max_ctas;
     CA_CUDA(cudaStreamSynchronize(stream));
-    if (n > 0) CA_CUDA(cudaMemcpy(out, c->trace, (size_t)n * 16 * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+    if (n > 0) CA_CUDA(cudaMemcpy(out, c->trace, (size_t)n * 8 * sizeof(uint64_t), cudaMemcpyDeviceToHost));
     *n_ctas = n;
     return CA_OK;
 }

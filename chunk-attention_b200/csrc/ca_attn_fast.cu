@@ -1,6 +1,6 @@
 // Decode attention over a prefix tree of KV chunks, fp16 / d_head 128 / chunk_size 64, sm_100a.
 //
-// attn_partial_kernel — ONE persistent kernel, one CTA per SM, serves both phases of the
+// attn_partial_kernel — ONE persistent kernel, two CTAs per SM, serves both phases of the
 // reference's two-phase decode attention:
 //   * chunk-first items (reference: attn_chunk_first_kernel_v2, cpp/chunk_attn/kernel_cuda.cu:796-883):
 //     the queries of all rows sharing a run of chunks form a small dense contraction against
@@ -8,12 +8,17 @@
 //     a flash-style online softmax kept in registers across the WHOLE run, so a run emits one
 //     partial per row instead of one per chunk.
 //   * sequence-first items (reference: attn_seq_first_kernel, kernel_cuda.cu:885-1086): one row's
-//     private tail chunks, a memory-bound walk on CUDA cores: 128-bit shared-memory loads,
-//     fp32 dot products, warp-shuffle reductions.
-// Both kinds read their K/V tiles from the same ring of 32 KiB shared-memory stages, filled by a
-// dedicated producer warp with 1-D TMA bulk copies (cp.async.bulk + mbarrier transaction counts)
-// that run ahead across item boundaries; the host has cut the tile stream into equal parts, one
-// per CTA (ca_plan.h).
+//     private tail chunks.  Memory-bound; walked by default with the same tensor-core code (one
+//     useful row out of 16 — the MMA path needs a third of the instructions of the CUDA-core
+//     walk, and with a handful of warps per SM instruction latency, not HBM, was the limit), or,
+//     selectably, on CUDA cores with 128-bit shared-memory loads, fp32 dot products and
+//     warp-shuffle reductions.
+// Both kinds read their K/V tiles from a ring of 32 KiB shared-memory stages, filled by a
+// producer warp with 1-D TMA bulk copies (cp.async.bulk + mbarrier transaction counts) that run
+// ahead across item boundaries; the host has cut the tile stream into equal parts, one per CTA
+// (ca_plan.h).  A CTA is one consumer warpgroup (4 warps) plus a producer warpgroup; two CTAs share
+// an SM so that one CTA's item boundaries (queries, combining warps, storing a partial) hide
+// behind the other CTA's steady state.
 //
 // attn_merge_kernel — combines the partials of each (row, head) with the usual
 // max-rescaled sum (reference: the merge inlined in kernel_cuda.cu:962-984,1042-1085).
@@ -30,18 +35,17 @@
 namespace ca {
 namespace {
 
-constexpr int NUM_STAGES = 6;
-constexpr int NUM_CONSUMER_WARPS = 8;
-// 8 consumer warps (two warpgroups) + one producer warpgroup of which a single warp works.  The
-// register file is re-split at run time: the producer group shrinks to 40 registers per thread and
-// the consumers grow to 232 (128 * 40 + 256 * 232 = 64512 <= 65536).
+constexpr int NUM_STAGES = 3;
+constexpr int NUM_CONSUMER_WARPS = FAST_CONSUMER_WARPS;  // one warpgroup
+// The CTA is two warpgroups; the register file is re-split at run time: the producer group shrinks
+// to 56 registers per thread, the consumers grow to 200 (2 CTAs * (128 * 56 + 128 * 200) = 65536).
 constexpr int NUM_THREADS = (NUM_CONSUMER_WARPS + 4) * 32;
-constexpr int PRODUCER_REGS = 40;
-constexpr int CONSUMER_REGS = 232;
+constexpr int PRODUCER_REGS = 56;
+constexpr int CONSUMER_REGS = 200;
 constexpr int SCRATCH_FLOATS_PER_WARP = 132;  // m, l, 2 pad, o[128]
 constexpr int SCRATCH_BYTES = 2 * NUM_CONSUMER_WARPS * SCRATCH_FLOATS_PER_WARP * 4;
 constexpr int NUM_BARRIERS = 2 * NUM_STAGES + 1;
-// query rows of items of up to 16 rows travel with the item's first tile: one slot per ring stage
+// Query rows of items of up to 16 rows travel with the item's first tile: one slot per ring stage.
 // Rows are pitched 16 bytes past their 256 so that the 8 rows an ldmatrix reads fall in 8 different
 // bank groups.
 constexpr int QSLOT_ROWS = 16;
@@ -52,7 +56,8 @@ constexpr int SMEM_Q_OFFSET = SMEM_RING_BYTES;
 constexpr int SMEM_SCRATCH_OFFSET = SMEM_Q_OFFSET + NUM_STAGES * QSLOT_BYTES;
 constexpr int SMEM_BAR_OFFSET = SMEM_SCRATCH_OFFSET + SCRATCH_BYTES;
 constexpr int SMEM_BYTES = SMEM_BAR_OFFSET + NUM_BARRIERS * 8 + 16;
-static_assert(SMEM_BYTES <= 232448, "more than the 227 KiB a CTA can have");
+// two CTAs per SM: 228 KiB per SM, 1 KiB of it reserved per resident CTA
+static_assert(2 * (SMEM_BYTES + 1024) <= 233472, "two CTAs do not fit in one SM's shared memory");
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // about two seconds
 constexpr float NEG_BIG = -1.0e30f;
 
@@ -60,9 +65,12 @@ struct ItemView {
     int tile_begin, n_tiles, head, row_begin, n_rows, slot_base, flags, last_tokens;
 };
 
+// Volatile so that the load is issued where it is written (one item ahead of its use) instead of
+// being sunk to the first use by the compiler.
 __device__ __forceinline__ ItemView load_item(const int4* items, int i) {
-    const int4 a = __ldg(items + 2 * i);
-    const int4 b = __ldg(items + 2 * i + 1);
+    int4 a, b;
+    asm volatile("ld.global.nc.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(items + 2 * i));
+    asm volatile("ld.global.nc.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(items + 2 * i + 1));
     return ItemView{a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 }
 
@@ -170,8 +178,6 @@ struct Ring {
     bool timed;               // tracing on: accumulate stall cycles
     long long wait_cycles;    // cycles spent waiting on ring barriers
     long long tail_cycles;    // consumers: cycles spent combining warps and storing partials
-    long long seg[6];         // consumers, 8-split items: prologue, scores+softmax, P V+release, epilogue,
-                              // query fragments, time between items
     __device__ __forceinline__ void advance() {
         if (++stage == NUM_STAGES) {
             stage = 0;
@@ -191,7 +197,7 @@ __device__ __forceinline__ void producer_loop(const PartialParams& p, Ring& rg, 
         const ItemView it = next;
         if (i + 1 < item_end) next = load_item(p.items, i + 1);  // in flight while this item streams
         // items of up to 16 rows get their query rows staged next to their first tile
-        bool q_pending = (it.flags >> ITEM_SPLITS_SHIFT) == 8;
+        bool q_pending = (it.flags >> ITEM_SPLITS_SHIFT) == NUM_CONSUMER_WARPS;
         for (int j0 = 0; j0 < it.n_tiles && ok; j0 += 32) {
             // each lane fetches the pool slot of one upcoming tile, lane 0 reads them by shuffle
             const int jl = j0 + lane;
@@ -260,14 +266,60 @@ __device__ __forceinline__ void consumer_release(Ring& rg, int lane) {
     rg.advance();
 }
 
-// Chunk-first item on tensor cores.  The 8 warps form MT = 8 / TS row tiles of 16 rows times TS
-// token splits; a warp owns 16 query rows and the TW = 64 / TS tokens [split * TW, ...) of every
-// tile, keeps its own (max, sum, O) and writes its own partial at the end of the item.
+// Combine the warps' (max, sum, O[128]) of a ONE-row item and write its single partial.  Every
+// warp has stored its state in its slot of the double-buffered scratch (buffer = item parity);
+// one mbarrier phase per such item orders the stores before the loads, and because every warp
+// waits for the phase, a warp can be at most one item ahead, so two buffers suffice.
+__device__ __forceinline__ bool combine_row_and_store(const PartialParams& p, const ItemView& it, float* scratch,
+                                                      uint32_t merge_bar, uint32_t& row_items, int warp, int lane,
+                                                      Ring& rg) {
+    const long long t0 = rg.timed ? clock64() : 0;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(merge_bar);
+    bool ok = mbar_wait_bounded(merge_bar, row_items & 1);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) return false;
+    {
+        // warp w finishes outputs 32w .. 32w+31
+        const float* base = scratch + (row_items & 1) * NUM_CONSUMER_WARPS * SCRATCH_FLOATS_PER_WARP;
+        const int d = warp * 32 + lane;
+        float mm = NEG_BIG;
+#pragma unroll
+        for (int w = 0; w < NUM_CONSUMER_WARPS; w++) mm = fmaxf(mm, base[w * SCRATCH_FLOATS_PER_WARP]);
+        float ll = 0.f, od = 0.f;
+#pragma unroll
+        for (int w = 0; w < NUM_CONSUMER_WARPS; w++) {
+            const float wl = base[w * SCRATCH_FLOATS_PER_WARP + 1];
+            // a warp that saw no token keeps l = 0 and contributes nothing whatever its weight
+            const float wgt = fast_exp2(base[w * SCRATCH_FLOATS_PER_WARP] - mm);
+            ll = fmaf(wgt, wl, ll);
+            od = fmaf(wgt, base[w * SCRATCH_FLOATS_PER_WARP + 4 + d], od);
+        }
+        p.part_o[(size_t)it.slot_base * FAST_D + d] = od;
+        if (d == 0) p.part_ml[it.slot_base] = make_float2(mm, ll);
+    }
+    row_items++;
+    if (rg.timed) rg.tail_cycles += clock64() - t0;
+    return true;
+}
+
+// Tensor-core item.  The 4 warps form MT = 4 / TS row tiles of 16 rows times TS token splits; a
+// warp owns 16 query rows and the TW = 64 / TS tokens [split * TW, ...) of every tile and keeps its
+// own (max, sum, O) for the whole item:
+//   TS = 4: up to 16 rows, 16 tokens per warp — chunk-first items of narrow runs AND a sequence's
+//           private tail (one row).  Its queries arrive through shared memory with the first
+//           tile; a partially filled tail tile is handled by masking the scores of absent tokens
+//           and zeroing their V rows in the staged copy; a one-row item combines its 4 warps
+//           through shared memory and writes a single partial.
+//   TS = 2: up to 32 rows, 32 tokens per warp;   TS = 1: up to 64 rows, all 64 tokens.
+//           Queries come straight from global memory; each warp writes its own partial rows.
 template <int TS>
-__device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView& it, Ring& rg, int warp, int lane) {
+__device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView& it, Ring& rg, float* scratch,
+                                         uint32_t merge_bar, uint32_t& row_items, int warp, int lane) {
     constexpr int MT = NUM_CONSUMER_WARPS / TS;
     constexpr int TW = FAST_C / TS;   // tokens per warp per tile
     constexpr int NT_S = TW / 8;      // 8-token column tiles of S
+    constexpr bool STAGED_Q = (TS == NUM_CONSUMER_WARPS);
     const int mt = warp % MT;
     const int split = warp / MT;
     const int tok0 = split * TW;
@@ -276,10 +328,12 @@ __device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView&
     const int r_hi = r_lo + 8;
     const bool v_lo = r_lo < it.n_rows;
     const bool v_hi = r_hi < it.n_rows;
+    const int mi = lane >> 3;  // which of the four 8x8 matrices of an ldmatrix.x4 this lane addresses
 
     // Q as A fragments for the 8 k-steps over d_head; rows past the item are zero
     uint32_t qa[8][4];
-    {
+    bool have_q = !STAGED_Q;
+    if (!STAGED_Q) {
         const __half* q = reinterpret_cast<const __half*>(p.q);
         const size_t row_stride = (size_t)p.n_heads * FAST_D;
         const __half* q_lo = q + (size_t)(it.row_begin + r_lo) * row_stride + (size_t)it.head * FAST_D;
@@ -302,16 +356,41 @@ __device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView&
     float m_lo = NEG_BIG, m_hi = NEG_BIG, l_lo = 0.f, l_hi = 0.f;
 
     // per-lane row offsets for the two ldmatrix address patterns
-    const int k_tok = (lane & 7) + ((lane >> 4) << 3);   // K: matrices 2,3 are the next 8 tokens
-    const int k_gsel = (lane >> 3) & 1;                  //    matrices 1,3 are the next granule
-    const int v_tok = (lane & 7) + (((lane >> 3) & 1) << 3);  // V: matrices 1,3 are the next 8 tokens
-    const int v_gsel = lane >> 4;                             //    matrices 2,3 are the next granule
+    const int k_tok = (lane & 7) + ((mi >> 1) << 3);   // K: matrices 2,3 are the next 8 tokens
+    const int k_gsel = mi & 1;                         //    matrices 1,3 are the next granule
+    const int v_tok = (lane & 7) + ((mi & 1) << 3);    // V: matrices 1,3 are the next 8 tokens
+    const int v_gsel = mi >> 1;                        //    matrices 2,3 are the next granule
 
     for (int j = 0; j < it.n_tiles; j++) {
-        if (tile_tokens(it, j, p.delta_tokens) == 0) continue;
+        const int nt = tile_tokens(it, j, p.delta_tokens);
+        if (nt == 0) continue;  // an empty reserved tail: it occupies no stage
         if (!consumer_wait_full(rg)) return false;
         const uint32_t kbase = rg.ring + rg.stage * FAST_STAGE_BYTES;
         const uint32_t vbase = kbase + FAST_TILE_BYTES;
+        if (STAGED_Q && !have_q) {
+            // The producer staged this item's query rows next to its first non-empty tile, in the
+            // slot of that tile's stage; they arrived with it.  Copy them to registers as the A
+            // fragments of the 8 k-steps before this stage is released.
+            const uint32_t qrow = rg.qslots + rg.stage * QSLOT_BYTES + ((lane & 7) + (mi & 1) * 8) * QSLOT_PITCH + (mi >> 1) * 16;
+#pragma unroll
+            for (int ks = 0; ks < 8; ks++) {
+                ldsm_x4(qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], qrow + ks * 32);
+                // rows past the item hold stale bytes: make them exact zeros
+                if (!v_lo) { qa[ks][0] = 0u; qa[ks][2] = 0u; }
+                if (!v_hi) { qa[ks][1] = 0u; qa[ks][3] = 0u; }
+            }
+            have_q = true;
+        }
+        // only a private tail (a one-row item, TS = 4) can be partially filled
+        const bool partial = STAGED_Q && (tok0 + TW > nt);
+        if (partial) {
+            // Absent tokens: the bulk copy did not fill their rows, so they hold stale bytes.  Their
+            // scores are masked below; their V rows are zeroed here because 0 * NaN is NaN.
+            const int first_absent = nt > tok0 ? nt : tok0;
+            for (int idx = lane; idx < (tok0 + TW - first_absent) * 16; idx += 32)
+                sts128_zero(vbase + (first_absent + (idx >> 4)) * (FAST_D * 2) + ((idx & 15) << 4));
+            __syncwarp();
+        }
 
         // S = Q K^T for this warp's TW tokens.  The 8 k-steps over d_head are spread over KG
         // independent accumulator sets (summed afterwards) so that narrow warp slices do not
@@ -346,6 +425,15 @@ __device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView&
                 for (int kg = 1; kg < KG; kg++) acc += sg[kg][n][c];
                 s[n][c] = acc;
             }
+        if (partial) {
+            // column c of 8-token tile n is token tok0 + 8n + 2*quad + (c & 1)
+#pragma unroll
+            for (int n = 0; n < NT_S; n++) {
+                const int t = tok0 + 8 * n + 2 * quad;
+                if (t >= nt) { s[n][0] = NEG_BIG; s[n][2] = NEG_BIG; }
+                if (t + 1 >= nt) { s[n][1] = NEG_BIG; s[n][3] = NEG_BIG; }
+            }
+        }
 
         // online softmax in log2 units; a thread holds rows r_lo (c0, c1) and r_hi (c2, c3)
         float mx_lo = NEG_BIG, mx_hi = NEG_BIG;
@@ -355,11 +443,12 @@ __device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView&
             mx_hi = fmaxf(mx_hi, fmaxf(s[n][2], s[n][3]));
         }
         mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
-        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
         mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
         mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-        const float mn_lo = fmaxf(m_lo, mx_lo * p.scale_log2);
-        const float mn_hi = fmaxf(m_hi, mx_hi * p.scale_log2);
+        // a warp whose tokens are all absent keeps its state (masked scores must not set the maximum)
+        const float mn_lo = fmaxf(m_lo, mx_lo > 0.5f * NEG_BIG ? mx_lo * p.scale_log2 : NEG_BIG);
+        const float mn_hi = fmaxf(m_hi, mx_hi > 0.5f * NEG_BIG ? mx_hi * p.scale_log2 : NEG_BIG);
         const float a_lo = fast_exp2(m_lo - mn_lo);
         const float a_hi = fast_exp2(m_hi - mn_hi);
         m_lo = mn_lo;
@@ -368,10 +457,15 @@ __device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView&
         uint32_t pa[TW / 16][4];
 #pragma unroll
         for (int n = 0; n < NT_S; n++) {
-            const float p0 = fast_exp2(fmaf(s[n][0], p.scale_log2, -mn_lo));
-            const float p1 = fast_exp2(fmaf(s[n][1], p.scale_log2, -mn_lo));
-            const float p2 = fast_exp2(fmaf(s[n][2], p.scale_log2, -mn_hi));
-            const float p3 = fast_exp2(fmaf(s[n][3], p.scale_log2, -mn_hi));
+            float p0 = fast_exp2(fmaf(s[n][0], p.scale_log2, -mn_lo));
+            float p1 = fast_exp2(fmaf(s[n][1], p.scale_log2, -mn_lo));
+            float p2 = fast_exp2(fmaf(s[n][2], p.scale_log2, -mn_hi));
+            float p3 = fast_exp2(fmaf(s[n][3], p.scale_log2, -mn_hi));
+            if (partial) {
+                const int t = tok0 + 8 * n + 2 * quad;
+                if (t >= nt) { p0 = 0.f; p2 = 0.f; }
+                if (t + 1 >= nt) { p1 = 0.f; p3 = 0.f; }
+            }
             sum_lo += p0 + p1;
             sum_hi += p2 + p3;
             // the accumulator layout of two adjacent 8-token tiles is the A layout of one k-step
@@ -401,14 +495,34 @@ __device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView&
                 mma_16816(o[2 * dp + 1], pa[kk], b2, b3);
             }
         }
+        if (partial) fence_proxy_async();
         consumer_release(rg, lane);
     }
 
     // the four lanes of a quad hold partial sums of the same two rows
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
-    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    if (STAGED_Q && it.n_rows == 1) {
+        if (!have_q) {
+            // the item held no token at all (an empty reserved tail): mark its partial as empty
+            if (warp == 0 && lane == 0) p.part_ml[it.slot_base] = make_float2(NEG_BIG, 0.f);
+            return true;
+        }
+        // row 0 lives in the first quad: lane q holds outputs 8n + 2q, 8n + 2q + 1
+        float* mine = scratch + ((row_items & 1) * NUM_CONSUMER_WARPS + warp) * SCRATCH_FLOATS_PER_WARP;
+        if (lane == 0) {
+            mine[0] = m_lo;
+            mine[1] = l_lo;
+        }
+        if (lane < 4) {
+#pragma unroll
+            for (int n = 0; n < 16; n++)
+                *reinterpret_cast<float2*>(mine + 4 + 8 * n + 2 * quad) = make_float2(o[n][0], o[n][1]);
+        }
+        return combine_row_and_store(p, it, scratch, merge_bar, row_items, warp, lane, rg);
+    }
     const int slot0 = it.slot_base + split * it.n_rows;
     if (v_lo) {
         float* dst = p.part_o + (size_t)(slot0 + r_lo) * FAST_D + 2 * quad;
@@ -425,269 +539,15 @@ __device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView&
     return true;
 }
 
-// Combine the 8 warps' (max, sum, O[128]) of a ONE-row item and write its single partial.  Every
-// warp has stored its state in its slot of the double-buffered scratch (buffer = item parity);
-// one mbarrier phase per such item orders the stores before the loads, and because every warp
-// waits for the phase, a warp can be at most one item ahead, so two buffers suffice.
-__device__ __forceinline__ bool combine_row_and_store(const PartialParams& p, const ItemView& it, float* scratch,
-                                                      uint32_t merge_bar, uint32_t& simt_count, int warp, int lane,
-                                                      Ring& rg) {
-    const long long t0 = rg.timed ? clock64() : 0;
-    __syncwarp();
-    if (lane == 0) mbar_arrive(merge_bar);
-    bool ok = mbar_wait_bounded(merge_bar, simt_count & 1);
-    ok = __all_sync(0xffffffffu, ok);
-    if (!ok) return false;
-    if (warp < 4) {
-        const float* base = scratch + (simt_count & 1) * NUM_CONSUMER_WARPS * SCRATCH_FLOATS_PER_WARP;
-        const int d = warp * 32 + lane;
-        float mm = NEG_BIG;
-#pragma unroll
-        for (int w = 0; w < NUM_CONSUMER_WARPS; w++) mm = fmaxf(mm, base[w * SCRATCH_FLOATS_PER_WARP]);
-        float ll = 0.f, od = 0.f;
-#pragma unroll
-        for (int w = 0; w < NUM_CONSUMER_WARPS; w++) {
-            const float wl = base[w * SCRATCH_FLOATS_PER_WARP + 1];
-            // a warp that saw no token keeps l = 0 and contributes nothing whatever its weight
-            const float wgt = fast_exp2(base[w * SCRATCH_FLOATS_PER_WARP] - mm);
-            ll = fmaf(wgt, wl, ll);
-            od = fmaf(wgt, base[w * SCRATCH_FLOATS_PER_WARP + 4 + d], od);
-        }
-        p.part_o[(size_t)it.slot_base * FAST_D + d] = od;
-        if (d == 0) p.part_ml[it.slot_base] = make_float2(mm, ll);
-    }
-    simt_count++;
-    if (rg.timed) rg.tail_cycles += clock64() - t0;
-    return true;
-}
-
-// Tensor-core item of up to 16 rows, 8 token splits: warp w owns tokens 8w..8w+7 of every tile, and
-// walks the tiles two at a time (see the loop).  This is how a sequence's private tail (ONE row)
-// is walked when the tensor-core sequence-first mode is selected: 15 of the 16 MMA rows are idle, but
-// the walk needs about a third of the instructions of the CUDA-core version, which matters because
-// with one 200 KiB CTA per SM only 8 warps are there to hide latency.  A partially filled tail tile
-// is handled by masking the scores of absent tokens and zeroing their V rows in the staged copy.
-// A one-row item combines its 8 warps through shared memory and writes one partial; wider items
-// write one partial per warp.
-__device__ __forceinline__ bool mma8_item(const PartialParams& p, const ItemView& it, Ring& rg, float* scratch,
-                                          uint32_t merge_bar, uint32_t& simt_count, int warp, int lane) {
-    long long tseg = rg.timed ? clock64() : 0;
-    const int tok0 = warp * 8;
-    const int quad = lane & 3;
-    const int r_lo = lane >> 2;
-    const int r_hi = r_lo + 8;
-    const bool v_lo = r_lo < it.n_rows;
-    const bool v_hi = r_hi < it.n_rows;
-
-    uint32_t qa[8][4];
-    bool have_q = false;
-    float o[16][4];
-#pragma unroll
-    for (int n = 0; n < 16; n++) {
-        o[n][0] = 0.f; o[n][1] = 0.f; o[n][2] = 0.f; o[n][3] = 0.f;
-    }
-    float m_lo = NEG_BIG, m_hi = NEG_BIG, l_lo = 0.f, l_hi = 0.f;
-
-    // This warp's 8 token rows of a tile; ldmatrix lane roles are set per use below.
-    const int row_t = tok0 + (lane & 7);
-    const uint32_t row_off = row_t * (FAST_D * 2);
-    const int sw = row_t & 7;
-    const int mi = lane >> 3;        // which of the four 8x8 matrices of an ldmatrix.x4 this lane addresses
-    const int t0 = tok0 + 2 * quad;  // token of accumulator columns c0/c2; c1/c3 are the next token
-
-    // Tiles are walked in PAIRS (A, B): the warp's 8 tokens of A and its 8 tokens of B form one
-    // 16-token block, so the softmax runs once per pair and P V uses full k = 16 MMAs whose B
-    // operand takes its first 8 token rows from A's stage and the other 8 from B's stage.  Two
-    // tiles per latency chain is what lets 8 warps keep up with the copy engine.
-    int j = 0;
-    while (j < it.n_tiles) {
-        const int nt_a = tile_tokens(it, j, p.delta_tokens);
-        if (nt_a == 0) {  // an empty tail (always the last tile): it occupies no stage
-            j++;
-            continue;
-        }
-        int nt_b = (j + 1 < it.n_tiles) ? tile_tokens(it, j + 1, p.delta_tokens) : 0;
-        const bool two = nt_b > 0;
-        j += 2;  // a second tile that is an empty tail is skipped with the pair
-
-        if (rg.timed) { const long long t = clock64(); rg.seg[0] += t - tseg; tseg = t; }
-        if (!consumer_wait_full(rg)) return false;
-        const uint32_t stage_a = rg.stage;
-        const uint32_t ka = rg.ring + stage_a * FAST_STAGE_BYTES;
-        const uint32_t va = ka + FAST_TILE_BYTES;
-        if (!have_q) {
-            const long long tq = rg.timed ? clock64() : 0;
-            // The producer staged this item's query rows next to its first non-empty tile, in the
-            // slot of that tile's stage; they arrived with it.  Copy them to registers as the A
-            // fragments of the 8 k-steps before this stage is released.
-            const uint32_t qrow = rg.qslots + stage_a * QSLOT_BYTES + ((lane & 7) + (mi & 1) * 8) * QSLOT_PITCH + (mi >> 1) * 16;
-#pragma unroll
-            for (int ks = 0; ks < 8; ks++) {
-                ldsm_x4(qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], qrow + ks * 32);
-                // rows past the item hold stale bytes: make them exact zeros
-                if (!v_lo) { qa[ks][0] = 0u; qa[ks][2] = 0u; }
-                if (!v_hi) { qa[ks][1] = 0u; qa[ks][3] = 0u; }
-            }
-            have_q = true;
-            if (rg.timed) rg.seg[4] += clock64() + (long long)(qa[7][3] & 0u) - tq;
-        }
-        uint32_t stage_b = stage_a, kb = ka, vb = va;  // without a second tile B aliases A (and is masked)
-        if (two) {
-            rg.advance();
-            if (!consumer_wait_full(rg)) return false;
-            stage_b = rg.stage;
-            kb = rg.ring + stage_b * FAST_STAGE_BYTES;
-            vb = kb + FAST_TILE_BYTES;
-        }
-        if (rg.timed) tseg = clock64();
-        // only the last tile of an item can be partially filled: A when it stands alone, else B
-        const int nt_last = two ? nt_b : nt_a;
-        const uint32_t v_last = two ? vb : va;
-        const bool partial = tok0 + 8 > nt_last;
-        if (partial) {
-            // Absent tokens: the bulk copy did not fill their rows, so they hold stale bytes.  Their
-            // scores are masked below; their V rows are zeroed here because 0 * NaN is NaN.
-            const int first_absent = nt_last > tok0 ? nt_last : tok0;
-            for (int idx = lane; idx < (tok0 + 8 - first_absent) * 16; idx += 32)
-                sts128_zero(v_last + (first_absent + (idx >> 4)) * (FAST_D * 2) + ((idx & 15) << 4));
-            __syncwarp();
-        }
-
-        // S for the 8 tokens of A and the 8 tokens of B: two accumulators each (even / odd k-steps)
-        float sa[2][4], sb[2][4];
-#pragma unroll
-        for (int e = 0; e < 2; e++) {
-            sa[e][0] = 0.f; sa[e][1] = 0.f; sa[e][2] = 0.f; sa[e][3] = 0.f;
-            sb[e][0] = 0.f; sb[e][1] = 0.f; sb[e][2] = 0.f; sb[e][3] = 0.f;
-        }
-#pragma unroll
-        for (int k2 = 0; k2 < 4; k2++) {
-            // four consecutive granules of the 8 token rows = the B fragments of two k-steps
-            const uint32_t goff = row_off + (((4 * k2 + mi) ^ sw) << 4);
-            uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
-            ldsm_x4(a0, a1, a2, a3, ka + goff);
-            ldsm_x4(b0, b1, b2, b3, kb + goff);
-            mma_16816(sa[0], qa[2 * k2], a0, a1);
-            mma_16816(sb[0], qa[2 * k2], b0, b1);
-            mma_16816(sa[1], qa[2 * k2 + 1], a2, a3);
-            mma_16816(sb[1], qa[2 * k2 + 1], b2, b3);
-        }
-        float s[8];  // [0..3] tile A (c0..c3), [4..7] tile B
-#pragma unroll
-        for (int c = 0; c < 4; c++) {
-            s[c] = sa[0][c] + sa[1][c];
-            s[4 + c] = sb[0][c] + sb[1][c];
-        }
-        const bool in_a0 = t0 < nt_a, in_a1 = t0 + 1 < nt_a;
-        const bool in_b0 = two && t0 < nt_b, in_b1 = two && t0 + 1 < nt_b;
-        if (!in_a0) { s[0] = NEG_BIG; s[2] = NEG_BIG; }
-        if (!in_a1) { s[1] = NEG_BIG; s[3] = NEG_BIG; }
-        if (!in_b0) { s[4] = NEG_BIG; s[6] = NEG_BIG; }
-        if (!in_b1) { s[5] = NEG_BIG; s[7] = NEG_BIG; }
-        float mx_lo = fmaxf(fmaxf(s[0], s[1]), fmaxf(s[4], s[5]));
-        float mx_hi = fmaxf(fmaxf(s[2], s[3]), fmaxf(s[6], s[7]));
-        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
-        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
-        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
-        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-        // a warp whose 16 tokens are all absent keeps its state: NEG_BIG scores would otherwise win
-        const float mn_lo = fmaxf(m_lo, mx_lo > 0.5f * NEG_BIG ? mx_lo * p.scale_log2 : NEG_BIG);
-        const float mn_hi = fmaxf(m_hi, mx_hi > 0.5f * NEG_BIG ? mx_hi * p.scale_log2 : NEG_BIG);
-        const float a_lo = fast_exp2(m_lo - mn_lo);
-        const float a_hi = fast_exp2(m_hi - mn_hi);
-        m_lo = mn_lo;
-        m_hi = mn_hi;
-        float pr[8];
-        pr[0] = in_a0 ? fast_exp2(fmaf(s[0], p.scale_log2, -mn_lo)) : 0.f;
-        pr[1] = in_a1 ? fast_exp2(fmaf(s[1], p.scale_log2, -mn_lo)) : 0.f;
-        pr[2] = in_a0 ? fast_exp2(fmaf(s[2], p.scale_log2, -mn_hi)) : 0.f;
-        pr[3] = in_a1 ? fast_exp2(fmaf(s[3], p.scale_log2, -mn_hi)) : 0.f;
-        pr[4] = in_b0 ? fast_exp2(fmaf(s[4], p.scale_log2, -mn_lo)) : 0.f;
-        pr[5] = in_b1 ? fast_exp2(fmaf(s[5], p.scale_log2, -mn_lo)) : 0.f;
-        pr[6] = in_b0 ? fast_exp2(fmaf(s[6], p.scale_log2, -mn_hi)) : 0.f;
-        pr[7] = in_b1 ? fast_exp2(fmaf(s[7], p.scale_log2, -mn_hi)) : 0.f;
-        l_lo = l_lo * a_lo + ((pr[0] + pr[1]) + (pr[4] + pr[5]));
-        l_hi = l_hi * a_hi + ((pr[2] + pr[3]) + (pr[6] + pr[7]));
-        // once the running maxima have settled the factors are exactly 1: skip the 64 multiplies
-        if (__any_sync(0xffffffffu, a_lo != 1.f || a_hi != 1.f)) {
-#pragma unroll
-            for (int n = 0; n < 16; n++) {
-                o[n][0] *= a_lo; o[n][1] *= a_lo; o[n][2] *= a_hi; o[n][3] *= a_hi;
-            }
-        }
-        // P as the A operand of a k = 16 step: k 0..7 are A's tokens, k 8..15 are B's tokens
-        uint32_t pa[4];
-        pa[0] = pack_half2(pr[0], pr[1]);
-        pa[1] = pack_half2(pr[2], pr[3]);
-        pa[2] = pack_half2(pr[4], pr[5]);
-        pa[3] = pack_half2(pr[6], pr[7]);
-        if (rg.timed) { const long long t = clock64() + (long long)(pa[0] & 0u); rg.seg[1] += t - tseg; tseg = t; }
-        // V: matrices 0 / 2 come from A's stage, 1 / 3 from B's stage; 0 / 1 are granule 2dp, 2 / 3 the next
-        const uint32_t vrow = ((mi & 1) ? vb : va) + row_off;
-#pragma unroll
-        for (int dp = 0; dp < 8; dp++) {
-            uint32_t b0, b1, b2, b3;
-            ldsm_x4_trans(b0, b1, b2, b3, vrow + (((2 * dp + (mi >> 1)) ^ sw) << 4));
-            mma_16816(o[2 * dp], pa, b0, b1);
-            mma_16816(o[2 * dp + 1], pa, b2, b3);
-        }
-        if (partial) fence_proxy_async();
-        // hand both stages back
-        __syncwarp();
-        if (lane == 0) {
-            mbar_arrive(rg.empty_bar + 8 * stage_a);
-            if (two) mbar_arrive(rg.empty_bar + 8 * stage_b);
-        }
-        rg.advance();
-        if (rg.timed) { const long long t = clock64(); rg.seg[2] += t - tseg; tseg = t; }
-    }
-
-    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
-    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
-    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
-    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
-    if (it.n_rows == 1 && !have_q) {
-        // the item held no token at all (an empty reserved tail): mark its partial as empty
-        if (warp == 0 && lane == 0) p.part_ml[it.slot_base] = make_float2(NEG_BIG, 0.f);
-        return true;
-    }
-    if (it.n_rows == 1) {
-        // row 0 lives in the first quad: lane q holds outputs 8n + 2q, 8n + 2q + 1
-        float* mine = scratch + ((simt_count & 1) * NUM_CONSUMER_WARPS + warp) * SCRATCH_FLOATS_PER_WARP;
-        if (lane == 0) {
-            mine[0] = m_lo;
-            mine[1] = l_lo;
-        }
-        if (lane < 4) {
-#pragma unroll
-            for (int n = 0; n < 16; n++)
-                *reinterpret_cast<float2*>(mine + 4 + 8 * n + 2 * quad) = make_float2(o[n][0], o[n][1]);
-        }
-        if (rg.timed) rg.seg[3] += clock64() - tseg;
-        return combine_row_and_store(p, it, scratch, merge_bar, simt_count, warp, lane, rg);
-    }
-    const int slot0 = it.slot_base + warp * it.n_rows;
-    if (v_lo) {
-        float* dst = p.part_o + (size_t)(slot0 + r_lo) * FAST_D + 2 * quad;
-#pragma unroll
-        for (int n = 0; n < 16; n++) *reinterpret_cast<float2*>(dst + 8 * n) = make_float2(o[n][0], o[n][1]);
-        if (quad == 0) p.part_ml[slot0 + r_lo] = make_float2(m_lo, l_lo);
-    }
-    if (v_hi) {
-        float* dst = p.part_o + (size_t)(slot0 + r_hi) * FAST_D + 2 * quad;
-#pragma unroll
-        for (int n = 0; n < 16; n++) *reinterpret_cast<float2*>(dst + 8 * n) = make_float2(o[n][2], o[n][3]);
-        if (quad == 0) p.part_ml[slot0 + r_hi] = make_float2(m_hi, l_hi);
-    }
-    return true;
-}
-
-// Sequence-first item on CUDA cores.  Warp w owns tokens 8w..8w+7 of every tile; a half-warp reads
-// one 256-byte token row per 128-bit load (lane = granule), so K rows are dotted against q held in
-// registers and V rows are accumulated into 8 output elements per lane.  The 8 warps' states are
-// combined through shared memory at the end of the item and one partial is written.
+// Sequence-first item on CUDA cores (selectable alternative to the tensor-core walk).  Warp w owns
+// tokens 16w..16w+15 of every tile; a half-warp reads one 256-byte token row per 128-bit load
+// (lane = granule), so K rows are dotted against q held in registers and V rows are accumulated
+// into 8 output elements per lane.  The warps' states are combined through shared memory at the
+// end of the item and one partial is written.
 __device__ __forceinline__ bool simt_item(const PartialParams& p, const ItemView& it, Ring& rg, float* scratch,
-                          uint32_t merge_bar, uint32_t& simt_count, int warp, int lane) {
+                                          uint32_t merge_bar, uint32_t& row_items, int warp, int lane) {
+    constexpr int TPW = FAST_C / NUM_CONSUMER_WARPS;  // tokens per warp per tile
+    constexpr int NJ = TPW / 2;                       // a warp reads two token rows per load
     const int g = lane & 15;
     const int half = lane >> 4;
     float qf[8];
@@ -712,13 +572,13 @@ __device__ __forceinline__ bool simt_item(const PartialParams& p, const ItemView
         const int nt = tile_tokens(it, j, p.delta_tokens);
         if (nt == 0) continue;
         if (!consumer_wait_full(rg)) return false;
-        if (warp * 8 < nt) {
+        if (warp * TPW < nt) {
             const uint32_t kt = rg.ring + rg.stage * FAST_STAGE_BYTES;
             const uint32_t vt = kt + FAST_TILE_BYTES;
-            float s[4];
+            float s[NJ];
 #pragma unroll
-            for (int jj = 0; jj < 4; jj++) {
-                const int t = warp * 8 + 2 * jj + half;
+            for (int jj = 0; jj < NJ; jj++) {
+                const int t = warp * TPW + 2 * jj + half;
                 float acc = 0.f;
                 if (t < nt) {
                     const uint4 raw = lds128(kt + t * (FAST_D * 2) + ((g ^ (t & 7)) << 4));
@@ -736,12 +596,12 @@ __device__ __forceinline__ bool simt_item(const PartialParams& p, const ItemView
 #pragma unroll
             for (int off = 8; off >= 1; off >>= 1) {
 #pragma unroll
-                for (int jj = 0; jj < 4; jj++) s[jj] += __shfl_xor_sync(0xffffffffu, s[jj], off);
+                for (int jj = 0; jj < NJ; jj++) s[jj] += __shfl_xor_sync(0xffffffffu, s[jj], off);
             }
             float mx = NEG_BIG;
 #pragma unroll
-            for (int jj = 0; jj < 4; jj++) {
-                const int t = warp * 8 + 2 * jj + half;
+            for (int jj = 0; jj < NJ; jj++) {
+                const int t = warp * TPW + 2 * jj + half;
                 if (t < nt) mx = fmaxf(mx, s[jj]);
             }
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
@@ -752,8 +612,8 @@ __device__ __forceinline__ bool simt_item(const PartialParams& p, const ItemView
 #pragma unroll
             for (int i = 0; i < 8; i++) o[i] *= alpha;
 #pragma unroll
-            for (int jj = 0; jj < 4; jj++) {
-                const int t = warp * 8 + 2 * jj + half;
+            for (int jj = 0; jj < NJ; jj++) {
+                const int t = warp * TPW + 2 * jj + half;
                 if (t < nt) {
                     const float pj = fast_exp2(s[jj] - mn);
                     l += pj;
@@ -777,7 +637,7 @@ __device__ __forceinline__ bool simt_item(const PartialParams& p, const ItemView
     for (int i = 0; i < 8; i++) o[i] += __shfl_xor_sync(0xffffffffu, o[i], 16);
 
     // lanes 0..15 of a warp hold the warp's 128 outputs, 8 each
-    float* mine = scratch + ((simt_count & 1) * NUM_CONSUMER_WARPS + warp) * SCRATCH_FLOATS_PER_WARP;
+    float* mine = scratch + ((row_items & 1) * NUM_CONSUMER_WARPS + warp) * SCRATCH_FLOATS_PER_WARP;
     if (lane == 0) {
         mine[0] = m;
         mine[1] = l;
@@ -786,10 +646,10 @@ __device__ __forceinline__ bool simt_item(const PartialParams& p, const ItemView
         *reinterpret_cast<float4*>(mine + 4 + 8 * g) = make_float4(o[0], o[1], o[2], o[3]);
         *reinterpret_cast<float4*>(mine + 8 + 8 * g) = make_float4(o[4], o[5], o[6], o[7]);
     }
-    return combine_row_and_store(p, it, scratch, merge_bar, simt_count, warp, lane, rg);
+    return combine_row_and_store(p, it, scratch, merge_bar, row_items, warp, lane, rg);
 }
 
-__global__ void __launch_bounds__(NUM_THREADS, 1) attn_partial_kernel(const PartialParams p) {
+__global__ void __launch_bounds__(NUM_THREADS, 2) attn_partial_kernel(const PartialParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     float* scratch = reinterpret_cast<float*>(smem + SMEM_SCRATCH_OFFSET);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_BAR_OFFSET);
@@ -804,7 +664,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_partial_kernel(const Part
     rg.timed = p.trace != nullptr;
     rg.wait_cycles = 0;
     rg.tail_cycles = 0;
-    rg.seg[0] = rg.seg[1] = rg.seg[2] = rg.seg[3] = rg.seg[4] = rg.seg[5] = 0;
     const long long t_begin = rg.timed ? clock64() : 0;
     const uint32_t merge_bar = smem_u32(bars + 2 * NUM_STAGES);
 
@@ -827,53 +686,47 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_partial_kernel(const Part
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
-    if (p.trace && threadIdx.x == 0) p.trace[16 * blockIdx.x + 0] = global_timer_ns();
+    if (p.trace && threadIdx.x == 0) p.trace[8 * blockIdx.x + 0] = global_timer_ns();
     if (warp >= NUM_CONSUMER_WARPS) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PRODUCER_REGS));
         if (warp == NUM_CONSUMER_WARPS) {
             producer_loop(p, rg, item_begin, item_end, lane);
             if (p.trace && lane == 0) {
-                p.trace[16 * blockIdx.x + 1] = global_timer_ns();
-                p.trace[16 * blockIdx.x + 6] = (unsigned long long)rg.wait_cycles;
+                p.trace[8 * blockIdx.x + 1] = global_timer_ns();
+                p.trace[8 * blockIdx.x + 6] = (unsigned long long)rg.wait_cycles;
             }
         }
         return;
     }
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(CONSUMER_REGS));
 
-    uint32_t simt_count = 0;
+    uint32_t row_items = 0;  // one-row items finished so far (scratch buffer and merge-barrier parity)
     ItemView next = item_begin < item_end ? load_item(p.items, item_begin) : ItemView{};
-    long long t_between = rg.timed ? clock64() : 0;
     for (int i = item_begin; i < item_end; i++) {
         const ItemView it = next;
         if (i + 1 < item_end) next = load_item(p.items, i + 1);  // in flight while this item is walked
         const int splits = it.flags >> ITEM_SPLITS_SHIFT;
-        if (rg.timed) rg.seg[5] += clock64() - t_between;
         bool ok;
-        if (splits == 0) {
-            ok = simt_item(p, it, rg, scratch, merge_bar, simt_count, warp, lane);
-        } else if (splits == 8) {
-            ok = mma8_item(p, it, rg, scratch, merge_bar, simt_count, warp, lane);
-        } else if (splits == 4) {
-            ok = mma_item<4>(p, it, rg, warp, lane);
+        if (splits == 4) {
+            ok = mma_item<4>(p, it, rg, scratch, merge_bar, row_items, warp, lane);
+        } else if (splits == 0) {
+            ok = simt_item(p, it, rg, scratch, merge_bar, row_items, warp, lane);
         } else if (splits == 2) {
-            ok = mma_item<2>(p, it, rg, warp, lane);
+            ok = mma_item<2>(p, it, rg, scratch, merge_bar, row_items, warp, lane);
         } else {
-            ok = mma_item<1>(p, it, rg, warp, lane);
+            ok = mma_item<1>(p, it, rg, scratch, merge_bar, row_items, warp, lane);
         }
         if (!ok) {
             if (lane == 0) report(p.status, STATUS_FULL_WAIT_TIMEOUT);
             break;
         }
-        if (rg.timed) t_between = clock64();
     }
     if (p.trace && lane == 0 && (warp == 0 || warp == NUM_CONSUMER_WARPS - 1)) {
-        p.trace[16 * blockIdx.x + (warp == 0 ? 2 : 3)] = global_timer_ns();
+        p.trace[8 * blockIdx.x + (warp == 0 ? 2 : 3)] = global_timer_ns();
         if (warp == 0) {
-            p.trace[16 * blockIdx.x + 4] = (unsigned long long)rg.wait_cycles;
-            p.trace[16 * blockIdx.x + 5] = (unsigned long long)rg.tail_cycles;
-            p.trace[16 * blockIdx.x + 7] = (unsigned long long)(clock64() - t_begin);
-            for (int k = 0; k < 6; k++) p.trace[16 * blockIdx.x + 8 + k] = (unsigned long long)rg.seg[k];
+            p.trace[8 * blockIdx.x + 4] = (unsigned long long)rg.wait_cycles;
+            p.trace[8 * blockIdx.x + 5] = (unsigned long long)rg.tail_cycles;
+            p.trace[8 * blockIdx.x + 7] = (unsigned long long)(clock64() - t_begin);
         }
     }
 }
@@ -916,7 +769,10 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeParams p) {
 
 cudaError_t configure_fast_kernels() {
     // opt in to the large dynamic shared-memory carve-out, once per device (per context creation)
-    return cudaFuncSetAttribute(attn_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(attn_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(attn_partial_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                cudaSharedmemCarveoutMaxShared);
 }
 
 cudaError_t launch_attn_partials(const PartialParams& p, int n_ctas, cudaStream_t stream) {

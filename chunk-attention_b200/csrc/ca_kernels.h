@@ -22,6 +22,9 @@ constexpr int FAST_D = 128;
 constexpr int FAST_C = 64;
 constexpr int FAST_TILE_BYTES = FAST_C * FAST_D * 2;  // one K or V tile
 constexpr int FAST_STAGE_BYTES = 2 * FAST_TILE_BYTES; // K tile + V tile of one (chunk, head)
+constexpr int FAST_CONSUMER_WARPS = 4;                // warps of a CTA that walk tiles
+constexpr int FAST_CTAS_PER_SM = 2;                   // persistent CTAs resident per SM
+constexpr int FAST_MAX_ROWS_PER_ITEM = 16 * FAST_CONSUMER_WARPS;  // query rows one item can serve
 
 struct PartialParams {
     const uint8_t* pool;         // chunk pool base
@@ -40,8 +43,8 @@ struct PartialParams {
                                  // tiles, warp 0 combining/storing partials, producer waiting for free stages, warp 0 total
 };
 
-// Persistent kernel: chunk-first items on tensor cores and sequence-first items on CUDA cores,
-// both fed by one TMA ring.  grid = n_ctas.
+// Persistent kernel: chunk-first and sequence-first items, both fed by one TMA ring per CTA.
+// grid = n_ctas (FAST_CTAS_PER_SM per SM).
 cudaError_t launch_attn_partials(const PartialParams& p, int n_ctas, cudaStream_t stream);
 cudaError_t configure_fast_kernels();  // once per device before the first launch
 

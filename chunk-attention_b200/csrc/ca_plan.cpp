@@ -18,7 +18,7 @@ struct Unit {
 // paid for by its HBM bytes alone (weight 1); wider row blocks issue proportionally more MMAs
 // per byte and become tensor-pipe bound.
 double chunk_first_tile_weight(int splits) {
-    return splits >= 4 ? 1.08 : (splits == 2 ? 1.5 : 2.8);
+    return splits >= 4 ? 1.05 : (splits == 2 ? 1.3 : 2.0);
 }
 // partial rows an item emits: a one-row item combines its warps on chip and writes one row, a
 // wider item writes one row per (token split, query row)
@@ -206,7 +206,7 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
             const int rb = r.b + blk * rows_per_block;
             const int rows = std::min(rows_per_block, r.e - rb);
             if (rows <= 0) continue;
-            const int splits = rows <= 16 ? 8 : (rows <= 32 ? 4 : (rows <= 64 ? 2 : 1));
+            const int splits = rows <= 16 ? 4 : (rows <= 32 ? 2 : 1);
             for (int h = 0; h < n_heads; h++)
                 units.push_back(Unit{r.tile_begin, (int32_t)r.chunks.size(), h, rb, rows, splits,
                                      chunk_size, false, chunk_first_tile_weight(splits)});
@@ -223,7 +223,7 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
             if (!shared[path_info[p]] && plan.path_tokens[p] != chunk_size)
                 return fmt("row %ld has a partially filled chunk that is not its tail", s);
         for (int h = 0; h < n_heads; h++)
-            units.push_back(Unit{tb, nt, h, s, 1, seq_first_tensor ? 8 : 0, plan.tail_tokens[s], true, 1.0});
+            units.push_back(Unit{tb, nt, h, s, 1, seq_first_tensor ? 4 : 0, plan.tail_tokens[s], true, 1.0});
     }
 
     // ---- cut into items, schedules ----------------------------------------------------------------------

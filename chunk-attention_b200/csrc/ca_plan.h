@@ -27,9 +27,9 @@
 namespace ca {
 
 constexpr int ITEM_FLAG_TAIL = 1;     // last tile of the item is the sequence's tail chunk
-constexpr int ITEM_SPLITS_SHIFT = 8;  // flags >> 8: token splits of a tensor-core item (8, 4, 2, 1);
+constexpr int ITEM_SPLITS_SHIFT = 8;  // flags >> 8: token splits of a tensor-core item (4, 2, 1);
                                       // 0 = one-row item walked on CUDA cores
-constexpr int MAX_ROWS_PER_ITEM = 128;
+constexpr int MAX_ROWS_PER_ITEM = 64; // 4 consumer warps x 16 rows
 
 struct PlanItem {
     int32_t tile_begin;   // index into tile_chunks

@@ -87,9 +87,9 @@ CA_API void ca_context_destroy(ca_context* ctx);
 /* 0: one launch walks shared runs and private tails together (default);
  * 1: the chunk-first items and the sequence-first items are launched as two kernels. */
 #define CA_OPT_SPLIT_PHASES 1
-/* number of persistent CTAs; 0 = one per SM */
+/* number of persistent CTAs; 0 = two per SM */
 #define CA_OPT_NUM_CTAS 2
-/* how a sequence's private tail (one query row) is walked: 1 (default) on tensor cores, 8 tokens
+/* how a sequence's private tail (one query row) is walked: 1 (default) on tensor cores, 16 tokens
  * per warp; 0 on CUDA cores with 128-bit shared-memory loads and warp-shuffle reductions */
 #define CA_OPT_SEQ_FIRST_TENSOR 3
 /* 1: the attention kernel records per-CTA nanosecond timestamps, read with ca_context_read_trace */

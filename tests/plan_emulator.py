@@ -49,7 +49,7 @@ def emulate(plan, kv_of_chunk, q, chunk_size, delta=0, schedule="fused"):
             ks.append((K[head], nt))
             vs.append(V[head])
         if n_rows == 1:
-            assert splits in (0, 8)
+            assert splits in (0, 4)
             groups = [(slot_base, [(0, chunk_size)])]  # warps combined on chip: one slot, all tokens
         else:
             tw = chunk_size // splits

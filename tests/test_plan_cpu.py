@@ -60,7 +60,7 @@ def shared_spec(n_seqs, shared, unique, base=0):
 def test_single_level_prefix(n_ctas, split, tensor_tails):
     ora = build_tree(shared_spec(6, 5 * C, 2 * C + 17))
     plan, loads = check(ora, 2, 8, n_ctas=n_ctas, split_phases=split, seq_first_tensor=tensor_tails)
-    assert sorted(set(int(f) >> 8 for f in plan.items()[:, 6])) == ([8] if tensor_tails else [0, 8])
+    assert sorted(set(int(f) >> 8 for f in plan.items()[:, 6])) == ([4] if tensor_tails else [0, 4])
     st = plan.stats()
     assert st["n_shared_chunks"] == 5 and st["n_runs"] == 1
     assert st["n_chunks"] == 5 + 6 * 3
@@ -73,10 +73,10 @@ def test_partial_tails_and_empty_tails():
 
 
 def test_two_level_tree_and_row_blocks():
-    # 3 groups under a root prefix; group sizes 2, 33 and 70 exercise the 4-, 2- and 1-split items
+    # 3 groups under a root prefix; group sizes 2, 20 and 70 exercise the 4-, 2- and 1-split items
     spec = []
     root = list(range(2 * C))
-    for g, n in enumerate((2, 33, 70)):
+    for g, n in enumerate((2, 20, 70)):
         gp = [10_000 * (g + 1) + j for j in range(C)]
         for s in range(n):
             spec.append(root + gp + [1_000_000 * (len(spec) + 1) + j for j in range(9)])
@@ -84,7 +84,7 @@ def test_two_level_tree_and_row_blocks():
     plan, _ = check(ora, 1, 4, n_ctas=20)
     items = plan.items()
     splits = sorted(set(int(f) >> 8 for f in items[:, 6]))
-    assert splits == [1, 2, 8]  # 70 rows -> 1 split, 33 -> 2, 2 rows and every private tail -> 8
+    assert splits == [1, 2, 4]  # 92 and 70 rows -> blocks of <= 64 rows, 1 split; 20 -> 2; 2 rows and tails -> 4
     assert plan.stats()["n_runs"] == 4
 
 
@@ -92,7 +92,7 @@ def test_more_than_128_sharers_splits_rows():
     ora = build_tree(shared_spec(150, C, 3), H=1, d=4)
     plan, _ = check(ora, 1, 4, n_ctas=8)
     rows = [int(r) for r in plan.items()[:, 4] if r > 1]
-    assert max(rows) <= 128 and sum(sorted(set(rows))) >= 150 - 1 or len(set(rows)) >= 1
+    assert max(rows) <= 64
 
 
 def test_no_sharing_and_full_sharing():
@@ -147,7 +147,7 @@ def test_random_traces(seed):
             ora.append_token(arg, k, v)
         if not ora.tails:
             continue
-        # the planner is geometry-agnostic: exercise it with chunk_size 8 (8 splits of 1 token)
+        # the planner is geometry-agnostic: exercise it with chunk_size 8 (4 splits of 2 tokens)
         check(ora, 2, 4, n_ctas=1 + seed, split_phases=bool(seed & 1))
 
 
@@ -161,12 +161,12 @@ def test_balance_config2_shape():
         for _ in range(8):
             infos.append((cid, C, s, s + 1)); cid += 1
         infos.append((cid, 0, s, s + 1)); cid += 1
-    plan = cabi.Plan(infos, 32, 32, n_ctas=148)
+    plan = cabi.Plan(infos, 32, 32, n_ctas=296)
     items, cta = plan.items(), plan.array(cabi.PLAN_CTA_ITEM_BEGIN)
-    assert len(cta) == 149
+    assert len(cta) == 297
     # empty tails cost (almost) nothing: count full tiles only
-    loads = [float((items[cta[c]:cta[c + 1], 1] - (items[cta[c]:cta[c + 1], 6] & 1)).sum()) for c in range(148)]
-    assert max(loads) - min(loads) <= 8.0   # chunk-first tiles weigh a little more than private ones
+    loads = [float((items[cta[c]:cta[c + 1], 1] - (items[cta[c]:cta[c + 1], 6] & 1)).sum()) for c in range(296)]
+    assert max(loads) - min(loads) <= 10.0  # chunk-first tiles and item boundaries weigh extra
     st = plan.stats()
     assert st["unique_kv_bytes"] == 301_989_888 and st["n_runs"] == 1
 
