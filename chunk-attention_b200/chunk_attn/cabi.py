@@ -16,9 +16,9 @@ CA_OK = 0
 CA_ERR_INVALID, CA_ERR_CUDA, CA_ERR_STATE, CA_ERR_DEVICE_STATUS = -1, -2, -3, -4
 CA_DTYPE_F16, CA_DTYPE_F32 = 0, 1
 CA_OPT_SPLIT_PHASES, CA_OPT_NUM_CTAS, CA_OPT_SEQ_FIRST_TENSOR, CA_OPT_TRACE = 1, 2, 3, 4
-(PLAN_ITEMS, PLAN_TILE_CHUNKS, PLAN_CTA_ITEM_BEGIN, PLAN_MERGE_OFF, PLAN_MERGE_SLOTS, PLAN_PATH_OFF,
- PLAN_PATH_CHUNKS, PLAN_PATH_TOKENS, PLAN_TAIL_CHUNK, PLAN_TAIL_TOKENS, PLAN_CTA_ITEM_BEGIN_CF,
- PLAN_CTA_ITEM_BEGIN_SF) = range(12)
+PLAN_ITEMS = 0
+(PLAN_MERGE_OFF, PLAN_MERGE_SLOTS, PLAN_PATH_OFF, PLAN_PATH_CHUNKS, PLAN_PATH_TOKENS, PLAN_TAIL_CHUNK,
+ PLAN_TAIL_TOKENS) = range(3, 10)
 
 # every symbol include/chunk_attn_b200.h declares
 EXPORTED = [
@@ -40,7 +40,8 @@ class ChunkInfo(C.Structure):
 class PlanStats(C.Structure):
     _fields_ = [("unique_kv_bytes", C.c_int64), ("n_chunks", C.c_int32), ("n_shared_chunks", C.c_int32),
                 ("n_runs", C.c_int32), ("n_items", C.c_int32), ("n_slots", C.c_int32),
-                ("n_ctas", C.c_int32), ("fast_path", C.c_int32), ("kernels_per_step", C.c_int32)]
+                ("n_ctas", C.c_int32), ("fast_path", C.c_int32), ("kernels_per_step", C.c_int32),
+                ("n_items_cf", C.c_int32)]
 
     def as_dict(self):
         return {f: getattr(self, f) for f, _ in self._fields_}
@@ -81,7 +82,7 @@ def _load():
         "ca_plan_array": (i32, [vp, i32, C.POINTER(C.POINTER(C.c_int32)), C.POINTER(i64)]),
         "ca_plan_stats_get": (i32, [vp, C.POINTER(PlanStats)]),
         "ca_plan_destroy": (None, [vp]),
-        "ca_attention_static": (i32, [vp, i32, vp, vp, i32, vp, i32, vp, vp, i32, vp, vp, i32, i32, vp, vp]),
+        "ca_attention_static": (i32, [vp, i32, vp, vp, i32, vp, i32, i32, vp, vp, i32, i32, vp, vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -125,7 +126,7 @@ class Plan:
         return np.ctypeslib.as_array(ptr, shape=(cnt.value,)).copy()
 
     def items(self):
-        return self.array(PLAN_ITEMS).reshape(-1, 8)
+        return self.array(PLAN_ITEMS).reshape(-1, 16)
 
     def stats(self):
         st = PlanStats()

@@ -95,7 +95,6 @@ struct ca_context {
     bool upload_pending = false;
     // device views into dev_blob
     const int4* d_items = nullptr;
-    const int32_t *d_tile_chunks = nullptr, *d_cta = nullptr, *d_cta_cf = nullptr, *d_cta_sf = nullptr;
     const int32_t *d_merge_off = nullptr, *d_merge_slots = nullptr;
     const int32_t *d_path_off = nullptr, *d_path_chunks = nullptr, *d_path_tokens = nullptr;
     const int32_t *d_tail_chunk = nullptr, *d_tail_tokens = nullptr;
@@ -105,6 +104,8 @@ struct ca_context {
     float2* part_ml = nullptr;
     size_t part_cap = 0;  // slots
     int* status = nullptr;
+    int* counters = nullptr;  // two item counters: a launch draws from one and zeroes the other
+    int launch_parity = 0;
 };
 
 extern "C" {
@@ -157,6 +158,8 @@ int ca_context_create(ca_context** out, int device, int n_heads, int d_head, int
     cudaError_t e = cudaEventCreateWithFlags(&c->upload_done, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaMalloc(&c->status, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(c->status, 0, sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc(&c->counters, 2 * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(c->counters, 0, 2 * sizeof(int));
     if (e == cudaSuccess && c->fast) e = ca::configure_fast_kernels();
     if (e != cudaSuccess) {
         ca_context_destroy(c);
@@ -179,6 +182,7 @@ void ca_context_destroy(ca_context* c) {
     if (c->part_ml) cudaFree(c->part_ml);
     if (c->trace) cudaFree(c->trace);
     if (c->status) cudaFree(c->status);
+    if (c->counters) cudaFree(c->counters);
     delete c;
 }
 
@@ -224,12 +228,8 @@ int ca_refresh_kernel_context(ca_context* c, const ca_chunk_info* infos, int n_i
 
     // pack every table into one staging buffer
     struct Part { const void* src; size_t bytes; size_t off; };
-    Part parts[12] = {
+    Part parts[8] = {
         {pl.items.data(), pl.items.size() * sizeof(ca::PlanItem), 0},
-        {pl.tile_chunks.data(), pl.tile_chunks.size() * 4, 0},
-        {pl.cta_item_begin.data(), pl.cta_item_begin.size() * 4, 0},
-        {pl.cta_item_begin_cf.data(), pl.cta_item_begin_cf.size() * 4, 0},
-        {pl.cta_item_begin_sf.data(), pl.cta_item_begin_sf.size() * 4, 0},
         {pl.merge_off.data(), pl.merge_off.size() * 4, 0},
         {pl.merge_slots.data(), pl.merge_slots.size() * 4, 0},
         {pl.path_off.data(), pl.path_off.size() * 4, 0},
@@ -270,17 +270,13 @@ int ca_refresh_kernel_context(ca_context* c, const ca_chunk_info* infos, int n_i
     CA_CUDA(cudaEventRecord(c->upload_done, stream));
     c->upload_pending = true;
     c->d_items = reinterpret_cast<const int4*>(c->dev_blob + parts[0].off);
-    c->d_tile_chunks = reinterpret_cast<const int32_t*>(c->dev_blob + parts[1].off);
-    c->d_cta = reinterpret_cast<const int32_t*>(c->dev_blob + parts[2].off);
-    c->d_cta_cf = reinterpret_cast<const int32_t*>(c->dev_blob + parts[3].off);
-    c->d_cta_sf = reinterpret_cast<const int32_t*>(c->dev_blob + parts[4].off);
-    c->d_merge_off = reinterpret_cast<const int32_t*>(c->dev_blob + parts[5].off);
-    c->d_merge_slots = reinterpret_cast<const int32_t*>(c->dev_blob + parts[6].off);
-    c->d_path_off = reinterpret_cast<const int32_t*>(c->dev_blob + parts[7].off);
-    c->d_path_chunks = reinterpret_cast<const int32_t*>(c->dev_blob + parts[8].off);
-    c->d_path_tokens = reinterpret_cast<const int32_t*>(c->dev_blob + parts[9].off);
-    c->d_tail_chunk = reinterpret_cast<const int32_t*>(c->dev_blob + parts[10].off);
-    c->d_tail_tokens = reinterpret_cast<const int32_t*>(c->dev_blob + parts[11].off);
+    c->d_merge_off = reinterpret_cast<const int32_t*>(c->dev_blob + parts[1].off);
+    c->d_merge_slots = reinterpret_cast<const int32_t*>(c->dev_blob + parts[2].off);
+    c->d_path_off = reinterpret_cast<const int32_t*>(c->dev_blob + parts[3].off);
+    c->d_path_chunks = reinterpret_cast<const int32_t*>(c->dev_blob + parts[4].off);
+    c->d_path_tokens = reinterpret_cast<const int32_t*>(c->dev_blob + parts[5].off);
+    c->d_tail_chunk = reinterpret_cast<const int32_t*>(c->dev_blob + parts[6].off);
+    c->d_tail_tokens = reinterpret_cast<const int32_t*>(c->dev_blob + parts[7].off);
 
     // partial-result scratch, grow-only
     const size_t slots = (size_t)pl.stats.n_slots;
@@ -353,26 +349,30 @@ int ca_attn_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_st
     p.n_heads = c->geo.n_heads;
     p.q = q;
     p.items = c->d_items;
-    p.tile_chunks = c->d_tile_chunks;
     p.part_o = c->part_o;
     p.part_ml = c->part_ml;
     p.delta_tokens = c->delta_tokens;
     p.scale_log2 = 1.4426950408889634f / std::sqrt((float)c->geo.d_head);
     p.status = c->status;
     p.trace = c->trace;
+    // one launch per range of items; every launch draws from the counter the previous launch zeroed
+    auto launch = [&](int lo, int hi) -> cudaError_t {
+        if (hi <= lo) return cudaSuccess;
+        p.item_lo = lo;
+        p.item_hi = hi;
+        p.counter = c->counters + c->launch_parity;
+        p.counter_next = c->counters + (c->launch_parity ^ 1);
+        c->launch_parity ^= 1;
+        const int n_ctas = c->plan.n_ctas < hi - lo ? c->plan.n_ctas : hi - lo;
+        c->trace_ctas = n_ctas;
+        return ca::launch_attn_partials(p, n_ctas, stream);
+    };
+    const int n_items = (int)c->plan.items.size();
     if (!c->plan.split_phases) {
-        p.cta_item_begin = c->d_cta;
-        c->trace_ctas = (int)c->plan.cta_item_begin.size() - 1;
-        CA_CUDA(ca::launch_attn_partials(p, (int)c->plan.cta_item_begin.size() - 1, stream));
+        CA_CUDA(launch(0, n_items));
     } else {
-        if ((phases & 1) && c->plan.n_items_cf > 0) {
-            p.cta_item_begin = c->d_cta_cf;
-            CA_CUDA(ca::launch_attn_partials(p, (int)c->plan.cta_item_begin_cf.size() - 1, stream));
-        }
-        if (phases & 2) {
-            p.cta_item_begin = c->d_cta_sf;
-            CA_CUDA(ca::launch_attn_partials(p, (int)c->plan.cta_item_begin_sf.size() - 1, stream));
-        }
+        if (phases & 1) CA_CUDA(launch(0, c->plan.n_items_cf));
+        if (phases & 2) CA_CUDA(launch(c->plan.n_items_cf, n_items));
     }
     return CA_OK;
 }
@@ -560,10 +560,8 @@ int ca_plan_array(const ca_plan* plan, int which, const int32_t** data, int64_t*
     switch (which) {
         case CA_PLAN_ITEMS:
             *data = reinterpret_cast<const int32_t*>(pl.items.data());
-            *count = (int64_t)pl.items.size() * 8;
+            *count = (int64_t)pl.items.size() * 16;
             return CA_OK;
-        case CA_PLAN_TILE_CHUNKS: v = &pl.tile_chunks; break;
-        case CA_PLAN_CTA_ITEM_BEGIN: v = &pl.cta_item_begin; break;
         case CA_PLAN_MERGE_OFF: v = &pl.merge_off; break;
         case CA_PLAN_MERGE_SLOTS: v = &pl.merge_slots; break;
         case CA_PLAN_PATH_OFF: v = &pl.path_off; break;
@@ -571,8 +569,6 @@ int ca_plan_array(const ca_plan* plan, int which, const int32_t** data, int64_t*
         case CA_PLAN_PATH_TOKENS: v = &pl.path_tokens; break;
         case CA_PLAN_TAIL_CHUNK: v = &pl.tail_chunk; break;
         case CA_PLAN_TAIL_TOKENS: v = &pl.tail_tokens; break;
-        case CA_PLAN_CTA_ITEM_BEGIN_CF: v = &pl.cta_item_begin_cf; break;
-        case CA_PLAN_CTA_ITEM_BEGIN_SF: v = &pl.cta_item_begin_sf; break;
         default: return fail(CA_ERR_INVALID, "unknown plan array");
     }
     *data = v->data();

@@ -15,10 +15,13 @@
 //     warp-shuffle reductions.
 // Both kinds read their K/V tiles from a ring of 32 KiB shared-memory stages, filled by a
 // producer warp with 1-D TMA bulk copies (cp.async.bulk + mbarrier transaction counts) that run
-// ahead across item boundaries; the host has cut the tile stream into equal parts, one per CTA
-// (ca_plan.h).  A CTA is one consumer warpgroup (4 warps) plus a producer warpgroup; two CTAs share
-// an SM so that one CTA's item boundaries (queries, combining warps, storing a partial) hide
-// behind the other CTA's steady state.
+// ahead across item boundaries.  Items (at most 8 tiles, cut by the host, ca_plan.h) are
+// self-scheduled: each CTA's producer draws the next item from a device counter two items ahead of
+// use and hands its description to the consumers through shared memory together with the item's
+// first tile, so the split of the work follows what each SM actually achieves.  A CTA is one
+// consumer warpgroup (4 warps) plus a producer warpgroup; two CTAs share an SM so that one CTA's
+// item boundaries (queries, combining warps, storing a partial) hide behind the other CTA's
+// steady state.
 //
 // attn_merge_kernel — combines the partials of each (row, head) with the usual
 // max-rescaled sum (reference: the merge inlined in kernel_cuda.cu:962-984,1042-1085).
@@ -62,16 +65,22 @@ constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // about two seconds
 constexpr float NEG_BIG = -1.0e30f;
 
 struct ItemView {
-    int tile_begin, n_tiles, head, row_begin, n_rows, slot_base, flags, last_tokens;
+    int n_tiles, head, row_begin, n_rows, slot_base, flags, last_tokens, end;  // end != 0: no more items
+};
+struct ItemChunks {
+    int c[9];  // pool slots of the item's tiles
 };
 
-// Volatile so that the load is issued where it is written (one item ahead of its use) instead of
-// being sunk to the first use by the compiler.
-__device__ __forceinline__ ItemView load_item(const int4* items, int i) {
-    int4 a, b;
-    asm volatile("ld.global.nc.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(items + 2 * i));
-    asm volatile("ld.global.nc.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(items + 2 * i + 1));
-    return ItemView{a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+// Volatile so that the loads are issued where they are written (an item ahead of their use)
+// instead of being sunk to the first use by the compiler.
+__device__ __forceinline__ void load_item(const int4* items, int i, ItemView& v, ItemChunks& ch) {
+    int4 a, b, c, d;
+    asm volatile("ld.global.nc.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(items + 4 * i));
+    asm volatile("ld.global.nc.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(items + 4 * i + 1));
+    asm volatile("ld.global.nc.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(c.x), "=r"(c.y), "=r"(c.z), "=r"(c.w) : "l"(items + 4 * i + 2));
+    asm volatile("ld.global.nc.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(d.x), "=r"(d.y), "=r"(d.z), "=r"(d.w) : "l"(items + 4 * i + 3));
+    v = ItemView{a.x, a.y, a.z, a.w, b.x, b.y, b.z, 0};
+    ch = ItemChunks{{b.w, c.x, c.y, c.z, c.w, d.x, d.y, d.z, d.w}};
 }
 
 // tokens held by tile j of an item; only the last tile of a sequence-first item can be partial
@@ -140,6 +149,9 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void sts128(uint32_t addr, int x, int y, int z, int w) {
+    asm volatile("st.shared.v4.s32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
 __device__ __forceinline__ void sts128_zero(uint32_t addr) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(addr), "r"(0u) : "memory");
 }
@@ -188,67 +200,103 @@ struct Ring {
 
 __device__ __forceinline__ void report(int* status, int code) { atomicCAS(status, STATUS_OK, code); }
 
-// ---- producer: one warp, lane 0 issues --------------------------------------------------------------
-__device__ __forceinline__ void producer_loop(const PartialParams& p, Ring& rg, int item_begin, int item_end, int lane) {
+// The description of an item travels to the consumers in the padding of the first two query rows of
+// the slot that belongs to the stage of the item's first tile (16 spare bytes after each 256-byte row).
+__device__ __forceinline__ uint32_t desc_addr(const Ring& rg, uint32_t stage) {
+    return rg.qslots + stage * QSLOT_BYTES + FAST_D * 2;
+}
+
+// ---- producer: one thread -----------------------------------------------------------------------------
+// Post one stage: wait for it to be free, optionally publish an item description and the item's
+// query rows, and start the tile's bulk copies.  bytes == 0 posts an empty stage (an item without
+// tokens, or the end marker).
+__device__ __forceinline__ bool producer_post(const PartialParams& p, Ring& rg, const ItemView* desc, bool stage_q,
+                                              const uint8_t* src, uint32_t bytes) {
+    const long long t0 = rg.timed ? clock64() : 0;
+    const bool ok = mbar_wait_bounded(rg.empty_bar + 8 * rg.stage, rg.phase ^ 1);
+    if (rg.timed) rg.wait_cycles += clock64() - t0;
+    if (!ok) return false;
+    const uint32_t bar = rg.full_bar + 8 * rg.stage;
+    uint32_t q_bytes = 0;
+    if (desc) {
+        const uint32_t da = desc_addr(rg, rg.stage);
+        sts128(da, desc->n_tiles, desc->head, desc->row_begin, desc->n_rows);
+        sts128(da + QSLOT_PITCH, desc->slot_base, desc->flags, desc->last_tokens, desc->end);
+        if (stage_q) q_bytes = (uint32_t)desc->n_rows * (FAST_D * 2);
+    }
+    mbar_arrive_expect_tx(bar, 2 * bytes + q_bytes);  // release: the description is visible to whoever sees the phase
+    if (bytes) {
+        const uint32_t dst = rg.ring + rg.stage * FAST_STAGE_BYTES;
+        bulk_copy_g2s(dst, src, bytes, bar);
+        bulk_copy_g2s(dst + FAST_TILE_BYTES, src + FAST_TILE_BYTES, bytes, bar);
+    }
+    if (q_bytes) {
+        const uint8_t* q = reinterpret_cast<const uint8_t*>(p.q) +
+                           ((size_t)desc->row_begin * p.n_heads + desc->head) * (FAST_D * 2);
+        const uint32_t qdst = rg.qslots + rg.stage * QSLOT_BYTES;
+        for (int r = 0; r < desc->n_rows; r++)
+            bulk_copy_g2s(qdst + r * QSLOT_PITCH, q + (size_t)r * p.n_heads * (FAST_D * 2), FAST_D * 2, bar);
+    }
+    rg.advance();
+    return true;
+}
+
+__device__ __forceinline__ void producer_loop(const PartialParams& p, Ring& rg) {
     uint32_t issued = 0;
     bool ok = true;
-    ItemView next = item_begin < item_end ? load_item(p.items, item_begin) : ItemView{};
-    for (int i = item_begin; i < item_end && ok; i++) {
-        const ItemView it = next;
-        if (i + 1 < item_end) next = load_item(p.items, i + 1);  // in flight while this item streams
+    // Items are drawn two ahead (the atomic's round trip) and described one ahead (the loads of the
+    // description), so neither latency is exposed while the current item streams.
+    // The first two items of a CTA are fixed by its index, so that nothing waits for an atomic at
+    // start-up; the counter hands out the items after those of all CTAs.
+    const int n_fixed = 2 * (int)gridDim.x;
+    int id0 = p.item_lo + (int)blockIdx.x;
+    int id1 = p.item_lo + (int)gridDim.x + (int)blockIdx.x;
+    ItemView it{};
+    ItemChunks ch{};
+    if (id0 < p.item_hi) load_item(p.items, id0, it, ch);
+    while (id0 < p.item_hi && ok) {
+        const int id2 = p.item_lo + n_fixed + atomicAdd(p.counter, 1);
+        ItemView it1{};
+        ItemChunks ch1{};
+        if (id1 < p.item_hi) load_item(p.items, id1, it1, ch1);
         // items of up to 16 rows get their query rows staged next to their first tile
-        bool q_pending = (it.flags >> ITEM_SPLITS_SHIFT) == NUM_CONSUMER_WARPS;
-        for (int j0 = 0; j0 < it.n_tiles && ok; j0 += 32) {
-            // each lane fetches the pool slot of one upcoming tile, lane 0 reads them by shuffle
-            const int jl = j0 + lane;
-            const int my_chunk = (jl < it.n_tiles) ? __ldg(p.tile_chunks + it.tile_begin + jl) : 0;
-            const int jn = min(32, it.n_tiles - j0);
-            for (int jj = 0; jj < jn; jj++) {
-                const int chunk = __shfl_sync(0xffffffffu, my_chunk, jj);
-                const int nt = tile_tokens(it, j0 + jj, p.delta_tokens);
-                if (nt == 0) continue;
-                if (lane == 0) {
-                    const long long t0 = rg.timed ? clock64() : 0;
-                    ok = mbar_wait_bounded(rg.empty_bar + 8 * rg.stage, rg.phase ^ 1);
-                    if (rg.timed) rg.wait_cycles += clock64() - t0;
-                    if (ok) {
-                        const uint8_t* src =
-                            p.pool + ((size_t)chunk * p.n_heads + it.head) * (size_t)FAST_STAGE_BYTES;
-                        const uint32_t bytes = (uint32_t)nt * (FAST_D * 2);
-                        const uint32_t bar = rg.full_bar + 8 * rg.stage;
-                        const uint32_t dst = rg.ring + rg.stage * FAST_STAGE_BYTES;
-                        const uint32_t q_bytes = q_pending ? (uint32_t)it.n_rows * (FAST_D * 2) : 0u;
-                        mbar_arrive_expect_tx(bar, 2 * bytes + q_bytes);
-                        bulk_copy_g2s(dst, src, bytes, bar);
-                        bulk_copy_g2s(dst + FAST_TILE_BYTES, src + FAST_TILE_BYTES, bytes, bar);
-                        if (q_pending) {
-                            const uint8_t* q = reinterpret_cast<const uint8_t*>(p.q) +
-                                               ((size_t)it.row_begin * p.n_heads + it.head) * (FAST_D * 2);
-                            const uint32_t qdst = rg.qslots + rg.stage * QSLOT_BYTES;
-                            for (int r = 0; r < it.n_rows; r++)
-                                bulk_copy_g2s(qdst + r * QSLOT_PITCH, q + (size_t)r * p.n_heads * (FAST_D * 2),
-                                              FAST_D * 2, bar);
-                        }
-                    }
+        const bool stage_q = (it.flags >> ITEM_SPLITS_SHIFT) == NUM_CONSUMER_WARPS;
+        bool first = true;
+#pragma unroll
+        for (int j = 0; j < 9; j++) {
+            if (j < it.n_tiles && ok) {
+                const int nt = tile_tokens(it, j, p.delta_tokens);
+                if (nt > 0) {
+                    const uint8_t* src = p.pool + ((size_t)ch.c[j] * p.n_heads + it.head) * (size_t)FAST_STAGE_BYTES;
+                    ok = producer_post(p, rg, first ? &it : nullptr, stage_q, src, (uint32_t)nt * (FAST_D * 2));
+                    issued += ok ? 1 : 0;
+                    first = false;
                 }
-                q_pending = false;
-                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                if (!ok) break;
-                issued++;
-                rg.advance();
             }
         }
+        if (first && ok) {  // no token in the whole item: the description still has to travel
+            ok = producer_post(p, rg, &it, false, nullptr, 0);
+            issued += ok ? 1 : 0;
+        }
+        id0 = id1;
+        id1 = id2;
+        it = it1;
+        ch = ch1;
     }
-    if (lane == 0) {
-        if (!ok) report(p.status, STATUS_EMPTY_WAIT_TIMEOUT);
-        // Do not leave while a copy into this CTA's shared memory may still be in flight: wait
-        // (bounded) for the completion of the last fills, newest NUM_STAGES at most.
-        const uint32_t n_check = issued < (uint32_t)NUM_STAGES ? issued : (uint32_t)NUM_STAGES;
-        for (uint32_t f = issued - n_check; f < issued; f++) {
-            if (!mbar_wait_bounded(rg.full_bar + 8 * (f % NUM_STAGES), (f / NUM_STAGES) & 1)) {
-                report(p.status, STATUS_DRAIN_TIMEOUT);
-                break;
-            }
+    if (ok) {
+        ItemView end_marker{};
+        end_marker.end = 1;
+        ok = producer_post(p, rg, &end_marker, false, nullptr, 0);
+        issued += ok ? 1 : 0;
+    }
+    if (!ok) report(p.status, STATUS_EMPTY_WAIT_TIMEOUT);
+    // Do not leave while a copy into this CTA's shared memory may still be in flight: wait
+    // (bounded) for the completion of the last fills, newest NUM_STAGES at most.
+    const uint32_t n_check = issued < (uint32_t)NUM_STAGES ? issued : (uint32_t)NUM_STAGES;
+    for (uint32_t f = issued - n_check; f < issued; f++) {
+        if (!mbar_wait_bounded(rg.full_bar + 8 * (f % NUM_STAGES), (f / NUM_STAGES) & 1)) {
+            report(p.status, STATUS_DRAIN_TIMEOUT);
+            break;
         }
     }
 }
@@ -361,10 +409,12 @@ __device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView&
     const int v_tok = (lane & 7) + ((mi & 1) << 3);    // V: matrices 1,3 are the next 8 tokens
     const int v_gsel = mi >> 1;                        //    matrices 2,3 are the next granule
 
+    bool waited = true;  // the caller has waited for the item's first stage (it carried the description)
     for (int j = 0; j < it.n_tiles; j++) {
         const int nt = tile_tokens(it, j, p.delta_tokens);
         if (nt == 0) continue;  // an empty reserved tail: it occupies no stage
-        if (!consumer_wait_full(rg)) return false;
+        if (!waited && !consumer_wait_full(rg)) return false;
+        waited = false;
         const uint32_t kbase = rg.ring + rg.stage * FAST_STAGE_BYTES;
         const uint32_t vbase = kbase + FAST_TILE_BYTES;
         if (STAGED_Q && !have_q) {
@@ -499,6 +549,7 @@ __device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView&
         consumer_release(rg, lane);
     }
 
+    if (waited) consumer_release(rg, lane);  // the item held no token: its first stage was empty
     // the four lanes of a quad hold partial sums of the same two rows
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
@@ -568,10 +619,12 @@ __device__ __forceinline__ bool simt_item(const PartialParams& p, const ItemView
 #pragma unroll
     for (int i = 0; i < 8; i++) o[i] = 0.f;
 
+    bool waited = true;  // the caller has waited for the item's first stage (it carried the description)
     for (int j = 0; j < it.n_tiles; j++) {
         const int nt = tile_tokens(it, j, p.delta_tokens);
         if (nt == 0) continue;
-        if (!consumer_wait_full(rg)) return false;
+        if (!waited && !consumer_wait_full(rg)) return false;
+        waited = false;
         if (warp * TPW < nt) {
             const uint32_t kt = rg.ring + rg.stage * FAST_STAGE_BYTES;
             const uint32_t vt = kt + FAST_TILE_BYTES;
@@ -631,6 +684,7 @@ __device__ __forceinline__ bool simt_item(const PartialParams& p, const ItemView
         consumer_release(rg, lane);
     }
 
+    if (waited) consumer_release(rg, lane);  // the item held no token: its first stage was empty
     // the two half-warps walked different tokens against the same running max
     l += __shfl_xor_sync(0xffffffffu, l, 16);
 #pragma unroll
@@ -681,17 +735,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 2) attn_partial_kernel(const Part
     // let the merge kernel (a programmatic dependent launch) be scheduled as soon as SMs drain
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    const int item_begin = __ldg(p.cta_item_begin + blockIdx.x);
-    const int item_end = __ldg(p.cta_item_begin + blockIdx.x + 1);
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    // the launch after this one draws from the other counter: zero it now (launches are stream-ordered)
+    if (blockIdx.x == 0 && threadIdx.x == 0) *p.counter_next = 0;
 
     if (p.trace && threadIdx.x == 0) p.trace[8 * blockIdx.x + 0] = global_timer_ns();
     if (warp >= NUM_CONSUMER_WARPS) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PRODUCER_REGS));
-        if (warp == NUM_CONSUMER_WARPS) {
-            producer_loop(p, rg, item_begin, item_end, lane);
-            if (p.trace && lane == 0) {
+        if (warp == NUM_CONSUMER_WARPS && lane == 0) {
+            producer_loop(p, rg);
+            if (p.trace) {
                 p.trace[8 * blockIdx.x + 1] = global_timer_ns();
                 p.trace[8 * blockIdx.x + 6] = (unsigned long long)rg.wait_cycles;
             }
@@ -701,10 +755,20 @@ __global__ void __launch_bounds__(NUM_THREADS, 2) attn_partial_kernel(const Part
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(CONSUMER_REGS));
 
     uint32_t row_items = 0;  // one-row items finished so far (scratch buffer and merge-barrier parity)
-    ItemView next = item_begin < item_end ? load_item(p.items, item_begin) : ItemView{};
-    for (int i = item_begin; i < item_end; i++) {
-        const ItemView it = next;
-        if (i + 1 < item_end) next = load_item(p.items, i + 1);  // in flight while this item is walked
+    while (true) {
+        // the next item announces itself with its first stage
+        if (!consumer_wait_full(rg)) {
+            if (lane == 0) report(p.status, STATUS_FULL_WAIT_TIMEOUT);
+            break;
+        }
+        const uint32_t da = desc_addr(rg, rg.stage);
+        const uint4 d0 = lds128(da);
+        const uint4 d1 = lds128(da + QSLOT_PITCH);
+        const ItemView it{(int)d0.x, (int)d0.y, (int)d0.z, (int)d0.w, (int)d1.x, (int)d1.y, (int)d1.z, (int)d1.w};
+        if (it.end) {
+            consumer_release(rg, lane);
+            break;
+        }
         const int splits = it.flags >> ITEM_SPLITS_SHIFT;
         bool ok;
         if (splits == 4) {
@@ -732,6 +796,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 2) attn_partial_kernel(const Part
 }
 
 // One warp per (row, head): out = sum_i 2^(m_i - M) O_i / sum_i 2^(m_i - M) l_i.
+// The partial list of a pair is read 32 slots at a time, one slot per lane, so that the two
+// dependent lookups (slot index, then its max and sum) cost one round trip per 32 partials instead
+// of one per partial; the O rows are then fetched with the slot numbers passed around by shuffles,
+// four independent loads in flight at a time.
 __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeParams p) {
     // When launched as a programmatic dependent of the partial kernel, wait here until that
     // kernel's results are visible; a no-op for an ordinary launch.
@@ -740,22 +808,55 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeParams p) {
     if (pair >= p.n_pairs) return;
     const int lane = threadIdx.x & 31;
     const int b = __ldg(p.merge_off + pair), e = __ldg(p.merge_off + pair + 1);
+    // pass 1: the maximum over all partials
     float mm = NEG_BIG;
-    for (int i = b; i < e; i++) mm = fmaxf(mm, p.part_ml[__ldg(p.merge_slots + i)].x);
+    for (int i = b + lane; i < e; i += 32) {
+        const float2 ml = p.part_ml[__ldg(p.merge_slots + i)];
+        if (ml.y > 0.f) mm = fmaxf(mm, ml.x);
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, off));
+    // pass 2: weights and the weighted sums
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float ll = 0.f;
-    for (int i = b; i < e; i++) {
-        const int slot = __ldg(p.merge_slots + i);
-        const float2 ml = p.part_ml[slot];
-        if (!(ml.y > 0.f)) continue;  // an empty piece: its O row was not written
-        const float w = fast_exp2(ml.x - mm);
-        ll = fmaf(w, ml.y, ll);
-        const float4 v = *reinterpret_cast<const float4*>(p.part_o + (size_t)slot * FAST_D + 4 * lane);
-        acc.x = fmaf(w, v.x, acc.x);
-        acc.y = fmaf(w, v.y, acc.y);
-        acc.z = fmaf(w, v.z, acc.z);
-        acc.w = fmaf(w, v.w, acc.w);
+    for (int base = b; base < e; base += 32) {
+        const int i = base + lane;
+        int slot = -1;
+        float w = 0.f;
+        if (i < e) {
+            slot = __ldg(p.merge_slots + i);
+            const float2 ml = p.part_ml[slot];
+            if (ml.y > 0.f) {  // an empty piece has no O row
+                w = fast_exp2(ml.x - mm);
+                ll = fmaf(w, ml.y, ll);
+            } else {
+                slot = -1;
+            }
+        }
+        const int n = min(32, e - base);
+        for (int k0 = 0; k0 < n; k0 += 4) {
+            float4 v[4];
+            float wk[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int sk = __shfl_sync(0xffffffffu, slot, (k0 + u) & 31);
+                wk[u] = __shfl_sync(0xffffffffu, w, (k0 + u) & 31);
+                const bool live = (k0 + u < n) && sk >= 0;
+                if (!live) wk[u] = 0.f;
+                v[u] = live ? *reinterpret_cast<const float4*>(p.part_o + (size_t)sk * FAST_D + 4 * lane)
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                acc.x = fmaf(wk[u], v[u].x, acc.x);
+                acc.y = fmaf(wk[u], v[u].y, acc.y);
+                acc.z = fmaf(wk[u], v[u].z, acc.z);
+                acc.w = fmaf(wk[u], v[u].w, acc.w);
+            }
+        }
     }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) ll += __shfl_xor_sync(0xffffffffu, ll, off);
     const float inv = ll > 0.f ? 1.f / ll : 0.f;  // a row with no token yields zeros
     const __half2 h01 = __floats2half2_rn(acc.x * inv, acc.y * inv);
     const __half2 h23 = __floats2half2_rn(acc.z * inv, acc.w * inv);

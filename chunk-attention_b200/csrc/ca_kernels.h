@@ -30,9 +30,10 @@ struct PartialParams {
     const uint8_t* pool;         // chunk pool base
     int n_heads;
     const void* q;               // fp16 [n_seqs, n_heads, 128]
-    const int4* items;           // PlanItem as two int4
-    const int32_t* tile_chunks;
-    const int32_t* cta_item_begin;
+    const int4* items;           // PlanItem as four int4
+    int item_lo, item_hi;        // the launch works through items [item_lo, item_hi)
+    int* counter;                // next item to hand out (relative to item_lo); zero when the launch starts
+    int* counter_next;           // the counter of the following launch: zeroed by this one
     float* part_o;               // [n_slots][128]
     float2* part_ml;             // [n_slots] (running max in log2 units, sum of exponentials)
     int delta_tokens;            // tokens appended to every tail since the plan was built

@@ -32,11 +32,16 @@ constexpr int kMaxDevices = 64;
 static __device__ __align__(256) unsigned char g_static_scratch[kPartOBytes + kPartMlBytes];
 // Kernel status word used when the caller passes none; cleared at the start of every call.
 static __device__ int g_static_status;
+// The two item counters of the self-scheduling kernel: a launch draws from one and zeroes the other
+// for the launch after it.  Zero when the library is loaded.
+static __device__ int g_static_counters[2];
 
 struct DeviceSetup {
     bool done = false;
     unsigned char* scratch = nullptr;  // device address of g_static_scratch on this device
     int* status = nullptr;             // device address of g_static_status on this device
+    int* counters = nullptr;           // device address of g_static_counters on this device
+    int parity = 0;                    // which counter the next launch draws from
 };
 DeviceSetup g_setup[kMaxDevices];
 std::mutex g_setup_mutex;
@@ -51,8 +56,7 @@ int fail(int code, const std::string& msg) {
 extern "C" {
 
 int ca_attention_static(const void* pool, int n_heads, const void* q, void* out, int n_seqs,
-                        const int32_t* items, int n_items, const int32_t* tile_chunks,
-                        const int32_t* cta_item_begin, int n_ctas, const int32_t* merge_off,
+                        const int32_t* items, int n_items, int n_ctas, const int32_t* merge_off,
                         const int32_t* merge_slots, int n_slots, int delta_tokens, int32_t* status,
                         ca_stream stream_) {
     if (n_seqs < 0 || n_heads <= 0 || n_items < 0 || n_ctas < 0 || n_slots < 0 || delta_tokens < 0)
@@ -62,8 +66,8 @@ int ca_attention_static(const void* pool, int n_heads, const void* q, void* out,
                                         std::to_string(kMaxSlots) + " (CA_STATIC_MAX_SLOTS): use ca_attention, or plan fewer, larger pieces");
     if (n_ctas > 4096) return fail(CA_ERR_INVALID, "more than 4096 CTAs");
     if (n_seqs == 0) return CA_OK;
-    if (!pool || !q || !out || !items || !tile_chunks || !cta_item_begin || !merge_off || !merge_slots)
-        return fail(CA_ERR_INVALID, "null pointer");
+    if (!pool || !q || !out || !items || !merge_off || !merge_slots) return fail(CA_ERR_INVALID, "null pointer");
+    if (n_ctas < 1 || n_items < 1) return fail(CA_ERR_INVALID, "a non-empty batch needs at least one item and one CTA");
     if (reinterpret_cast<uintptr_t>(q) % 16 || reinterpret_cast<uintptr_t>(out) % 8 ||
         reinterpret_cast<uintptr_t>(pool) % 256 || reinterpret_cast<uintptr_t>(items) % 16)
         return fail(CA_ERR_INVALID, "misaligned pointer (pool 256, q and items 16, out 8 bytes)");
@@ -85,6 +89,9 @@ int ca_attention_static(const void* pool, int n_heads, const void* q, void* out,
             e = cudaGetSymbolAddress(&p, g_static_status);
             if (e != cudaSuccess) return fail(CA_ERR_CUDA, std::string("cudaGetSymbolAddress(status): ") + cudaGetErrorString(e));
             su.status = static_cast<int*>(p);
+            e = cudaGetSymbolAddress(&p, g_static_counters);
+            if (e != cudaSuccess) return fail(CA_ERR_CUDA, std::string("cudaGetSymbolAddress(counters): ") + cudaGetErrorString(e));
+            su.counters = static_cast<int*>(p);
             e = ca::configure_fast_kernels();
             if (e != cudaSuccess) return fail(CA_ERR_CUDA, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
             su.done = true;
@@ -92,9 +99,11 @@ int ca_attention_static(const void* pool, int n_heads, const void* q, void* out,
     }
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     int* status_word = status ? status : su.status;
-    // The scratch keeps whatever the previous call left in it.  Nothing in it has to start at
-    // zero: every partial row a merge list names is written by this call before it is read.  The
-    // status word does have to start at zero, because kernels only ever set it.
+    // The scratch keeps whatever the previous call left in it.  No partial row has to start at
+    // zero: every row a merge list names is written by this call before it is read.  The status
+    // word does have to start at zero, because kernels only ever set it; so does the item counter
+    // this launch draws from, which the previous launch zeroed (the library image zeroes both for
+    // the first one).
     e = cudaMemsetAsync(status_word, 0, sizeof(int), stream);
     if (e != cudaSuccess) return fail(CA_ERR_CUDA, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
 
@@ -103,14 +112,20 @@ int ca_attention_static(const void* pool, int n_heads, const void* q, void* out,
     p.n_heads = n_heads;
     p.q = q;
     p.items = reinterpret_cast<const int4*>(items);
-    p.tile_chunks = tile_chunks;
-    p.cta_item_begin = cta_item_begin;
+    p.item_lo = 0;
+    p.item_hi = n_items;
+    {
+        std::lock_guard<std::mutex> lock(g_setup_mutex);
+        p.counter = su.counters + su.parity;
+        p.counter_next = su.counters + (su.parity ^ 1);
+        su.parity ^= 1;
+    }
     p.part_o = reinterpret_cast<float*>(su.scratch);
     p.part_ml = reinterpret_cast<float2*>(su.scratch + kPartOBytes);
     p.delta_tokens = delta_tokens;
     p.scale_log2 = 1.4426950408889634f / std::sqrt((float)ca::FAST_D);
     p.status = status_word;
-    e = ca::launch_attn_partials(p, n_ctas, stream);
+    e = ca::launch_attn_partials(p, n_ctas < n_items ? n_ctas : n_items, stream);
     if (e != cudaSuccess) return fail(CA_ERR_CUDA, std::string("partial kernel launch: ") + cudaGetErrorString(e));
     ca::MergeParams m;
     m.part_o = p.part_o;

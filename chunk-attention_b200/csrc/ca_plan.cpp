@@ -9,27 +9,10 @@ namespace ca {
 namespace {
 
 struct Unit {
-    int32_t tile_begin, n_tiles, head, row_begin, n_rows, splits, last_tokens;
-    bool tail;     // last tile is a sequence's tail chunk
-    double w;      // relative cost of one full tile of this unit
+    std::vector<int32_t> chunks;  // pool slots, root to leaf
+    int32_t head, row_begin, n_rows, splits, last_tokens;
+    bool tail;                    // last tile is a sequence's tail chunk
 };
-
-// Relative cost of streaming one tile through a chunk-first item.  Up to 32 rows the tile is
-// paid for by its HBM bytes alone (weight 1); wider row blocks issue proportionally more MMAs
-// per byte and become tensor-pipe bound.
-double chunk_first_tile_weight(int splits) {
-    return splits >= 4 ? 1.05 : (splits == 2 ? 1.3 : 2.0);
-}
-// partial rows an item emits: a one-row item combines its warps on chip and writes one row, a
-// wider item writes one row per (token split, query row)
-int item_slots(int n_rows, int splits) { return n_rows == 1 ? 1 : n_rows * std::max(1, splits); }
-// Fixed cost of starting and finishing an item (descriptor, queries, combining the warps, storing the
-// partial), in units of one full tile.
-constexpr double kItemOverhead = 0.25;
-// A tail tile costs what it holds now, plus a little for the tokens appended before the next rebuild.
-double tail_tile_weight(int tokens, int chunk_size) {
-    return std::min(1.0, std::max(0.05, (tokens + 4.0) / chunk_size));
-}
 
 std::string fmt(const char* f, long a = 0, long b = 0, long c = 0) {
     char buf[256];
@@ -37,62 +20,37 @@ std::string fmt(const char* f, long a = 0, long b = 0, long c = 0) {
     return buf;
 }
 
-// Lay the units [ubegin, uend) end to end, cut the stream into at most n_ctas equal-weight
-// parts and append the resulting items.  A tile belongs to the part its midpoint falls in.
-void cut_units(Plan& plan, const std::vector<Unit>& units, size_t ubegin, size_t uend, int n_ctas,
-               std::vector<int32_t>& cta_item_begin, int32_t& n_slots) {
-    double total = 0;
+// Cut the units [ubegin, uend) into items.  Guided self-scheduling: an item takes
+// remaining_tiles / n_ctas tiles, clamped to [1, MAX_TILES_PER_ITEM], so the list starts with
+// full-size items and ends with single tiles.
+void cut_units(Plan& plan, const std::vector<Unit>& units, size_t ubegin, size_t uend, int n_ctas, int32_t& n_slots) {
+    int64_t remaining = 0;
+    for (size_t u = ubegin; u < uend; u++) remaining += (int64_t)units[u].chunks.size();
     for (size_t u = ubegin; u < uend; u++) {
         const Unit& un = units[u];
-        total += kItemOverhead + un.w * un.n_tiles -
-                 (un.tail ? un.w - tail_tile_weight(un.last_tokens, plan.chunk_size) : 0.0);
-    }
-    int eff = (int)std::min<double>(n_ctas, std::max(1.0, total / 1.5));
-    const size_t first_item = plan.items.size();
-    std::vector<int32_t> item_cta;
-    double acc = 0;
-    auto cta_of = [&](double x) {
-        int c = total > 0 ? (int)(x * eff / total) : 0;
-        return std::min(eff - 1, std::max(0, c));
-    };
-    for (size_t u = ubegin; u < uend; u++) {
-        const Unit& un = units[u];
-        int piece_start = 0, cur = -1;
-        auto emit = [&](int j_end) {
-            PlanItem it;
-            it.tile_begin = un.tile_begin + piece_start;
-            it.n_tiles = j_end - piece_start;
+        const int n_tiles = (int)un.chunks.size();
+        int j = 0;
+        while (j < n_tiles) {
+            int want = (int)std::min<int64_t>(MAX_TILES_PER_ITEM - 1, std::max<int64_t>(1, remaining / n_ctas));
+            // a sequence's tail chunk (partially filled or still empty) rides along with the piece
+            // before it instead of becoming an item of its own
+            if (n_tiles - (j + want) == 1 && un.tail) want++;
+            const int len = std::min(want, n_tiles - j);
+            PlanItem it{};
+            it.n_tiles = len;
             it.head = un.head;
             it.row_begin = un.row_begin;
             it.n_rows = un.n_rows;
             it.slot_base = n_slots;
-            const bool has_last = (j_end == un.n_tiles);
+            const bool has_last = (j + len == n_tiles);
             it.flags = ((un.tail && has_last) ? ITEM_FLAG_TAIL : 0) | (un.splits << ITEM_SPLITS_SHIFT);
             it.last_tokens = has_last ? un.last_tokens : plan.chunk_size;
+            for (int k = 0; k < len; k++) it.chunk[k] = un.chunks[j + k];
             n_slots += item_slots(un.n_rows, un.splits);
             plan.items.push_back(it);
-            item_cta.push_back(cur);
-        };
-        acc += kItemOverhead;
-        for (int j = 0; j < un.n_tiles; j++) {
-            const double w = (un.tail && j == un.n_tiles - 1) ? tail_tile_weight(un.last_tokens, plan.chunk_size) : un.w;
-            const int c = cta_of(acc + 0.5 * w);
-            if (cur < 0) cur = c;
-            if (c != cur) {
-                emit(j);
-                piece_start = j;
-                cur = c;
-            }
-            acc += w;
+            j += len;
+            remaining -= len;
         }
-        if (un.n_tiles > 0) emit(un.n_tiles);
-    }
-    cta_item_begin.assign(eff + 1, (int32_t)plan.items.size());
-    // items are in non-decreasing CTA order: the first item of CTA c is the first with cta >= c
-    size_t i = 0;
-    for (int c = 0; c <= eff; c++) {
-        while (i < item_cta.size() && item_cta[i] < c) i++;
-        cta_item_begin[c] = (int32_t)(first_item + i);
     }
 }
 
@@ -164,12 +122,11 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
     plan.merge_off.assign((size_t)n_seqs * n_heads + 1, 0);
     if (!fast_path) {
         plan.n_ctas = 0;
-        plan.cta_item_begin.assign(1, 0);
         return "";
     }
 
     // ---- classify chunks, group shared ones into runs ----------------------------------------------
-    struct Run { int32_t b, e, tile_begin; std::vector<int32_t> chunks; };
+    struct Run { int32_t b, e; std::vector<int32_t> chunks; };
     std::vector<Run> runs;
     std::unordered_map<uint64_t, int> run_of;
     std::vector<char> shared(n_infos, 0);
@@ -185,7 +142,7 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
             if (f == run_of.end()) {
                 r = (int)runs.size();
                 run_of.emplace(key, r);
-                runs.push_back(Run{ci.seq_begin, ci.seq_end, 0, {}});
+                runs.push_back(Run{ci.seq_begin, ci.seq_end, {}});
             } else {
                 r = f->second;
             }
@@ -194,11 +151,9 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
     }
     plan.stats.n_runs = (int)runs.size();
 
-    // ---- tile table and units ---------------------------------------------------------------------------
+    // ---- units ---------------------------------------------------------------------------------------------
     std::vector<Unit> units;
     for (Run& r : runs) {
-        r.tile_begin = (int32_t)plan.tile_chunks.size();
-        plan.tile_chunks.insert(plan.tile_chunks.end(), r.chunks.begin(), r.chunks.end());
         const int n = r.e - r.b;
         const int n_blocks = (n + MAX_ROWS_PER_ITEM - 1) / MAX_ROWS_PER_ITEM;
         const int rows_per_block = (n + n_blocks - 1) / n_blocks;
@@ -207,39 +162,37 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
             const int rows = std::min(rows_per_block, r.e - rb);
             if (rows <= 0) continue;
             const int splits = rows <= 16 ? 4 : (rows <= 32 ? 2 : 1);
-            for (int h = 0; h < n_heads; h++)
-                units.push_back(Unit{r.tile_begin, (int32_t)r.chunks.size(), h, rb, rows, splits,
-                                     chunk_size, false, chunk_first_tile_weight(splits)});
+            for (int h = 0; h < n_heads; h++) units.push_back(Unit{r.chunks, h, rb, rows, splits, chunk_size, false});
         }
     }
     const size_t n_units_cf = units.size();
     for (int s = 0; s < n_seqs; s++) {
-        const int32_t tb = (int32_t)plan.tile_chunks.size();
+        std::vector<int32_t> priv;
         for (int32_t p = plan.path_off[s]; p < plan.path_off[s + 1]; p++)
-            if (!shared[path_info[p]]) plan.tile_chunks.push_back(plan.path_chunks[p]);
-        const int32_t nt = (int32_t)plan.tile_chunks.size() - tb;
+            if (!shared[path_info[p]]) priv.push_back(plan.path_chunks[p]);
         // a non-final private tile must be full: only the tail may be partially filled
         for (int32_t p = plan.path_off[s]; p + 1 < plan.path_off[s + 1]; p++)
             if (!shared[path_info[p]] && plan.path_tokens[p] != chunk_size)
                 return fmt("row %ld has a partially filled chunk that is not its tail", s);
         for (int h = 0; h < n_heads; h++)
-            units.push_back(Unit{tb, nt, h, s, 1, seq_first_tensor ? 4 : 0, plan.tail_tokens[s], true, 1.0});
+            units.push_back(Unit{priv, h, s, 1, seq_first_tensor ? 4 : 0, plan.tail_tokens[s], true});
     }
 
-    // ---- cut into items, schedules ----------------------------------------------------------------------
+    // ---- items ---------------------------------------------------------------------------------------------
     int32_t n_slots = 0;
     if (!split_phases) {
-        cut_units(plan, units, 0, units.size(), n_ctas, plan.cta_item_begin, n_slots);
+        cut_units(plan, units, 0, units.size(), n_ctas, n_slots);
         plan.n_items_cf = 0;
-        plan.n_ctas = (int)plan.cta_item_begin.size() - 1;
+        for (const PlanItem& it : plan.items) plan.n_items_cf += it.n_rows > 1 ? 1 : 0;
         plan.stats.kernels_per_step = 2;
     } else {
-        cut_units(plan, units, 0, n_units_cf, n_ctas, plan.cta_item_begin_cf, n_slots);
+        // each phase is a launch of its own, with its own taper towards small items
+        cut_units(plan, units, 0, n_units_cf, n_ctas, n_slots);
         plan.n_items_cf = (int)plan.items.size();
-        cut_units(plan, units, n_units_cf, units.size(), n_ctas, plan.cta_item_begin_sf, n_slots);
-        plan.n_ctas = std::max((int)plan.cta_item_begin_cf.size(), (int)plan.cta_item_begin_sf.size()) - 1;
+        cut_units(plan, units, n_units_cf, units.size(), n_ctas, n_slots);
         plan.stats.kernels_per_step = (plan.n_items_cf > 0 ? 1 : 0) + 2;
     }
+    plan.n_ctas = (int)std::min<int64_t>(n_ctas, std::max<int64_t>(1, (int64_t)plan.items.size()));
 
     // ---- merge lists -------------------------------------------------------------------------------------
     for (const PlanItem& it : plan.items) {
@@ -260,6 +213,7 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
         }
     }
     plan.stats.n_items = (int)plan.items.size();
+    plan.stats.n_items_cf = plan.n_items_cf;
     plan.stats.n_slots = n_slots;
     plan.stats.n_ctas = plan.n_ctas;
     return "";

@@ -8,13 +8,16 @@
 //
 //  * shared chunks (more sharers than tpp_threshold, always full) are grouped into RUNS, the
 //    maximal chains of chunks that serve the identical row range; one run x head x row block
-//    is a chunk-first unit and produces ONE partial per row for the whole chain instead of one
-//    per chunk;
+//    is a chunk-first unit and produces ONE partial per row for a whole piece of the chain
+//    instead of one per chunk;
 //  * the remaining chunks of a sequence (its private tail) x head are a sequence-first unit;
-//  * every unit is a list of 32 KiB K+V tiles.  The units are laid end to end into one stream
-//    of weighted tiles, and the stream is cut into n_ctas equal parts; a unit that straddles a
-//    cut becomes two ITEMS, each emitting its own partial.  Each persistent CTA walks its
-//    items in order, so its TMA ring never drains between items;
+//  * every unit is a list of 32 KiB K+V tiles and is cut into ITEMS of at most 8 tiles (9 when a
+//    tail chunk rides along), each
+//    emitting its own partial.  Items are self-scheduled: the persistent CTAs draw the next item
+//    from a device counter, so the split of the work adapts to whatever each SM achieves.  Item
+//    sizes follow guided self-scheduling — as large as allowed while much work remains, shrinking
+//    towards single tiles at the end of the list — so that all CTAs finish within about one tile
+//    of each other;
 //  * merge lists name, per (row, head), the partial slots the merge kernel combines.
 #pragma once
 #include <stdint.h>
@@ -30,33 +33,34 @@ constexpr int ITEM_FLAG_TAIL = 1;     // last tile of the item is the sequence's
 constexpr int ITEM_SPLITS_SHIFT = 8;  // flags >> 8: token splits of a tensor-core item (4, 2, 1);
                                       // 0 = one-row item walked on CUDA cores
 constexpr int MAX_ROWS_PER_ITEM = 64; // 4 consumer warps x 16 rows
+constexpr int MAX_TILES_PER_ITEM = 9;  // 8 by size, plus a sequence's tail chunk riding along
 
 struct PlanItem {
-    int32_t tile_begin;   // index into tile_chunks
-    int32_t n_tiles;
+    int32_t n_tiles;      // 1 .. MAX_TILES_PER_ITEM
     int32_t head;
     int32_t row_begin;    // first row of q / out this item serves
     int32_t n_rows;       // 1: sequence-first item; >= 2: chunk-first item
     int32_t slot_base;    // first partial slot
     int32_t flags;
     int32_t last_tokens;  // tokens in the last tile when the plan was built
+    int32_t chunk[MAX_TILES_PER_ITEM];  // pool slots of the tiles
 };
-static_assert(sizeof(PlanItem) == 32, "PlanItem is read on the device as two int4");
+static_assert(sizeof(PlanItem) == 64, "PlanItem is read on the device as four int4");
 
 struct Plan {
     int n_seqs = 0, n_heads = 0, chunk_size = 0, tpp_threshold = 1, n_ctas = 1;
     bool split_phases = false;
-    std::vector<PlanItem> items;          // chunk-first items first when split_phases
-    std::vector<int32_t> tile_chunks;
-    std::vector<int32_t> cta_item_begin;     // fused schedule (n_ctas + 1)
-    std::vector<int32_t> cta_item_begin_cf;  // split schedules
-    std::vector<int32_t> cta_item_begin_sf;
+    std::vector<PlanItem> items;          // chunk-first items first
+    int n_items_cf = 0;                   // how many of them are chunk-first items
     std::vector<int32_t> merge_off, merge_slots;
     std::vector<int32_t> path_off, path_chunks, path_tokens;
     std::vector<int32_t> tail_chunk, tail_tokens;
-    int n_items_cf = 0;
     ca_plan_stats stats{};
 };
+
+// partial rows an item emits: a one-row item combines its warps on chip and writes one row, a
+// wider item writes one row per (token split, query row)
+inline int item_slots(int n_rows, int splits) { return n_rows == 1 ? 1 : n_rows * (splits > 1 ? splits : 1); }
 
 // Returns an empty string on success, else the reason the input was rejected.
 std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int n_seqs, int n_heads,

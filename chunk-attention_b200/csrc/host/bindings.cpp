@@ -26,6 +26,7 @@ py::dict stats_to_dict(const ca_plan_stats& st) {
     d["n_ctas"] = st.n_ctas;
     d["fast_path"] = st.fast_path;
     d["kernels_per_step"] = st.kernels_per_step;
+    d["n_items_cf"] = st.n_items_cf;
     return d;
 }
 

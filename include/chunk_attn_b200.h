@@ -164,11 +164,12 @@ typedef struct ca_plan_stats {
     int32_t n_chunks;          /* live non-root chunks, empty tails included                      */
     int32_t n_shared_chunks;   /* chunks walked by the chunk-first phase                          */
     int32_t n_runs;            /* maximal chains of shared chunks with identical sharers          */
-    int32_t n_items;           /* pieces of work after cutting to CTAs                            */
+    int32_t n_items;           /* self-scheduled pieces of work (at most 9 tiles each)            */
     int32_t n_slots;           /* partial rows                                                    */
     int32_t n_ctas;            /* persistent CTAs launched                                        */
     int32_t fast_path;         /* 1 when the tensor-core/TMA kernels serve this geometry          */
     int32_t kernels_per_step;  /* launches one ca_attention call makes                            */
+    int32_t n_items_cf;        /* how many items are chunk-first items (they come first)          */
 } ca_plan_stats;
 CA_API int ca_context_stats(const ca_context* ctx, ca_plan_stats* out);
 
@@ -188,9 +189,10 @@ CA_API int ca_context_stats(const ca_context* ctx, ca_plan_stats* out);
  * calling thread's current device:
  *   pool            the chunk pool (layout above), 256-byte aligned
  *   q, out          [n_seqs, n_heads, 128] fp16, contiguous
- *   items .. merge_slots   the work list: the arrays ca_plan_build produces (CA_PLAN_ITEMS,
- *                   CA_PLAN_TILE_CHUNKS, CA_PLAN_CTA_ITEM_BEGIN with n_ctas + 1 entries,
- *                   CA_PLAN_MERGE_OFF, CA_PLAN_MERGE_SLOTS), copied to the device by the caller
+ *   items, merge_off, merge_slots   the work list: the arrays ca_plan_build produces
+ *                   (CA_PLAN_ITEMS with n_items entries of 16 ints, CA_PLAN_MERGE_OFF,
+ *                   CA_PLAN_MERGE_SLOTS), copied to the device by the caller
+ *   n_ctas          persistent CTAs to launch (ca_plan_stats.n_ctas)
  *   n_slots         ca_plan_stats.n_slots of that plan; above CA_STATIC_MAX_SLOTS the call is refused
  *                   with CA_ERR_INVALID and a message naming both numbers
  *   delta_tokens    tokens appended to every tail since the plan was built
@@ -201,23 +203,21 @@ CA_API int ca_context_stats(const ca_context* ctx, ca_plan_stats* out);
  * and sets the kernel's shared-memory attribute; make that first call before any stream capture.
  * All calls on a device share the one scratch array, which still holds the previous call's
  * partial rows when the next call starts (none of them needs clearing: every row a merge list names
- * is rewritten first).  Two calls that overlap on the GPU (different streams, or different threads)
+ * is rewritten first; the two item counters next to them are the exception, and each launch zeroes
+ * the one the next launch will use).  Two calls that overlap on the GPU (different streams, or different threads)
  * therefore race on it: keep calls on one device stream-ordered. */
 #define CA_STATIC_MAX_SLOTS 16384
 CA_API int ca_attention_static(const void* pool, int n_heads, const void* q, void* out, int n_seqs,
-                               const int32_t* items, int n_items, const int32_t* tile_chunks,
-                               const int32_t* cta_item_begin, int n_ctas, const int32_t* merge_off,
+                               const int32_t* items, int n_items, int n_ctas, const int32_t* merge_off,
                                const int32_t* merge_slots, int n_slots, int delta_tokens,
                                int32_t* status, ca_stream stream);
 
 /* ---- host-only planner (no GPU needed) -------------------------------------------------------
  * The work-list builder used by ca_refresh_kernel_context, exposed so that it can be checked on
  * a machine without a GPU.  Arrays are owned by the plan. */
-#define CA_PLAN_ITEMS 0          /* int32[n_items][8]: tile_begin, n_tiles, head, row_begin,
-                                    n_rows, slot_base, flags(bit0 last tile is a tail; bits 8..:
-                                    token splits, 0 = CUDA-core walk), last_tokens               */
-#define CA_PLAN_TILE_CHUNKS 1    /* int32[]: pool slots, indexed by tile_begin + j               */
-#define CA_PLAN_CTA_ITEM_BEGIN 2 /* int32[n_ctas + 1]                                            */
+#define CA_PLAN_ITEMS 0          /* int32[n_items][16]: n_tiles, head, row_begin, n_rows, slot_base,
+                                    flags (bit0: last tile is a tail; bits 8..: token splits, 0 =
+                                    CUDA-core walk), last_tokens, pool slots of up to 9 tiles      */
 #define CA_PLAN_MERGE_OFF 3      /* int32[n_seqs * n_heads + 1]                                  */
 #define CA_PLAN_MERGE_SLOTS 4    /* int32[]                                                      */
 #define CA_PLAN_PATH_OFF 5       /* int32[n_seqs + 1]   (sequence-first-only path lists)         */
@@ -225,8 +225,6 @@ CA_API int ca_attention_static(const void* pool, int n_heads, const void* q, voi
 #define CA_PLAN_PATH_TOKENS 7    /* int32[]: tokens in that chunk at refresh                     */
 #define CA_PLAN_TAIL_CHUNK 8     /* int32[n_seqs]                                                */
 #define CA_PLAN_TAIL_TOKENS 9    /* int32[n_seqs]                                                */
-#define CA_PLAN_CTA_ITEM_BEGIN_CF 10 /* split-phase schedules: chunk-first items                 */
-#define CA_PLAN_CTA_ITEM_BEGIN_SF 11 /* split-phase schedules: sequence-first items              */
 CA_API int ca_plan_build(ca_plan** out, const ca_chunk_info* infos, int n_infos, int n_seqs,
                          int n_heads, int chunk_size, int tpp_threshold, int n_ctas,
                          int64_t max_chunks, int split_phases, int seq_first_tensor);

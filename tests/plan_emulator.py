@@ -14,30 +14,24 @@ def emulate(plan, kv_of_chunk, q, chunk_size, delta=0, schedule="fused"):
     """plan: cabi.Plan; kv_of_chunk: chunk_id -> (K [H, C, d], V [H, C, d]) float arrays;
     q: [n_seqs, H, d].  Returns out [n_seqs, H, d] float64 and the list of (cta, item) visits."""
     items = plan.items()
-    tiles = plan.array(cabi.PLAN_TILE_CHUNKS)
     st = plan.stats()
     n_seqs, H, d = q.shape
     scale = 1.0 / math.sqrt(d)
     part_o = np.full((st["n_slots"], d), np.nan)
     part_m = np.full(st["n_slots"], np.nan)
     part_l = np.full(st["n_slots"], np.nan)
+    # items are self-scheduled: any CTA may take any item, each exactly once
+    loads = [int(r[0]) for r in items]
+    assert all(1 <= n <= 9 for n in loads)
+    if schedule == "split":
+        kinds = [int(r[3]) > 1 for r in items]
+        assert kinds == sorted(kinds, reverse=True), "chunk-first items must come first"
+        assert sum(kinds) == st["n_items_cf"]
 
-    if schedule == "fused":
-        begins = [plan.array(cabi.PLAN_CTA_ITEM_BEGIN)]
-    else:
-        begins = [plan.array(cabi.PLAN_CTA_ITEM_BEGIN_CF), plan.array(cabi.PLAN_CTA_ITEM_BEGIN_SF)]
-    visited = np.zeros(len(items), np.int32)
-    loads = []
-    for cta_begin in begins:
-        for c in range(len(cta_begin) - 1):
-            w = 0
-            for i in range(cta_begin[c], cta_begin[c + 1]):
-                visited[i] += 1
-                w += items[i][1]
-            loads.append(w)
-    assert (visited == 1).all(), "every item must be walked by exactly one CTA"
-
-    for (tile_begin, n_tiles, head, row_begin, n_rows, slot_base, flags, last_tokens) in items:
+    for row in items:
+        n_tiles, head, row_begin, n_rows, slot_base, flags, last_tokens = (int(x) for x in row[:7])
+        tiles = row[7:]
+        tile_begin = 0
         splits = flags >> 8
         tail = flags & 1
         ks, vs = [], []

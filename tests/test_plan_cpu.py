@@ -60,7 +60,7 @@ def shared_spec(n_seqs, shared, unique, base=0):
 def test_single_level_prefix(n_ctas, split, tensor_tails):
     ora = build_tree(shared_spec(6, 5 * C, 2 * C + 17))
     plan, loads = check(ora, 2, 8, n_ctas=n_ctas, split_phases=split, seq_first_tensor=tensor_tails)
-    assert sorted(set(int(f) >> 8 for f in plan.items()[:, 6])) == ([4] if tensor_tails else [0, 4])
+    assert sorted(set(int(f) >> 8 for f in plan.items()[:, 5])) == ([4] if tensor_tails else [0, 4])
     st = plan.stats()
     assert st["n_shared_chunks"] == 5 and st["n_runs"] == 1
     assert st["n_chunks"] == 5 + 6 * 3
@@ -83,7 +83,7 @@ def test_two_level_tree_and_row_blocks():
     ora = build_tree(spec, H=1, d=4)
     plan, _ = check(ora, 1, 4, n_ctas=20)
     items = plan.items()
-    splits = sorted(set(int(f) >> 8 for f in items[:, 6]))
+    splits = sorted(set(int(f) >> 8 for f in items[:, 5]))
     assert splits == [1, 2, 4]  # 92 and 70 rows -> blocks of <= 64 rows, 1 split; 20 -> 2; 2 rows and tails -> 4
     assert plan.stats()["n_runs"] == 4
 
@@ -91,7 +91,7 @@ def test_two_level_tree_and_row_blocks():
 def test_more_than_128_sharers_splits_rows():
     ora = build_tree(shared_spec(150, C, 3), H=1, d=4)
     plan, _ = check(ora, 1, 4, n_ctas=8)
-    rows = [int(r) for r in plan.items()[:, 4] if r > 1]
+    rows = [int(r) for r in plan.items()[:, 3] if r > 1]
     assert max(rows) <= 64
 
 
@@ -151,8 +151,8 @@ def test_random_traces(seed):
         check(ora, 2, 4, n_ctas=1 + seed, split_phases=bool(seed & 1))
 
 
-def test_balance_config2_shape():
-    # 32 sequences, 2048 shared + 512 unique tokens, 32 heads, 148 CTAs: the tile stream is cut evenly
+def test_items_of_config2_shape():
+    # 32 sequences, 2048 shared + 512 unique tokens, 32 heads: full-size items first, single tiles last
     infos = []
     cid = 0
     for _ in range(32):
@@ -162,13 +162,17 @@ def test_balance_config2_shape():
             infos.append((cid, C, s, s + 1)); cid += 1
         infos.append((cid, 0, s, s + 1)); cid += 1
     plan = cabi.Plan(infos, 32, 32, n_ctas=296)
-    items, cta = plan.items(), plan.array(cabi.PLAN_CTA_ITEM_BEGIN)
-    assert len(cta) == 297
-    # empty tails cost (almost) nothing: count full tiles only
-    loads = [float((items[cta[c]:cta[c + 1], 1] - (items[cta[c]:cta[c + 1], 6] & 1)).sum()) for c in range(296)]
-    assert max(loads) - min(loads) <= 10.0  # chunk-first tiles and item boundaries weigh extra
+    items = plan.items()
+    sizes = items[:, 0]
+    full = sizes - (items[:, 5] & 1)          # the tails are empty here
+    assert sizes.max() == 9 and full.max() == 8 and full[0] == 8 and full.min() >= 1
+    # guided self-scheduling: full-size items while much work remains, single tiles at the end
+    assert (full[:296] == 8).all() and (full[-296:] == 1).all()
+    means = [full[i:i + 200].mean() for i in range(0, len(full) - 200, 200)]
+    assert all(a >= b - 0.5 for a, b in zip(means, means[1:]))
     st = plan.stats()
-    assert st["unique_kv_bytes"] == 301_989_888 and st["n_runs"] == 1
+    assert st["unique_kv_bytes"] == 301_989_888 and st["n_runs"] == 1 and st["n_ctas"] == 296
+    assert int((sizes - (items[:, 5] & 1)).sum()) == 32 * 32 + 32 * 32 * 8  # every full tile exactly once
 
 
 def test_rejects_bad_work_lists():

@@ -35,13 +35,10 @@ def test_static_entry_point_matches_ca_attention_twice():
 
     # the caller's side of the allocation-free call: build the work list on the host and put it in
     # device memory of its own, once
-    plan = cabi.Plan(infos, len(rows), H, chunk_size=64, n_ctas=148, max_chunks=128)
+    plan = cabi.Plan(infos, len(rows), H, chunk_size=64, n_ctas=296, max_chunks=128)
     st = plan.stats()
     assert 0 < st["n_slots"] <= cabi.CA_STATIC_MAX_SLOTS
     items = device_i32(plan.array(cabi.PLAN_ITEMS))
-    tile_chunks = device_i32(plan.array(cabi.PLAN_TILE_CHUNKS))
-    cta_begin_host = plan.array(cabi.PLAN_CTA_ITEM_BEGIN)
-    cta_begin = device_i32(cta_begin_host)
     merge_off = device_i32(plan.array(cabi.PLAN_MERGE_OFF))
     merge_slots = device_i32(plan.array(cabi.PLAN_MERGE_SLOTS))
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
@@ -54,8 +51,8 @@ def test_static_entry_point_matches_ca_attention_twice():
         stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
         cabi.check(cabi.lib.ca_attention_static(
             eng.pool.data_ptr(), H, q.data_ptr(), out.data_ptr(), len(rows), items.data_ptr(), st["n_items"],
-            tile_chunks.data_ptr(), cta_begin.data_ptr(), len(cta_begin_host) - 1, merge_off.data_ptr(),
-            merge_slots.data_ptr(), st["n_slots"], 0, status.data_ptr(), stream))
+            st["n_ctas"], merge_off.data_ptr(), merge_slots.data_ptr(), st["n_slots"], 0, status.data_ptr(),
+            stream))
         torch.cuda.synchronize()
         assert int(status.item()) == 0
         assert torch.isfinite(out).all()
@@ -64,7 +61,6 @@ def test_static_entry_point_matches_ca_attention_twice():
     # a work list that does not fit the fixed scratch is refused before anything is launched
     rc = cabi.lib.ca_attention_static(
         eng.pool.data_ptr(), H, q.data_ptr(), out.data_ptr(), len(rows), items.data_ptr(), st["n_items"],
-        tile_chunks.data_ptr(), cta_begin.data_ptr(), len(cta_begin_host) - 1, merge_off.data_ptr(),
-        merge_slots.data_ptr(), cabi.CA_STATIC_MAX_SLOTS + 1, 0, None, stream)
+        st["n_ctas"], merge_off.data_ptr(), merge_slots.data_ptr(), cabi.CA_STATIC_MAX_SLOTS + 1, 0, None, stream)
     assert rc == cabi.CA_ERR_INVALID
     assert b"CA_STATIC_MAX_SLOTS" in cabi.lib.ca_last_error()
