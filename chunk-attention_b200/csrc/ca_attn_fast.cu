@@ -796,10 +796,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 2) attn_partial_kernel(const Part
 }
 
 // One warp per (row, head): out = sum_i 2^(m_i - M) O_i / sum_i 2^(m_i - M) l_i.
-// The partial list of a pair is read 32 slots at a time, one slot per lane, so that the two
-// dependent lookups (slot index, then its max and sum) cost one round trip per 32 partials instead
-// of one per partial; the O rows are then fetched with the slot numbers passed around by shuffles,
-// four independent loads in flight at a time.
+// The kernel is a chain of dependent lookups (list bounds -> slot numbers -> max and sum -> O rows),
+// so it is organised to pay each round trip once: a lane looks up one partial's slot, max and sum
+// (32 partials per pass, usually all of them), the maximum is found with shuffles, and the O rows
+// are then fetched eight at a time with the slot numbers passed around by shuffles.
 __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeParams p) {
     // When launched as a programmatic dependent of the partial kernel, wait here until that
     // kernel's results are visible; a no-op for an ordinary launch.
@@ -808,37 +808,47 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeParams p) {
     if (pair >= p.n_pairs) return;
     const int lane = threadIdx.x & 31;
     const int b = __ldg(p.merge_off + pair), e = __ldg(p.merge_off + pair + 1);
-    // pass 1: the maximum over all partials
-    float mm = NEG_BIG;
-    for (int i = b + lane; i < e; i += 32) {
+    // the first 32 partials stay in registers; longer lists are re-read pass by pass
+    int slot0 = -1;
+    float2 ml0 = make_float2(NEG_BIG, 0.f);
+    if (b + lane < e) {
+        slot0 = __ldg(p.merge_slots + b + lane);
+        ml0 = p.part_ml[slot0];
+    }
+    float mm = ml0.y > 0.f ? ml0.x : NEG_BIG;
+    for (int i = b + 32 + lane; i < e; i += 32) {
         const float2 ml = p.part_ml[__ldg(p.merge_slots + i)];
         if (ml.y > 0.f) mm = fmaxf(mm, ml.x);
     }
 #pragma unroll
     for (int off = 16; off >= 1; off >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, off));
-    // pass 2: weights and the weighted sums
+
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float ll = 0.f;
     for (int base = b; base < e; base += 32) {
-        const int i = base + lane;
-        int slot = -1;
-        float w = 0.f;
-        if (i < e) {
-            slot = __ldg(p.merge_slots + i);
-            const float2 ml = p.part_ml[slot];
-            if (ml.y > 0.f) {  // an empty piece has no O row
-                w = fast_exp2(ml.x - mm);
-                ll = fmaf(w, ml.y, ll);
-            } else {
-                slot = -1;
+        int slot = slot0;
+        float2 ml = ml0;
+        if (base != b) {
+            slot = -1;
+            ml = make_float2(NEG_BIG, 0.f);
+            if (base + lane < e) {
+                slot = __ldg(p.merge_slots + base + lane);
+                ml = p.part_ml[slot];
             }
         }
+        float w = 0.f;
+        if (ml.y > 0.f) {  // an empty piece has no O row
+            w = fast_exp2(ml.x - mm);
+            ll = fmaf(w, ml.y, ll);
+        } else {
+            slot = -1;
+        }
         const int n = min(32, e - base);
-        for (int k0 = 0; k0 < n; k0 += 4) {
-            float4 v[4];
-            float wk[4];
+        for (int k0 = 0; k0 < n; k0 += 8) {
+            float4 v[8];
+            float wk[8];
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
+            for (int u = 0; u < 8; u++) {
                 const int sk = __shfl_sync(0xffffffffu, slot, (k0 + u) & 31);
                 wk[u] = __shfl_sync(0xffffffffu, w, (k0 + u) & 31);
                 const bool live = (k0 + u < n) && sk >= 0;
@@ -847,7 +857,7 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeParams p) {
                             : make_float4(0.f, 0.f, 0.f, 0.f);
             }
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
+            for (int u = 0; u < 8; u++) {
                 acc.x = fmaf(wk[u], v[u].x, acc.x);
                 acc.y = fmaf(wk[u], v[u].y, acc.y);
                 acc.z = fmaf(wk[u], v[u].z, acc.z);
