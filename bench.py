@@ -40,6 +40,7 @@ def parse():
     ap.add_argument("--tails", default="tensor", choices=["tensor", "simt"],
                     help="private tails on tensor cores (default) or on CUDA cores")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-ref-cuda", action="store_true", help="skip timing the reference's own CUDA kernels")
     return ap.parse_args()
 
 
@@ -189,6 +190,42 @@ def run_reference_arm(args):
             "e2e": {"value": base["value"], "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line))
+
+
+def time_reference_cuda(name, dev, steps, warmup):
+    """The reference's own CUDA kernels (unmodified sources recompiled for sm_100a into oracle/_ref/cuda)
+    on the same workload, same GPU, same run: CUDA events around `steps` forwards.  Its chunk-first
+    kernel reads q rows past the batch, so q is the head of a zero-padded buffer; it only supports
+    batches of 16/32/48/64/96/128 rows with sharing."""
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    from ref_loader import load_reference
+    from chunk_attn import workloads as W
+    ref = load_reference("cuda")
+    if ref is None:
+        return {"us_per_step": None, "note": "oracle/_ref/cuda is not built"}
+    w = make_workload(name, total_heads(name), "cpu" if name == "cfg2" else dev)
+    if w.n_seqs > 128:
+        return {"us_per_step": None, "note": "the reference's chunk-first kernel supports at most 128 rows"}
+    chunk_bytes = w.n_heads * 2 * 64 * 128 * 2
+    n_chunks = W.unique_kv_bytes(w) // chunk_bytes + w.n_seqs + 8
+    ra = ref.Attention(n_heads=w.n_heads, d_head=128, chunk_size=64, memory_mb=(n_chunks * chunk_bytes >> 20) + 2,
+                       dtype=torch.float16, device=dev)
+    rows = W.populate(ra, w, device=dev, dtype=torch.float16)
+    qbuf = torch.zeros(w.n_seqs + 160, w.n_heads, 128, device=dev, dtype=torch.float16)
+    qbuf[:w.n_seqs] = w.q[rows].to(dev, torch.float16)
+    q = qbuf[:w.n_seqs]
+    for _ in range(max(3, warmup)):
+        ra.forward(q)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        ra.forward(q)
+    e1.record()
+    torch.cuda.synchronize()
+    return {"us_per_step": e0.elapsed_time(e1) / steps * 1e3, "steps": steps,
+            "note": "reference CUDA kernels recompiled for sm_100a, same inputs, same GPU, same run"}
 
 
 # ---- this engine --------------------------------------------------------------------------------------------------
@@ -374,6 +411,13 @@ def run_b200(args):
                 "clocks": clocks, "device_status": status}
         if single:
             line["strong_scaling_ref"] = single
+        if world == 1 and not args.no_ref_cuda:
+            try:
+                del attn, engine
+                torch.cuda.empty_cache()
+                line["reference_cuda"] = time_reference_cuda(name, dev, min(K, 100), W_)
+            except Exception as exc:  # reported, never a gate
+                line["reference_cuda"] = {"us_per_step": None, "note": "failed: %s" % str(exc)[:200]}
         if not args.no_cpu_baseline and world == 1:
             try:
                 line["cpu_baseline"], _ = time_reference_cpu(name, 10, 1, max_seconds=25.0)

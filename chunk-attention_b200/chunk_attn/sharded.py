@@ -60,11 +60,12 @@ class HeadShardedAttention:
         if self.world == 1:
             return out_local
         n = out_local.shape[0]
-        shape = (self.world, n, self.h_local, self.d_head)
+        shape = (self.world * n, self.h_local, self.d_head)  # rank-major concatenation along dim 0
         if self._gather_buf is None or self._gather_buf.shape != shape or self._gather_buf.dtype != out_local.dtype:
             self._gather_buf = torch.empty(shape, dtype=out_local.dtype, device=out_local.device)
         dist.all_gather_into_tensor(self._gather_buf, out_local.contiguous(), group=self.group)
-        return self._gather_buf.permute(1, 0, 2, 3).reshape(n, self.n_heads, self.d_head)
+        return self._gather_buf.view(self.world, n, self.h_local, self.d_head).permute(1, 0, 2, 3).reshape(
+            n, self.n_heads, self.d_head)
 
     def forward(self, q, partition=0, gather=True):
         out = self.forward_local(q, partition)

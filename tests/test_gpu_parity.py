@@ -6,6 +6,7 @@ engine accumulates in fp32, so 1e-3 is asserted (and far less is observed).  fp3
 oracle: max-abs 1e-4.
 """
 import math
+import os
 
 import numpy as np
 import pytest
@@ -365,3 +366,23 @@ def test_against_reference_cuda_kernels():
     torch.cuda.synchronize()
     out = attn.forward(q=q)
     assert (out.float() - out_ref.float()).abs().max().item() < 2e-3
+
+
+# ---- golden vectors of the unmodified reference ---------------------------------------------------------------
+from golden_replay import fixtures, replay  # noqa: E402
+from workloads import tails_shape, tree_shape  # noqa: E402
+
+
+@pytest.mark.parametrize("path", fixtures(), ids=lambda p: os.path.basename(p)[:-4])
+def test_engine_reproduces_reference_golden_vectors(path):
+    # fp32 engine (any-geometry kernel) through the C ABI against outputs of the reference's MKL path
+    engines = []
+
+    def make(H, d, C):
+        engines.append(CabiEngine(H, d, C, torch.float32, max_chunks=256))
+        return engines[-1]
+
+    worst = replay(path, make, tol=TOL_F32, tree_of=lambda e: tree_shape(e.tree.get_trie()),
+                   tails_of=lambda e: tails_shape(e.tree.tails), to_input=torch.from_numpy,
+                   to_numpy=lambda t: t.float().cpu().numpy())
+    assert worst < TOL_F32 and engines[0].ctx.status() == 0
