@@ -144,7 +144,14 @@ def time_reference_cpu(name, steps, warmup, max_seconds=150.0):
     scale_up = heads_full / heads
     w = make_workload(name, heads, "cpu")
     ref = load_reference("cpu")
-    cores = torch.get_num_threads()
+    # all the host threads the process may use (torchrun exports OMP_NUM_THREADS=1 to its workers; the
+    # reference sizes its OpenMP team from torch's thread count when a cache is constructed)
+    try:
+        avail = len(os.sched_getaffinity(0))
+    except AttributeError:
+        avail = os.cpu_count() or 1
+    cores = max(torch.get_num_threads(), avail)
+    torch.set_num_threads(cores)
     if ref is not None:
         kind = "reference"
         need_mb = int(W.unique_kv_bytes(w) * 2 / 2 ** 20 * 1.1) + w.n_seqs * 2 + 64  # fp32 pool + empty tails
@@ -189,7 +196,7 @@ def run_reference_arm(args):
             "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line))
+    emit(line)
 
 
 def time_reference_cuda(name, dev, steps, warmup):
@@ -387,7 +394,9 @@ def run_b200(args):
             achieved = ukv_local / (dur_ms * 1e-3) / 1e9
             roof = {"bound": "hbm", "kernel": "attn_partial_kernel", "achieved": achieved, "peak": peak,
                     "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
-                    "traffic": None,  # dram bytes per launch: see profiles/ (ncu capture)
+                    # dram__bytes_read.sum + dram__bytes_write.sum of one launch from the ncu capture summarised
+                    # in profiles/attn_partial_kernel_cfg2.md (302.98 MB + 10.5 MB); only that workload was captured
+                    "traffic": 313.5e6 if (name == "cfg2" and world == 1) else None,
                     "algorithmic_bytes_per_launch": ukv_local,
                     "kernel_ms": {"partials_mean": dur_ms, "partials_min": min(kern["partials"]),
                                   "merge_mean": statistics.mean(kern["merge"])}}
@@ -424,13 +433,26 @@ def run_b200(args):
             except Exception as exc:  # the baseline is reported, never a gate
                 line["cpu_baseline"] = {"value": None, "unit": "us", "cores": 0, "kind": "unavailable",
                                         "sample": "failed: %s" % exc}
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
 
+def emit(line):
+    """The one JSON line goes to the process's original stdout; everything else any library prints
+    (NCCL's version banner, the reference's logger) was diverted to stderr in main()."""
+    os.write(_REAL_STDOUT, (json.dumps(line) + "\n").encode())
+
+
+_REAL_STDOUT = 1
+
+
 def main():
+    global _REAL_STDOUT
     args = parse()
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)  # C-level and Python-level prints now land on stderr
     if args.impl == "reference":
         run_reference_arm(args)
     else:
