@@ -76,6 +76,79 @@ def total_heads(name):
     return 64 if name == "cfg5" else 32
 
 
+def run_cfg4(args):
+    """Two-level prefix tree with incremental decode (configuration 4): 128 sequences in 4 groups,
+    64 decode steps of append_token + forward, 8 sequences replaced every 16 steps.  Reports the whole
+    step (append + lazy work-list rebuild + forward) and the forward alone, both with CUDA events, and
+    the host time of the work-list rebuilds."""
+    import torch
+    from chunk_attn import Attention, workloads as W
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    cfg = W.Config4(gen_device=dev)
+    attn = Attention(n_heads=32, d_head=128, chunk_size=64, memory_mb=1400, dtype=torch.float16, device=dev)
+    seqs = []
+
+    def add(segs):
+        tokens, k, v = W.cat_segments(segs, device=dev, dtype=torch.float16)
+        seqs.insert(attn.add_seq(tokens=tokens, k=k, v=v), segs)
+
+    for segs in cfg.initial():
+        add(segs)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    step_ms, fwd_ms, refresh_host_ms, ukv = [], [], [], []
+    for rep in range(max(1, args.steps // cfg.steps) + 1):   # first pass over the 64 steps is the warm-up
+        for step in range(cfg.steps):
+            if step and step % cfg.churn_every == 0:
+                for _ in range(cfg.churn):
+                    i = cfg.rng.randrange(len(seqs))
+                    attn.remove_seq(i)
+                    seqs.pop(i)
+                for _ in range(cfg.churn):
+                    add(cfg.new_sequence(cfg.rng.randrange(cfg.n_groups)))
+            q, nk, nv = (t.to(torch.float16) for t in cfg.step_inputs(len(seqs)))
+            toks = [7_000_000 + step] * len(seqs)
+            torch.cuda.synchronize()
+            e0, e1, e2 = ev(), ev(), ev()
+            t0 = time.perf_counter()
+            e0.record()
+            attn.append_token(tokens=toks, k=nk, v=nv)
+            attn.refresh_kernel_context(False)
+            t1 = time.perf_counter()
+            e1.record()
+            out = attn.forward(q=q)
+            e2.record()
+            torch.cuda.synchronize()
+            if rep > 0:
+                step_ms.append(e0.elapsed_time(e2))
+                fwd_ms.append(e1.elapsed_time(e2))
+                refresh_host_ms.append((t1 - t0) * 1e3)
+                ukv.append(attn.plan_stats()["unique_kv_bytes"])
+        # shrink back to the initial state so that every pass sees the same sizes
+        while seqs:
+            attn.remove_seq(len(seqs) - 1)
+            seqs.pop()
+        cfg = W.Config4(gen_device=dev)
+        for segs in cfg.initial():
+            add(segs)
+    peak, peak_src = measured_peak()
+    fwd = statistics.mean(fwd_ms)
+    line = {"metric": METRIC, "value": statistics.mean(step_ms) * 1e3, "unit": "us", "n_gpus": 1, "steps": len(step_ms),
+            "warmup": cfg.steps, "ms_per_step": statistics.mean(step_ms), "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "cfg4: H32 d128 c64 fp16, 128 seqs in 4 groups (1024 root + 1024 group + 256 unique), "
+                                   "64 decode steps appending 1 token/seq, 8 seqs replaced every 16 steps; value = append + "
+                                   "work-list rebuild + forward", "l2": "unique K/V (620-760 MB) exceeds the 126 MB L2"},
+            "forward_us": fwd * 1e3, "forward_us_median": statistics.median(fwd_ms) * 1e3,
+            "unique_kv_bytes_mean": statistics.mean(ukv),
+            "hbm_frac_forward": statistics.mean(ukv) / (fwd * 1e-3) / 1e9 / peak, "peak_source": peak_src,
+            "host_ms_append_and_rebuild": {"mean": statistics.mean(refresh_host_ms), "max": max(refresh_host_ms),
+                                           "median": statistics.median(refresh_host_ms)},
+            "gpu_launches": len(step_ms) * 3, "device_status": attn.device_status()}
+    emit(line)
+
+
+
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -455,6 +528,8 @@ def main():
     os.dup2(2, 1)  # C-level and Python-level prints now land on stderr
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "cfg4":
+        run_cfg4(args)
     else:
         run_b200(args)
 
