@@ -41,6 +41,8 @@ def parse():
                     help="private tails on tensor cores (default) or on CUDA cores")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ref-cuda", action="store_true", help="skip timing the reference's own CUDA kernels")
+    ap.add_argument("--gather", default="nccl", choices=["nccl", "p2p"],
+                    help="N > 1: all-gather with NCCL, or rows stored into peers' outputs by the merge kernel")
     return ap.parse_args()
 
 
@@ -339,7 +341,8 @@ def run_b200(args):
         n_chunks = W.unique_kv_bytes(w) // chunk_bytes + w.n_seqs + 8   # + one empty tail per sequence
         need_mb = (n_chunks * chunk_bytes + 2 ** 20 - 1) // 2 ** 20 + 1
         if sharded:
-            attn = HeadShardedAttention(H, 128, 64, memory_mb=need_mb, dtype=torch.float16, device=dev)
+            attn = HeadShardedAttention(H, 128, 64, memory_mb=need_mb, dtype=torch.float16, device=dev,
+                                        gather=args.gather)
             engine = attn.local
         else:
             attn = Attention(n_heads=n_heads_local, d_head=128, chunk_size=64, memory_mb=need_mb,
@@ -481,7 +484,7 @@ def run_b200(args):
                 "dtype": "f16", "data": "synthetic",
                 "config": {"workload": describe(name, world), "l2": "unique K/V per GPU (%.0f MB) exceeds the 126 MB L2: no flush between steps" % (ukv_local / 1e6)
                            if ukv_local > 126e6 else "unique K/V per GPU (%.0f MB) fits in L2" % (ukv_local / 1e6),
-                           "parallelism": "heads/%d" % world, "phases": "split" if args.split_phases else "fused", "tails": args.tails,
+                           "parallelism": "heads/%d" % world, "gather": args.gather if world > 1 else None, "phases": "split" if args.split_phases else "fused", "tails": args.tails,
                            "plan": stats},
                 "unique_kv_bytes": ukv_total,
                 "unique_kv_gbs_per_gpu": ukv_local / (ms * 1e-3) / 1e9,

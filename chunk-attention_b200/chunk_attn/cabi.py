@@ -24,7 +24,7 @@ PLAN_ITEMS = 0
 EXPORTED = [
     "ca_last_error", "ca_version", "ca_chunk_bytes", "ca_tile_elem_offset", "ca_context_create",
     "ca_context_destroy", "ca_context_set_option", "ca_refresh_kernel_context", "ca_append_kv",
-    "ca_context_delta_tokens", "ca_attention", "ca_attn_partials", "ca_attn_merge",
+    "ca_context_delta_tokens", "ca_attention", "ca_attention_to_peers", "ca_attn_partials", "ca_attn_merge",
     "ca_scatter_prefill", "ca_copy_chunks", "ca_read_chunk", "ca_status_read", "ca_context_stats",
     "ca_context_read_trace",
     "ca_plan_build", "ca_plan_array", "ca_plan_stats_get", "ca_plan_destroy", "ca_attention_static",
@@ -70,6 +70,7 @@ def _load():
         "ca_append_kv": (i32, [vp, vp, vp, i32, vp]),
         "ca_context_delta_tokens": (i32, [vp]),
         "ca_attention": (i32, [vp, vp, vp, i32, i32, vp]),
+        "ca_attention_to_peers": (i32, [vp, vp, C.POINTER(vp), i32, i32, i32, i32, vp]),
         "ca_attn_partials": (i32, [vp, vp, i32, i32, vp]),
         "ca_attn_merge": (i32, [vp, vp, i32, vp]),
         "ca_scatter_prefill": (i32, [vp, vp, vp, i64, i64, i32, i32, C.POINTER(C.c_int32), vp]),
@@ -168,6 +169,11 @@ class Context:
 
     def attention(self, q, out, partition=0):
         check(lib.ca_attention(self._h, q.data_ptr(), out.data_ptr(), q.shape[0], partition, self._stream()))
+
+    def attention_to_peers(self, q, peer_ptrs, total_heads, head_offset):
+        arr = (C.c_void_p * len(peer_ptrs))(*peer_ptrs)
+        check(lib.ca_attention_to_peers(self._h, q.data_ptr(), arr, len(peer_ptrs), total_heads, head_offset,
+                                        q.shape[0], self._stream()))
 
     def attn_partials(self, q, phases=3):
         check(lib.ca_attn_partials(self._h, q.data_ptr(), q.shape[0], phases, self._stream()))

@@ -3,8 +3,12 @@
 Attention heads are independent, so rank r of G owns heads [r*H/G, (r+1)*H/G) of q, k, v, of every
 chunk and of the output.  Every rank replays the identical add / append / remove trace on its own
 `Attention(n_heads=H/G)`: the prefix tree is replicated and deterministic, so row indices agree
-everywhere without any metadata exchange.  The only collective is the optional all-gather of the
-[n_seqs, H/G, d] output slices (NCCL over NVLink), followed by the permute to [n_seqs, H, d].
+everywhere without any metadata exchange.  The only exchange is the optional gather of the [n_seqs, H/G, d] output slices into [n_seqs, H, d]
+on every rank, in one of two ways:
+  gather="nccl"  all_gather_into_tensor (NCCL over NVLink) followed by a permute;
+  gather="p2p"   the merge kernel itself stores every output row into each rank's full-width buffer
+                 (symmetric memory, plain peer stores over NVLink), followed by one barrier on the
+                 stream: compute and gather in a single kernel, no collective call and no permute.
 The reference itself is single-device (no torch.distributed anywhere in it).
 """
 import torch
@@ -13,7 +17,7 @@ import torch.distributed as dist
 
 class HeadShardedAttention:
     def __init__(self, n_heads, d_head, chunk_size, memory_mb=1024, share_prefix=True, tpp_threshold=1,
-                 dtype=None, device=None, group=None, attention_factory=None):
+                 dtype=None, device=None, group=None, attention_factory=None, gather="nccl"):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -29,6 +33,10 @@ class HeadShardedAttention:
                                        memory_mb=memory_mb, share_prefix=share_prefix,
                                        tpp_threshold=tpp_threshold, dtype=dtype, device=device)
         self._gather_buf = None
+        if gather not in ("nccl", "p2p"):
+            raise ValueError("gather must be 'nccl' or 'p2p'")
+        self.gather_mode = gather if self.world > 1 else "nccl"
+        self._symm = None      # (tensor [rows, H, d], handle, peer pointers)
 
     def _mine(self, t):
         """Accept full-width [*, H, d] tensors (sliced here) or already-local [*, H/G, d] ones."""
@@ -67,6 +75,34 @@ class HeadShardedAttention:
         return self._gather_buf.view(self.world, n, self.h_local, self.d_head).permute(1, 0, 2, 3).reshape(
             n, self.n_heads, self.d_head)
 
+    def _symm_buffers(self, n_rows, dtype, device):
+        """Two full-width output buffers in symmetric memory, used alternately, grown to the largest
+        batch seen (a collective: every rank reaches this at the same step because the trees are
+        replicated)."""
+        if self._symm is None or self._symm[0][0].shape[0] < n_rows:
+            import torch.distributed._symmetric_memory as symm_mem
+            rows = max(n_rows, 64)
+            group = self.group if self.group is not None else dist.group.WORLD
+            bufs = []
+            for _ in range(2):
+                buf = symm_mem.empty((rows, self.n_heads, self.d_head), dtype=dtype, device=device)
+                hdl = symm_mem.rendezvous(buf, group)
+                bufs.append((buf, hdl, [int(p) for p in hdl.buffer_ptrs]))
+            self._symm = bufs
+            self._step = 0
+        return self._symm
+
     def forward(self, q, partition=0, gather=True):
+        if gather and self.gather_mode == "p2p" and partition != 2:
+            ql = self._mine(q).contiguous()
+            # Buffer k & 1 for step k.  When a rank passes the barrier of step k + 1, every rank's stream
+            # has passed its reads of step k's buffer, so step k + 2 may overwrite it without a barrier
+            # of its own: one barrier per step.
+            buf, hdl, ptrs = self._symm_buffers(ql.shape[0], ql.dtype, ql.device)[self._step & 1]
+            self._step += 1
+            self.local.forward_to_peers(q=ql, peer_out_ptrs=ptrs, total_heads=self.n_heads,
+                                        head_offset=self.rank * self.h_local)
+            hdl.barrier(channel=0)   # every rank's rows have landed everywhere
+            return buf[:ql.shape[0]]
         out = self.forward_local(q, partition)
         return self.gather(out) if gather else out

@@ -395,6 +395,36 @@ int ca_attn_merge(ca_context* c, void* out, int n_seqs, ca_stream stream_) {
     return CA_OK;
 }
 
+int ca_attention_to_peers(ca_context* c, const void* q, void* const* peer_out, int n_peers, int total_heads,
+                          int head_offset, int n_seqs, ca_stream stream_) {
+    int rc = check_attention_args(c, q, n_seqs);
+    if (rc != CA_OK) return rc;
+    if (!c->fast) return fail(CA_ERR_INVALID, "writing into peers' outputs exists only for fp16 / d_head 128 / chunk_size 64");
+    if (n_peers < 1 || n_peers > ca::MERGE_MAX_PEERS || !peer_out) return fail(CA_ERR_INVALID, "1 to 8 peer outputs are required");
+    if (head_offset < 0 || total_heads < head_offset + c->geo.n_heads) return fail(CA_ERR_INVALID, "head slice outside the full width");
+    for (int i = 0; i < n_peers; i++)
+        if (!peer_out[i] || reinterpret_cast<uintptr_t>(peer_out[i]) % 8) return fail(CA_ERR_INVALID, "null or misaligned peer output");
+    if (n_seqs == 0) return CA_OK;
+    rc = ca_attn_partials(c, q, n_seqs, 3, stream_);
+    if (rc != CA_OK) return rc;
+    DeviceGuard guard(c->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    ca::MergeParams m;
+    m.part_o = c->part_o;
+    m.part_ml = c->part_ml;
+    m.merge_off = c->d_merge_off;
+    m.merge_slots = c->d_merge_slots;
+    m.out = nullptr;
+    m.n_pairs = n_seqs * c->geo.n_heads;
+    m.n_heads = c->geo.n_heads;
+    m.n_peers = n_peers;
+    m.total_heads = total_heads;
+    m.head_offset = head_offset;
+    for (int i = 0; i < n_peers; i++) m.peer_out[i] = peer_out[i];
+    CA_CUDA(ca::launch_attn_merge(m, static_cast<cudaStream_t>(stream_), true));
+    return CA_OK;
+}
+
 int ca_attention(ca_context* c, const void* q, void* out, int n_seqs, int partition, ca_stream stream_) {
     int rc = check_attention_args(c, q, n_seqs);
     if (rc != CA_OK) return rc;

@@ -873,7 +873,17 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeParams p) {
     uint2 packed;
     packed.x = *reinterpret_cast<const uint32_t*>(&h01);
     packed.y = *reinterpret_cast<const uint32_t*>(&h23);
-    *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.out) + (size_t)pair * FAST_D + 4 * lane) = packed;
+    if (p.n_peers == 0) {
+        *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.out) + (size_t)pair * FAST_D + 4 * lane) = packed;
+    } else {
+        // head-sharded: the row goes into every rank's full-width output (plain stores to peer memory)
+        const int row = pair / p.n_heads;
+        const int head = pair - row * p.n_heads;
+        const size_t off = ((size_t)row * p.total_heads + p.head_offset + head) * FAST_D + 4 * lane;
+#pragma unroll
+        for (int i = 0; i < MERGE_MAX_PEERS; i++)
+            if (i < p.n_peers) *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.peer_out[i]) + off) = packed;
+    }
 }
 
 }  // namespace

@@ -49,13 +49,21 @@ struct PartialParams {
 cudaError_t launch_attn_partials(const PartialParams& p, int n_ctas, cudaStream_t stream);
 cudaError_t configure_fast_kernels();  // once per device before the first launch
 
+constexpr int MERGE_MAX_PEERS = 8;
 struct MergeParams {
     const float* part_o;
     const float2* part_ml;
     const int32_t* merge_off;    // [n_rows * n_heads + 1]
     const int32_t* merge_slots;
-    void* out;                   // fp16 [n_rows, n_heads, 128]
+    void* out;                   // fp16 [n_rows, n_heads, 128]; unused when n_peers > 0
     int n_pairs;                 // n_rows * n_heads
+    // Head-sharded output written straight into every rank's full-width buffer (peer memory over
+    // NVLink): row s, local head h goes to peer_out[i] + ((s * total_heads) + head_offset + h) * 128.
+    int n_heads = 0;             // local heads (needed to split a pair index when n_peers > 0)
+    int n_peers = 0;             // 0: write `out` only
+    int total_heads = 0;
+    int head_offset = 0;
+    void* peer_out[MERGE_MAX_PEERS] = {};
 };
 cudaError_t launch_attn_merge(const MergeParams& p, cudaStream_t stream, bool dependent_launch);
 

@@ -180,6 +180,21 @@ torch::Tensor Attention::forward(torch::Tensor q, int partition) {
     return output;
 }
 
+void Attention::forward_to_peers(torch::Tensor q, const std::vector<int64_t>& peer_out_ptrs, int total_heads,
+                                 int head_offset) {
+    if (!q.is_contiguous()) throw std::runtime_error("q is not contiguous");
+    if (q.dim() != 3 || q.size(0) != (int64_t)tree_->n_seqs() || q.size(1) != n_heads_ || q.size(2) != d_head_ ||
+        q.device() != options_.device() || q.scalar_type() != c10::typeMetaToScalarType(options_.dtype()))
+        throw std::runtime_error("forward_to_peers: q must be [n_seqs, n_heads, d_head] with the dtype and device of the cache");
+    std::vector<void*> ptrs;
+    for (int64_t p : peer_out_ptrs) ptrs.push_back(reinterpret_cast<void*>(p));
+    c10::cuda::CUDAGuard guard(options_.device());
+    refresh_kernel_context(false);
+    check_rc(ca_attention_to_peers(ctx_, q.data_ptr(), ptrs.data(), (int)ptrs.size(), total_heads, head_offset,
+                                   (int)q.size(0), stream()),
+             "forward_to_peers");
+}
+
 void Attention::print(Chunk* root, int level) {
     if (root == nullptr) root = tree_->root();
     std::string indent(4 * level, ' ');

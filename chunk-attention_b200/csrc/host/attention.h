@@ -39,6 +39,9 @@ class Attention {
     int64_t peak_memory_allocated() const { return tree_->pool().peak_memory_allocated(); }
     void duplicate(int seq_idx, int copies);
     torch::Tensor forward(torch::Tensor q, int partition = 0);
+    // head-sharded forward: rows are written into every rank's full-width output buffer (device
+    // addresses this GPU can reach), this cache's heads landing at head_offset of total_heads
+    void forward_to_peers(torch::Tensor q, const std::vector<int64_t>& peer_out_ptrs, int total_heads, int head_offset);
 
     Chunk* get_trie() { return tree_->root(); }
     std::vector<Chunk*> tails() { return tree_->tails(); }

@@ -81,6 +81,8 @@ PYBIND11_MODULE(chunk_attn_c, m) {
       .def("plan_stats", [](Attention& a) { return stats_to_dict(a.plan_stats()); })
       .def("set_option", &Attention::set_option, py::arg("option"), py::arg("value"))
       .def("device_status", &Attention::device_status)
+      .def("forward_to_peers", &Attention::forward_to_peers, py::arg("q"), py::arg("peer_out_ptrs"),
+           py::arg("total_heads"), py::arg("head_offset"))
       .def("attn_partials", &Attention::attn_partials, py::arg("q"), py::arg("phases") = 3)
       .def("attn_merge", &Attention::attn_merge, py::arg("out"));
 

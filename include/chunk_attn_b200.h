@@ -117,6 +117,16 @@ CA_API int ca_context_delta_tokens(const ca_context* ctx);
 CA_API int ca_attention(ca_context* ctx, const void* q, void* out, int n_seqs, int partition,
                         ca_stream stream);
 
+/* Head-sharded variant of ca_attention (one process per GPU, this context holds n_heads of
+ * total_heads, starting at head_offset): the merge kernel writes every output row straight into
+ * each rank's full-width buffer peer_out[i], fp16 [n_seqs, total_heads, d_head], with plain stores
+ * to peer memory over NVLink — compute and gather in one kernel, no collective library call.
+ * peer_out is a HOST array of n_peers (<= 8) device pointers that this GPU can address (the rank's
+ * own buffer included); the caller orders the ranks before anyone reads (a barrier on the stream).
+ * No counterpart in the reference, which is single-device. */
+CA_API int ca_attention_to_peers(ca_context* ctx, const void* q, void* const* peer_out, int n_peers,
+                                 int total_heads, int head_offset, int n_seqs, ca_stream stream);
+
 /* The two halves of ca_attention, separately launchable (profiling, tests):
  * ca_attn_partials = chunk-first over shared runs + sequence-first over private tails, emitting
  * per-piece partial outputs with their running max and sum-of-exponentials

@@ -254,6 +254,24 @@ def test_config2_full_size_vs_oracle():
     assert st["n_shared_chunks"] == 32 and st["n_runs"] == 1 and st["kernels_per_step"] == 2
 
 
+def test_rows_written_into_peer_outputs():
+    # ca_attention_to_peers on one GPU: two local buffers stand in for two ranks' full-width outputs
+    w = W.single_level("peers", 4, 128, 64, torch.float16, 9, 3 * 64, 64 + 30, 95, 0.5)
+    eng = fast_engine(H=4)
+    rows = W.populate(eng, w)
+    q = w.q[rows].to("cuda", torch.float16).contiguous()
+    expected = eng.forward(q)
+    total_heads, head_offset = 12, 4
+    peers = [torch.full((9, total_heads, 128), float("nan"), dtype=torch.float16, device="cuda") for _ in range(2)]
+    eng.ctx.attention_to_peers(q, [p.data_ptr() for p in peers], total_heads, head_offset)
+    torch.cuda.synchronize()
+    for p in peers:
+        assert torch.equal(p[:, head_offset:head_offset + 4], expected)
+        assert torch.isnan(p[:, :head_offset]).all() and torch.isnan(p[:, head_offset + 4:]).all()
+    with pytest.raises(cabi.CAError):
+        eng.ctx.attention_to_peers(q, [peers[0].data_ptr()], 6, 4)   # the slice does not fit in 6 heads
+
+
 # ---- the drop-in class ------------------------------------------------------------------------------------
 def test_attention_class_matches_cabi_engine_and_reference_api():
     torch.set_default_dtype(torch.float32)
