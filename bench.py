@@ -41,7 +41,7 @@ def parse():
                     help="private tails on tensor cores (default) or on CUDA cores")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ref-cuda", action="store_true", help="skip timing the reference's own CUDA kernels")
-    ap.add_argument("--gather", default="nccl", choices=["nccl", "p2p"],
+    ap.add_argument("--gather", default="p2p", choices=["nccl", "p2p"],
                     help="N > 1: all-gather with NCCL, or rows stored into peers' outputs by the merge kernel")
     return ap.parse_args()
 
@@ -362,6 +362,26 @@ def run_b200(args):
         return attn, engine, q, ukv
 
     attn, engine, q, ukv_local = build(h_local, world > 1)
+    gather_note = None
+    if world > 1 and args.gather == "p2p":
+        # the peer-store path must give exactly what the NCCL all-gather gives; if symmetric memory cannot
+        # be set up on this machine, say so and time the NCCL path instead
+        try:
+            out_p2p = attn.forward(q, gather=True).clone()
+            out_nccl = attn.gather(attn.forward_local(q))
+            ok = torch.equal(out_p2p, out_nccl)
+            flag = torch.tensor([1 if ok else 0], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag.item()) != 1:
+                raise SystemExit("p2p gather differs from the NCCL all-gather")
+            gather_note = "p2p (verified equal to the NCCL all-gather on this batch)"
+        except SystemExit:
+            raise
+        except Exception as exc:
+            attn.gather_mode = "nccl"
+            gather_note = "nccl (p2p unavailable: %s)" % str(exc)[:120]
+    elif world > 1:
+        gather_note = "nccl"
     stats = engine.plan_stats()
     assert stats["unique_kv_bytes"] == ukv_local
     step = (lambda: attn.forward(q, gather=True)) if world > 1 else (lambda: attn.forward(q=q))
@@ -484,7 +504,7 @@ def run_b200(args):
                 "dtype": "f16", "data": "synthetic",
                 "config": {"workload": describe(name, world), "l2": "unique K/V per GPU (%.0f MB) exceeds the 126 MB L2: no flush between steps" % (ukv_local / 1e6)
                            if ukv_local > 126e6 else "unique K/V per GPU (%.0f MB) fits in L2" % (ukv_local / 1e6),
-                           "parallelism": "heads/%d" % world, "gather": args.gather if world > 1 else None, "phases": "split" if args.split_phases else "fused", "tails": args.tails,
+                           "parallelism": "heads/%d" % world, "gather": gather_note, "phases": "split" if args.split_phases else "fused", "tails": args.tails,
                            "plan": stats},
                 "unique_kv_bytes": ukv_total,
                 "unique_kv_gbs_per_gpu": ukv_local / (ms * 1e-3) / 1e9,
