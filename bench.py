@@ -41,6 +41,7 @@ def parse():
                     help="private tails on tensor cores (default) or on CUDA cores")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ref-cuda", action="store_true", help="skip timing the reference's own CUDA kernels")
+    ap.add_argument("--no-scale-point", action="store_true", help="N = 1: skip the one-GPU point of the cfg5 series")
     ap.add_argument("--gather", default="p2p", choices=["nccl", "p2p"],
                     help="N > 1: all-gather with NCCL, or rows stored into peers' outputs by the merge kernel")
     return ap.parse_args()
@@ -334,9 +335,10 @@ def run_b200(args):
         raise SystemExit("%d heads do not split over %d GPUs" % (H, world))
     h_local = H // world
 
-    def build(n_heads_local, sharded):
-        gen_device = "cpu" if name == "cfg2" else dev
-        w = make_workload(name, n_heads_local, gen_device, rank if sharded else 0)
+    def build(n_heads_local, sharded, wname=None):
+        wname = wname or name
+        gen_device = "cpu" if wname == "cfg2" else dev
+        w = make_workload(wname, n_heads_local, gen_device, rank if sharded else 0)
         chunk_bytes = n_heads_local * 2 * 64 * 128 * 2
         n_chunks = W.unique_kv_bytes(w) // chunk_bytes + w.n_seqs + 8   # + one empty tail per sequence
         need_mb = (n_chunks * chunk_bytes + 2 ** 20 - 1) // 2 ** 20 + 1
@@ -516,6 +518,29 @@ def run_b200(args):
                 "clocks": clocks, "device_status": status}
         if single:
             line["strong_scaling_ref"] = single
+        if world == 1 and args.workload == "auto" and not args.no_scale_point:
+            # The multi-GPU runs of this benchmark use cfg5 (strong scaling over heads).  Its one-GPU point,
+            # measured here in the same run, is what their values compare with — not `value` above.
+            try:
+                del attn, engine
+                torch.cuda.empty_cache()
+                a5, _, q5, ukv5 = build(total_heads("cfg5"), False, "cfg5")
+                for _ in range(5):
+                    a5.forward(q=q5)
+                torch.cuda.synchronize()
+                e0.record()
+                for _ in range(30):
+                    a5.forward(q=q5)
+                e1.record()
+                torch.cuda.synchronize()
+                us5 = e0.elapsed_time(e1) / 30 * 1e3
+                line["scale_series_n1"] = {"workload": describe("cfg5", 1), "us_per_step": us5, "steps": 30,
+                                           "hbm_frac_whole_step": ukv5 / (us5 * 1e-6) / 1e9 / peak}
+                del a5, q5
+                attn = engine = None
+                torch.cuda.empty_cache()
+            except Exception as exc:
+                line["scale_series_n1"] = {"us_per_step": None, "note": "failed: %s" % str(exc)[:200]}
         if world == 1 and not args.no_ref_cuda:
             try:
                 del attn, engine
