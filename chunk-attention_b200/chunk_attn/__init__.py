@@ -10,4 +10,4 @@ __version__ = "1.0.0b200"
 import torch  # noqa: F401  (libtorch must be loaded before the extension)
 
 from .lib.chunk_attn_c import *  # noqa: F401,F403
-from .lib.chunk_attn_c import Attention, Chunk, PrefixTree  # noqa: F401
+from .lib.chunk_attn_c import Attention, Chunk, PrefixTree, ops  # noqa: F401

@@ -28,6 +28,7 @@ EXPORTED = [
     "ca_scatter_prefill", "ca_copy_chunks", "ca_read_chunk", "ca_status_read", "ca_context_stats",
     "ca_context_read_trace",
     "ca_plan_build", "ca_plan_array", "ca_plan_stats_get", "ca_plan_destroy", "ca_attention_static",
+    "ca_rms_norm", "ca_fused_add_rms_norm", "ca_rotary_embedding",
 ]
 CA_STATIC_MAX_SLOTS = 16384
 
@@ -83,6 +84,9 @@ def _load():
         "ca_plan_array": (i32, [vp, i32, C.POINTER(C.POINTER(C.c_int32)), C.POINTER(i64)]),
         "ca_plan_stats_get": (i32, [vp, C.POINTER(PlanStats)]),
         "ca_plan_destroy": (None, [vp]),
+        "ca_rms_norm": (i32, [vp, vp, vp, C.c_float, i64, i32, i32, vp]),
+        "ca_fused_add_rms_norm": (i32, [vp, vp, vp, C.c_float, i64, i32, i32, vp]),
+        "ca_rotary_embedding": (i32, [vp, vp, vp, vp, i32, i64, i64, i32, i32, i32, i64, i32, i32, vp]),
         "ca_attention_static": (i32, [vp, i32, vp, vp, i32, vp, i32, i32, vp, vp, i32, i32, vp, vp]),
     }
     for name, (res, args) in sig.items():

@@ -13,6 +13,10 @@ using ca_host::Attention;
 using ca_host::Chunk;
 using ca_host::PrefixTree;
 
+namespace ca_host {
+void init_ops(py::module& m);
+}
+
 namespace {
 
 py::dict stats_to_dict(const ca_plan_stats& st) {
@@ -85,6 +89,10 @@ PYBIND11_MODULE(chunk_attn_c, m) {
            py::arg("total_heads"), py::arg("head_offset"))
       .def("attn_partials", &Attention::attn_partials, py::arg("q"), py::arg("phases") = 3)
       .def("attn_merge", &Attention::attn_merge, py::arg("out"));
+
+    // the reference carries this submodule whenever it is built for CUDA (python_exports.cpp:83-86)
+    py::module ops = m.def_submodule("ops");
+    ca_host::init_ops(ops);
 
     py::class_<PrefixTree>(m, "PrefixTree", py::module_local())
       .def(py::init([](int chunk_size, int64_t max_chunks, bool share_prefix) {

@@ -183,6 +183,27 @@ typedef struct ca_plan_stats {
 } ca_plan_stats;
 CA_API int ca_context_stats(const ca_context* ctx, ca_plan_stats* out);
 
+/* ---- element-wise companions (`chunk_attn.ops`) ----------------------------------------------------
+ * The three kernels the reference's model code imports from the same extension module
+ * (cpp/chunk_attn/python_exports_ops.cpp:11-19).  fp16 or fp32, device pointers, rows contiguous.
+ *
+ * ca_rms_norm: out[t, :] = round(input[t, :] * rsqrt(mean(input[t, :]^2) + epsilon)) * weight
+ *   (replaces vllm::rms_norm, cpp/chunk_attn/layernorm_kernels.cu:83-105).
+ * ca_fused_add_rms_norm: residual += input (rounded), then input = rms_norm(residual) * weight, in place
+ *   (replaces vllm::fused_add_rms_norm, layernorm_kernels.cu:107-129).
+ * ca_rotary_embedding: rotates the first rot_dim elements of every head of query and key in place by the
+ *   angle of the token's position; cos_sin_cache is [max_position, rot_dim] = [cos | sin] per position;
+ *   query_stride / key_stride are the element strides between tokens; is_neox pairs (i, i + rot_dim/2),
+ *   otherwise (2i, 2i + 1) (replaces vllm::rotary_embedding, cpp/chunk_attn/pos_encoding_kernels.cu:94-139). */
+CA_API int ca_rms_norm(void* out, const void* input, const void* weight, float epsilon, int64_t num_tokens,
+                       int hidden_size, int dtype, ca_stream stream);
+CA_API int ca_fused_add_rms_norm(void* input, void* residual, const void* weight, float epsilon,
+                                 int64_t num_tokens, int hidden_size, int dtype, ca_stream stream);
+CA_API int ca_rotary_embedding(const int64_t* positions, void* query, void* key, const void* cos_sin_cache,
+                               int rot_dim, int64_t query_stride, int64_t key_stride, int num_heads,
+                               int num_kv_heads, int head_size, int64_t num_tokens, int is_neox, int dtype,
+                               ca_stream stream);
+
 /* ---- allocation-free decode step ---------------------------------------------------------------
  * No counterpart in the reference: this entry point exists for callers that cannot allocate device
  * memory when they reach the decode step, for instance a plugin inside a serving process whose
