@@ -27,12 +27,17 @@ template <> struct Elem<float> {
 template <> struct Elem<__half> {
     static __device__ __forceinline__ float to_f(__half x) { return __half2float(x); }
     static __device__ __forceinline__ __half from_f(float x) { return __float2half_rn(x); }
-    static __device__ __forceinline__ __half mul(__half a, __half b) { return __hmul(a, b); }
+    // Each product and sum goes through float and back, one rounding to fp16 per operation, exactly
+    // as the reference's element type does on the device; plain fp16 intrinsics without a rounding
+    // modifier could be fused into one multiply-add with a single rounding.
+    static __device__ __forceinline__ __half mul(__half a, __half b) {
+        return __float2half_rn(__half2float(a) * __half2float(b));
+    }
     static __device__ __forceinline__ __half rot_x(__half x, __half y, __half c, __half s) {
-        return __hsub(__hmul(x, c), __hmul(y, s));
+        return __float2half_rn(__half2float(mul(x, c)) - __half2float(mul(y, s)));
     }
     static __device__ __forceinline__ __half rot_y(__half x, __half y, __half c, __half s) {
-        return __hadd(__hmul(y, c), __hmul(x, s));
+        return __float2half_rn(__half2float(mul(y, c)) + __half2float(mul(x, s)));
     }
 };
 
