@@ -77,7 +77,8 @@ int Attention::add_seq(const std::vector<int>& tokens, torch::Tensor k, torch::T
     if (k.dim() != 3 || v.dim() != 3 || k.size(0) != v.size(0) || k.size(1) != n_heads_ || v.size(1) != n_heads_ ||
         k.size(2) != d_head_ || v.size(2) != d_head_)
         throw std::runtime_error("add_seq: k and v must be [n_tokens, n_heads, d_head]");
-    if (k.size(0) != (int64_t)tokens.size()) throw std::runtime_error("add_seq: one K/V row per token is required");
+    // rows past the last token (a right-padded prompt) are ignored, as the reference's slices do
+    if (k.size(0) < (int64_t)tokens.size()) throw std::runtime_error("add_seq: one K/V row per token is required");
     std::vector<NewChunk> created;
     const int seq_idx = tree_->add_seq(tokens, created);
     valid_ = false;
