@@ -12,7 +12,7 @@ Workloads (synthetic, seeded; chunk_attn/workloads.py):
          K/V, larger than the 126 MB L2, so nothing needs flushing between steps)
   N > 1  cfg5: H64 split evenly over the ranks, 256 sequences = 4096 shared + 1024 unique tokens,
          output all-gathered (NCCL); strong scaling: total work is fixed
-`--workload` overrides the choice (cfg2, cfg5, cfg3_s<shared>).
+`--workload` overrides the choice (cfg2, cfg5, cfg3_s<shared>, cfg4, llama: the decoder loop).
 """
 import argparse
 import json
@@ -42,6 +42,12 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ref-cuda", action="store_true", help="skip timing the reference's own CUDA kernels")
     ap.add_argument("--no-scale-point", action="store_true", help="N = 1: skip the one-GPU point of the cfg5 series")
+    ap.add_argument("--llama-batch", type=int, default=64)
+    ap.add_argument("--llama-prompt", type=int, default=1024)
+    ap.add_argument("--llama-shared", type=int, default=0)
+    ap.add_argument("--llama-completion", type=int, default=64)
+    ap.add_argument("--runs", type=int, default=3, help="llama workload: timed repetitions")
+    ap.add_argument("--warmup-runs", type=int, default=1, help="llama workload: untimed repetitions")
     ap.add_argument("--gather", default="p2p", choices=["nccl", "p2p"],
                     help="N > 1: all-gather with NCCL, or rows stored into peers' outputs by the merge kernel")
     return ap.parse_args()
@@ -150,6 +156,93 @@ def run_cfg4(args):
             "gpu_launches": len(step_ms) * 3, "device_status": attn.device_status()}
     emit(line)
 
+
+
+def run_llama(args):
+    """The reference's offline decoder benchmark (tests/benchmark_chunk_attn.py:131-175): a ONE-layer
+    Llama-7B-shaped decoder (hidden 4096, 32 heads, MLP 11008, vocabulary 32000; random weights, there
+    are no checkpoints here), `batch` prompts of `n_prompt` tokens of which `n_shared` are common,
+    prefill + `n_completion` greedy decode steps; tokens/s = batch * n_completion / wall time of
+    prefill + decode, as the reference computes it.  The decode step is also split with CUDA events
+    into the attention calls (append_token + forward) and the rest (GEMMs, norms, rotary, sampling)."""
+    import random
+    import torch
+    from chunk_attn.models.llama_hf import LlamaConfig, LlamaForCausalLM
+    from chunk_attn.models.sequence import Sequence
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    batch, n_prompt, n_completion = args.llama_batch, args.llama_prompt, args.llama_completion
+    n_shared = args.llama_shared
+    cfg = LlamaConfig(num_hidden_layers=1, chunk_attn_kvcache_gb=8.0, torch_dtype=torch.float16, torch_device="cuda:0")
+    model = LlamaForCausalLM(cfg, seed=0).to(device=dev, dtype=torch.float16).eval()
+    rnd = random.Random(0)
+
+    def prompts():
+        return [[42] * n_shared + [rnd.randint(10, 100) for _ in range(n_prompt - n_shared)] for _ in range(batch)]
+
+    model([Sequence(prompt_tokens=[42])], None, prefill=True)  # warm-up of the GEMM paths, as the reference does
+    kv_caches = model.create_kv_caches()
+    attn_ms = []
+    kv = kv_caches[0]
+    orig_append, orig_forward = kv.append_token, kv.forward
+
+    class Timed:
+        """Stands in front of the layer's cache: CUDA events around append_token .. forward."""
+        def __init__(self):
+            self.pairs = []
+        def __getattr__(self, name):
+            return getattr(kv, name)
+        def append_token(self, **kw):
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self._e0 = e
+            return orig_append(**kw)
+        def forward(self, **kw):
+            out = orig_forward(**kw)
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self.pairs.append((self._e0, e))
+            return out
+
+    runs = []
+    for rep in range(args.warmup_runs + args.runs):
+        for c in kv_caches:
+            c.clear()
+        timed = Timed()
+        seq_ids = prompts()
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        seqs = [Sequence(prompt_tokens=p) for p in seq_ids]
+        new_tokens = model(seqs, [timed], prefill=True)
+        for s, t in zip(seqs, new_tokens):
+            s.append(t)
+        order = []
+        for s in seqs:
+            order.insert(s.index, s)
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        for _ in range(n_completion):
+            new_tokens = model(order, [timed], prefill=False)
+            for s, t in zip(order, new_tokens):
+                s.append(t)
+        torch.cuda.synchronize()
+        t3 = time.perf_counter()
+        if rep >= args.warmup_runs:
+            runs.append({"tps": batch * n_completion / (t3 - t1), "prefill_ms": (t2 - t1) * 1e3,
+                         "decode_ms_per_step": (t3 - t2) * 1e3 / n_completion,
+                         "attention_us_per_step": statistics.mean(a.elapsed_time(b) for a, b in timed.pairs) * 1e3})
+    best = max(runs, key=lambda r: r["tps"])
+    st = kv.plan_stats()
+    line = {"metric": "llama_1layer_offline_tps", "value": statistics.median(r["tps"] for r in runs), "unit": "tokens/s",
+            "n_gpus": 1, "steps": len(runs) * n_completion, "warmup": args.warmup_runs * n_completion,
+            "ms_per_step": statistics.median(r["decode_ms_per_step"] for r in runs), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "llama: 1-layer Llama-7B-shaped decoder (hidden 4096, 32 heads, d128, chunk 64, random fp16 "
+                                   "weights), batch %d, prompt %d (%d shared), %d greedy decode steps; tokens/s over prefill + "
+                                   "decode wall time" % (batch, n_prompt, n_shared, n_completion)},
+            "runs": runs, "best_tps": best["tps"], "unique_kv_bytes_final": st["unique_kv_bytes"],
+            "n_shared_chunks_final": st["n_shared_chunks"], "device_status": kv.device_status()}
+    emit(line)
 
 
 class ClockSampler:
@@ -578,6 +671,8 @@ def main():
         run_reference_arm(args)
     elif args.workload == "cfg4":
         run_cfg4(args)
+    elif args.workload == "llama":
+        run_llama(args)
     else:
         run_b200(args)
 

@@ -25,7 +25,7 @@ EXPORTED = [
     "ca_last_error", "ca_version", "ca_chunk_bytes", "ca_tile_elem_offset", "ca_context_create",
     "ca_context_destroy", "ca_context_set_option", "ca_refresh_kernel_context", "ca_append_kv",
     "ca_context_delta_tokens", "ca_attention", "ca_attention_to_peers", "ca_attn_partials", "ca_attn_merge",
-    "ca_scatter_prefill", "ca_copy_chunks", "ca_read_chunk", "ca_status_read", "ca_context_stats",
+    "ca_scatter_prefill", "ca_scatter_rows", "ca_copy_chunks", "ca_read_chunk", "ca_status_read", "ca_context_stats",
     "ca_context_read_trace",
     "ca_plan_build", "ca_plan_array", "ca_plan_stats_get", "ca_plan_destroy", "ca_attention_static",
     "ca_rms_norm", "ca_fused_add_rms_norm", "ca_rotary_embedding",
@@ -75,6 +75,7 @@ def _load():
         "ca_attn_partials": (i32, [vp, vp, i32, i32, vp]),
         "ca_attn_merge": (i32, [vp, vp, i32, vp]),
         "ca_scatter_prefill": (i32, [vp, vp, vp, i64, i64, i32, i32, C.POINTER(C.c_int32), vp]),
+        "ca_scatter_rows": (i32, [vp, vp, vp, i64, i64, i32, C.POINTER(C.c_int32), C.POINTER(C.c_int32), vp]),
         "ca_copy_chunks": (i32, [vp, C.POINTER(C.c_int32), C.POINTER(C.c_int32), i32, vp]),
         "ca_read_chunk": (i32, [vp, i32, i32, vp, vp, vp]),
         "ca_status_read": (i32, [vp, vp, C.POINTER(C.c_int32)]),
@@ -190,6 +191,13 @@ class Context:
         ids = (C.c_int32 * max(1, len(chunk_ids)))(*chunk_ids)
         check(lib.ca_scatter_prefill(self._h, k.data_ptr(), v.data_ptr(), k.stride(0), k.stride(1),
                                      first_token, n_tokens, ids, self._stream()))
+
+    def scatter_rows(self, k, v, chunk_ids, rows):
+        assert k.stride(2) == 1 and v.stride(2) == 1 and k.stride() == v.stride() and len(chunk_ids) == len(rows)
+        ids = (C.c_int32 * max(1, len(chunk_ids)))(*chunk_ids)
+        rr = (C.c_int32 * max(1, len(rows)))(*rows)
+        check(lib.ca_scatter_rows(self._h, k.data_ptr(), v.data_ptr(), k.stride(0), k.stride(1), len(chunk_ids),
+                                  ids, rr, self._stream()))
 
     def copy_chunks(self, src, dst):
         s = (C.c_int32 * max(1, len(src)))(*src)

@@ -489,6 +489,41 @@ int ca_scatter_prefill(ca_context* c, const void* k, const void* v, int64_t stri
     return CA_OK;
 }
 
+int ca_scatter_rows(ca_context* c, const void* k, const void* v, int64_t stride_token, int64_t stride_head,
+                    int n_tokens, const int32_t* chunk_ids, const int32_t* rows, ca_stream stream_) {
+    if (!c) return fail(CA_ERR_INVALID, "context is null");
+    if (n_tokens < 0) return fail(CA_ERR_INVALID, "negative token count");
+    if (n_tokens == 0) return CA_OK;
+    if (!k || !v || !chunk_ids || !rows) return fail(CA_ERR_INVALID, "k, v, chunk_ids or rows is null");
+    for (int i = 0; i < n_tokens; i++) {
+        if (chunk_ids[i] < 0 || chunk_ids[i] >= c->max_chunks) return fail(CA_ERR_INVALID, "chunk id outside the pool");
+        if (rows[i] < 0 || rows[i] >= c->geo.chunk_size) return fail(CA_ERR_INVALID, "row outside the chunk");
+    }
+    DeviceGuard guard(c->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    const int es = c->geo.esize;
+    const bool vec16 = c->geo.epg > 1 && reinterpret_cast<uintptr_t>(k) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(v) % 16 == 0 && (stride_token * es) % 16 == 0 &&
+                       (stride_head * es) % 16 == 0;
+    // the plan's tail fill counts no longer describe the pool: the next step needs a fresh work list
+    c->valid = false;
+    for (int t0 = 0; t0 < n_tokens; t0 += ca::SCATTER_MAX_ROWS) {
+        const int nt = n_tokens - t0 < ca::SCATTER_MAX_ROWS ? n_tokens - t0 : ca::SCATTER_MAX_ROWS;
+        ca::ScatterRowsParams p;
+        p.pool = c->pool;
+        p.geo = c->geo;
+        p.k = static_cast<const char*>(k) + (int64_t)t0 * stride_token * es;
+        p.v = static_cast<const char*>(v) + (int64_t)t0 * stride_token * es;
+        p.stride_token = stride_token;
+        p.stride_head = stride_head;
+        p.n_tokens = nt;
+        std::memcpy(p.chunk_ids, chunk_ids + t0, nt * sizeof(int32_t));
+        std::memcpy(p.rows, rows + t0, nt * sizeof(int32_t));
+        CA_CUDA(ca::launch_scatter_rows(p, vec16, static_cast<cudaStream_t>(stream_)));
+    }
+    return CA_OK;
+}
+
 int ca_copy_chunks(ca_context* c, const int32_t* src_ids, const int32_t* dst_ids, int n, ca_stream stream_) {
     if (!c) return fail(CA_ERR_INVALID, "context is null");
     if (n < 0) return fail(CA_ERR_INVALID, "negative count");

@@ -108,6 +108,20 @@ struct ScatterParams {
 };
 cudaError_t launch_scatter_prefill(const ScatterParams& p, bool vec16, cudaStream_t stream);
 
+// token i of k / v goes to row rows[i] of chunk chunk_ids[i]
+constexpr int SCATTER_MAX_ROWS = 256;
+struct ScatterRowsParams {
+    void* pool;
+    Geometry geo;
+    const void* k;
+    const void* v;
+    int64_t stride_token, stride_head;  // in elements
+    int n_tokens;
+    int32_t chunk_ids[SCATTER_MAX_ROWS];
+    int32_t rows[SCATTER_MAX_ROWS];
+};
+cudaError_t launch_scatter_rows(const ScatterRowsParams& p, bool vec16, cudaStream_t stream);
+
 constexpr int COPY_MAX_PAIRS = 256;
 struct CopyParams {
     void* pool;

@@ -9,7 +9,8 @@ namespace ca {
 namespace {
 
 struct Unit {
-    std::vector<int32_t> chunks;  // pool slots, root to leaf
+    const int32_t* chunks;        // pool slots, root to leaf (storage shared by the unit's heads)
+    int32_t n_chunks;
     int32_t head, row_begin, n_rows, splits, last_tokens;
     bool tail;                    // last tile is a sequence's tail chunk
 };
@@ -25,10 +26,10 @@ std::string fmt(const char* f, long a = 0, long b = 0, long c = 0) {
 // full-size items and ends with single tiles.
 void cut_units(Plan& plan, const std::vector<Unit>& units, size_t ubegin, size_t uend, int n_ctas, int32_t& n_slots) {
     int64_t remaining = 0;
-    for (size_t u = ubegin; u < uend; u++) remaining += (int64_t)units[u].chunks.size();
+    for (size_t u = ubegin; u < uend; u++) remaining += units[u].n_chunks;
     for (size_t u = ubegin; u < uend; u++) {
         const Unit& un = units[u];
-        const int n_tiles = (int)un.chunks.size();
+        const int n_tiles = un.n_chunks;
         int j = 0;
         while (j < n_tiles) {
             int want = (int)std::min<int64_t>(MAX_TILES_PER_ITEM - 1, std::max<int64_t>(1, remaining / n_ctas));
@@ -36,7 +37,8 @@ void cut_units(Plan& plan, const std::vector<Unit>& units, size_t ubegin, size_t
             // before it instead of becoming an item of its own
             if (n_tiles - (j + want) == 1 && un.tail) want++;
             const int len = std::min(want, n_tiles - j);
-            PlanItem it{};
+            plan.items.emplace_back();
+            PlanItem& it = plan.items.back();
             it.n_tiles = len;
             it.head = un.head;
             it.row_begin = un.row_begin;
@@ -47,7 +49,6 @@ void cut_units(Plan& plan, const std::vector<Unit>& units, size_t ubegin, size_t
             it.last_tokens = has_last ? un.last_tokens : plan.chunk_size;
             for (int k = 0; k < len; k++) it.chunk[k] = un.chunks[j + k];
             n_slots += item_slots(un.n_rows, un.splits);
-            plan.items.push_back(it);
             j += len;
             remaining -= len;
         }
@@ -59,7 +60,16 @@ void cut_units(Plan& plan, const std::vector<Unit>& units, size_t ubegin, size_t
 std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int n_seqs, int n_heads,
                        int chunk_size, int tpp_threshold, int n_ctas, int64_t max_chunks,
                        bool split_phases, int d_head, int esize, bool fast_path, bool seq_first_tensor) {
-    plan = Plan();
+    // the vectors keep their capacity from one rebuild to the next
+    plan.items.clear();
+    plan.merge_slots.clear();
+    plan.path_chunks.clear();
+    plan.path_tokens.clear();
+    plan.tail_chunk.clear();
+    plan.tail_tokens.clear();
+    plan.n_items_cf = 0;
+    plan.n_ctas = 1;
+    plan.stats = ca_plan_stats{};
     if (n_infos < 0 || n_seqs < 0 || n_heads <= 0 || chunk_size <= 0 || n_ctas <= 0)
         return "negative or zero size";
     if (n_infos > 0 && infos == nullptr) return "infos is null";
@@ -152,7 +162,11 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
     plan.stats.n_runs = (int)runs.size();
 
     // ---- units ---------------------------------------------------------------------------------------------
+    // the chunk lists are stored once (per run, per sequence) and referenced by every head's unit
+    std::vector<int32_t> priv_arena;
+    priv_arena.reserve(path_total);  // never reallocates: the units keep pointers into it
     std::vector<Unit> units;
+    units.reserve((runs.size() * 2 + (size_t)n_seqs) * n_heads);
     for (Run& r : runs) {
         const int n = r.e - r.b;
         const int n_blocks = (n + MAX_ROWS_PER_ITEM - 1) / MAX_ROWS_PER_ITEM;
@@ -162,24 +176,34 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
             const int rows = std::min(rows_per_block, r.e - rb);
             if (rows <= 0) continue;
             const int splits = rows <= 16 ? 4 : (rows <= 32 ? 2 : 1);
-            for (int h = 0; h < n_heads; h++) units.push_back(Unit{r.chunks, h, rb, rows, splits, chunk_size, false});
+            for (int h = 0; h < n_heads; h++)
+                units.push_back(Unit{r.chunks.data(), (int32_t)r.chunks.size(), h, rb, rows, splits, chunk_size, false});
         }
     }
     const size_t n_units_cf = units.size();
     for (int s = 0; s < n_seqs; s++) {
-        std::vector<int32_t> priv;
+        const int32_t* priv = priv_arena.data() + priv_arena.size();
+        int32_t n_priv = 0;
         for (int32_t p = plan.path_off[s]; p < plan.path_off[s + 1]; p++)
-            if (!shared[path_info[p]]) priv.push_back(plan.path_chunks[p]);
+            if (!shared[path_info[p]]) {
+                priv_arena.push_back(plan.path_chunks[p]);
+                n_priv++;
+            }
         // a non-final private tile must be full: only the tail may be partially filled
         for (int32_t p = plan.path_off[s]; p + 1 < plan.path_off[s + 1]; p++)
             if (!shared[path_info[p]] && plan.path_tokens[p] != chunk_size)
                 return fmt("row %ld has a partially filled chunk that is not its tail", s);
         for (int h = 0; h < n_heads; h++)
-            units.push_back(Unit{priv, h, s, 1, seq_first_tensor ? 4 : 0, plan.tail_tokens[s], true});
+            units.push_back(Unit{priv, n_priv, h, s, 1, seq_first_tensor ? 4 : 0, plan.tail_tokens[s], true});
     }
 
     // ---- items ---------------------------------------------------------------------------------------------
     int32_t n_slots = 0;
+    {
+        int64_t tiles = 0;
+        for (const Unit& u : units) tiles += u.n_chunks;
+        plan.items.reserve((size_t)(tiles / 4 + units.size() + 4 * (size_t)n_ctas));
+    }
     if (!split_phases) {
         cut_units(plan, units, 0, units.size(), n_ctas, n_slots);
         plan.n_items_cf = 0;
@@ -197,8 +221,8 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
     // ---- merge lists -------------------------------------------------------------------------------------
     for (const PlanItem& it : plan.items) {
         const int splits = it.n_rows == 1 ? 1 : std::max(1, it.flags >> ITEM_SPLITS_SHIFT);
-        for (int r = 0; r < it.n_rows; r++)
-            plan.merge_off[(size_t)(it.row_begin + r) * n_heads + it.head + 1] += splits;
+        int32_t* off = plan.merge_off.data() + (size_t)it.row_begin * n_heads + it.head + 1;
+        for (int r = 0; r < it.n_rows; r++, off += n_heads) *off += splits;
     }
     for (size_t i = 1; i < plan.merge_off.size(); i++) plan.merge_off[i] += plan.merge_off[i - 1];
     plan.merge_slots.resize(plan.merge_off.back());
@@ -206,10 +230,13 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
         std::vector<int32_t> cursor(plan.merge_off.begin(), plan.merge_off.end() - 1);
         for (const PlanItem& it : plan.items) {
             const int splits = it.n_rows == 1 ? 1 : std::max(1, it.flags >> ITEM_SPLITS_SHIFT);
-            for (int sp = 0; sp < splits; sp++)
-                for (int r = 0; r < it.n_rows; r++)
-                    plan.merge_slots[cursor[(size_t)(it.row_begin + r) * n_heads + it.head]++] =
-                        it.slot_base + sp * it.n_rows + r;
+            // per (row, head) the slots are listed split by split, as the loops below visit them
+            int32_t* cur = cursor.data() + (size_t)it.row_begin * n_heads + it.head;
+            for (int r = 0; r < it.n_rows; r++, cur += n_heads) {
+                int32_t* dst = plan.merge_slots.data() + *cur;
+                for (int sp = 0; sp < splits; sp++) dst[sp] = it.slot_base + sp * it.n_rows + r;
+                *cur += splits;
+            }
         }
     }
     plan.stats.n_items = (int)plan.items.size();

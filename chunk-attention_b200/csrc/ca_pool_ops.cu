@@ -1,5 +1,5 @@
 // Device-side maintenance of the chunk pool: append one token per sequence, ingest a prefill,
-// clone chunks (copy-on-write), read a chunk back in logical order.  All of them are pure data
+// write single token rows (beam forks), clone chunks (copy-on-write), read a chunk back in logical order.  All of them are pure data
 // movement into / out of the swizzled tile layout (ca_layout.h) with 16-byte accesses wherever
 // the geometry allows.
 //
@@ -73,6 +73,25 @@ __global__ void scatter_prefill_kernel(const ScatterParams p) {
 }
 
 template <typename U>
+__global__ void scatter_rows_kernel(const ScatterRowsParams p) {
+    const Geometry& g = p.geo;
+    const int upr = units_per_row<U>(g);
+    const int64_t total = (int64_t)p.n_tokens * g.n_heads * 2 * upr;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int unit = (int)(idx % upr);
+    int64_t r = idx / upr;
+    const int kv = (int)(r & 1);
+    r >>= 1;
+    const int h = (int)(r % g.n_heads);
+    const int tok = (int)(r / g.n_heads);
+    const char* src = reinterpret_cast<const char*>(kv ? p.v : p.k) +
+                      ((int64_t)tok * p.stride_token + (int64_t)h * p.stride_head) * g.esize;
+    char* dst = reinterpret_cast<char*>(p.pool) + tile_base_elems(g, p.chunk_ids[tok], h, kv) * g.esize;
+    move_unit<U>(dst, src, g, p.rows[tok], unit);
+}
+
+template <typename U>
 __global__ void copy_chunks_kernel(const CopyParams p) {
     const int pair = blockIdx.y;
     const U* src = reinterpret_cast<const U*>(reinterpret_cast<const char*>(p.pool) + p.src[pair] * p.chunk_bytes);
@@ -125,6 +144,20 @@ cudaError_t launch_scatter_prefill(const ScatterParams& p, bool vec16, cudaStrea
         scatter_prefill_kernel<uint16_t><<<blocks_for(total, 256), 256, 0, stream>>>(p);
     } else {
         scatter_prefill_kernel<uint32_t><<<blocks_for(total, 256), 256, 0, stream>>>(p);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_scatter_rows(const ScatterRowsParams& p, bool vec16, cudaStream_t stream) {
+    const int upr = vec16 ? p.geo.gpr : p.geo.d_head;
+    const int64_t total = (int64_t)p.n_tokens * p.geo.n_heads * 2 * upr;
+    if (total <= 0) return cudaSuccess;
+    if (vec16) {
+        scatter_rows_kernel<uint4><<<blocks_for(total, 256), 256, 0, stream>>>(p);
+    } else if (p.geo.esize == 2) {
+        scatter_rows_kernel<uint16_t><<<blocks_for(total, 256), 256, 0, stream>>>(p);
+    } else {
+        scatter_rows_kernel<uint32_t><<<blocks_for(total, 256), 256, 0, stream>>>(p);
     }
     return cudaGetLastError();
 }

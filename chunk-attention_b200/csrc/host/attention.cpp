@@ -59,7 +59,29 @@ void Attention::init() {
 }
 
 Attention::~Attention() {
+    if (worker_.joinable()) {
+        {
+            std::lock_guard<std::mutex> lock(worker_mutex_);
+            worker_stop_ = true;
+        }
+        worker_cv_.notify_all();
+        worker_.join();
+    }
     if (ctx_) ca_context_destroy(ctx_);
+}
+
+void Attention::worker_loop() {
+    for (;;) {
+        std::function<void()> task;
+        {
+            std::unique_lock<std::mutex> lock(worker_mutex_);
+            worker_cv_.wait(lock, [this] { return worker_stop_ || !worker_queue_.empty(); });
+            if (worker_queue_.empty()) return;  // stop requested and nothing left to run
+            task = std::move(worker_queue_.front());
+            worker_queue_.pop_front();
+        }
+        task();
+    }
 }
 
 void* Attention::stream() const {
@@ -106,9 +128,64 @@ int Attention::add_seq(const std::vector<int>& tokens, torch::Tensor k, torch::T
     return seq_idx;
 }
 
-std::shared_ptr<std::future<int>> Attention::add_seq_async(const std::vector<int>&, torch::Tensor, torch::Tensor) {
-    // disabled in the reference as well (cpp/chunk_attn/attention.cpp:198)
-    throw std::runtime_error("add_seq_async is not supported: call add_seq from the serving thread");
+std::shared_ptr<std::future<int>> Attention::add_seq_async(const std::vector<int>& tokens, torch::Tensor k,
+                                                           torch::Tensor v) {
+    // The reference declares this and throws (cpp/chunk_attn/attention.cpp:195-208).  Here the
+    // insertion runs on this object's worker thread; the tensors are held by value until it is done.
+    auto promise = std::make_shared<std::promise<int>>();
+    auto future = std::make_shared<std::future<int>>(promise->get_future());
+    const c10::cuda::CUDAStream caller_stream = c10::cuda::getCurrentCUDAStream(options_.device().index());
+    {
+        std::lock_guard<std::mutex> lock(worker_mutex_);
+        if (!worker_.joinable()) worker_ = std::thread([this] { worker_loop(); });
+        worker_queue_.emplace_back([this, promise, tokens, k, v, caller_stream]() mutable {
+            try {
+                c10::cuda::CUDAStreamGuard guard(caller_stream);  // the current stream is per thread
+                promise->set_value(add_seq(tokens, k, v));
+            } catch (...) {
+                promise->set_exception(std::current_exception());
+            }
+            k.reset();
+            v.reset();
+        });
+    }
+    worker_cv_.notify_one();
+    return future;
+}
+
+int Attention::append_completion(int seq_idx, const std::vector<int>& tokens, torch::Tensor k, torch::Tensor v) {
+    const int64_t n = (int64_t)tokens.size();
+    if (k.dim() != 3 || v.dim() != 3 || k.size(0) != n || v.size(0) != n || k.size(1) != n_heads_ || v.size(1) != n_heads_ ||
+        k.size(2) != d_head_ || v.size(2) != d_head_)
+        throw std::runtime_error("append_completion: k and v must be [n_tokens, n_heads, d_head]");
+    std::vector<std::pair<Chunk*, Chunk*>> pairs;
+    std::vector<std::pair<Chunk*, int>> slots;
+    tree_->append_completion(seq_idx, tokens, pairs, slots);
+    valid_ = false;
+    k = to_cache(k);
+    v = to_cache(v);
+    if (k.strides() != v.strides()) {
+        k = k.contiguous();
+        v = v.contiguous();
+    }
+    c10::cuda::CUDAGuard guard(options_.device());
+    if (!pairs.empty()) {  // copy-on-write of the forked leaf, before the beams diverge
+        std::vector<int32_t> src, dst;
+        for (auto& p : pairs) {
+            src.push_back(p.first->id);
+            dst.push_back(p.second->id);
+        }
+        check_rc(ca_copy_chunks(ctx_, src.data(), dst.data(), (int)src.size(), stream()), "append_completion");
+    }
+    std::vector<int32_t> ids, rows;
+    for (auto& s : slots) {
+        ids.push_back(s.first->id);
+        rows.push_back(s.second);
+    }
+    check_rc(ca_scatter_rows(ctx_, k.data_ptr(), v.data_ptr(), k.stride(0), k.stride(1), (int)ids.size(), ids.data(),
+                             rows.data(), stream()),
+             "append_completion");
+    return seq_idx;
 }
 
 void Attention::remove_seq(int seq_idx) {

@@ -10,8 +10,13 @@
 #pragma once
 #include <torch/torch.h>
 
+#include <condition_variable>
+#include <deque>
+#include <functional>
 #include <future>
 #include <memory>
+#include <mutex>
+#include <thread>
 #include <vector>
 
 #include "../../../include/chunk_attn_b200.h"
@@ -30,6 +35,9 @@ class Attention {
     Attention& operator=(const Attention&) = delete;
 
     int add_seq(const std::vector<int>& tokens, torch::Tensor k, torch::Tensor v);
+    // add_seq on a worker thread of this object; the kernels go to the stream that is current on the
+    // calling thread now.  Insertions run in the order they were queued.  Until the future is ready
+    // no other method of this object may be called (the tree is not locked).
     std::shared_ptr<std::future<int>> add_seq_async(const std::vector<int>& tokens, torch::Tensor k, torch::Tensor v);
     void remove_seq(int seq_idx);
     std::vector<Chunk*> append_token(const std::vector<int>& tokens, torch::Tensor k, torch::Tensor v, bool fused = true);
@@ -38,6 +46,10 @@ class Attention {
     void clear();
     int64_t peak_memory_allocated() const { return tree_->pool().peak_memory_allocated(); }
     void duplicate(int seq_idx, int copies);
+    // One beam-search step for row seq_idx: it forks into tokens.size() rows (seq_idx, seq_idx + 1, ...),
+    // row seq_idx + i continuing with tokens[i] whose K/V are k[i], v[i] ([n_tokens, n_heads, d_head]).
+    // Returns seq_idx.
+    int append_completion(int seq_idx, const std::vector<int>& tokens, torch::Tensor k, torch::Tensor v);
     torch::Tensor forward(torch::Tensor q, int partition = 0);
     // head-sharded forward: rows are written into every rank's full-width output buffer (device
     // addresses this GPU can reach), this cache's heads landing at head_offset of total_heads
@@ -71,6 +83,14 @@ class Attention {
     std::unique_ptr<PrefixTree> tree_;
     ca_context* ctx_ = nullptr;
     bool valid_ = false;
+
+    // add_seq_async: one worker thread, started on first use, runs the queued insertions in order
+    void worker_loop();
+    std::thread worker_;
+    std::mutex worker_mutex_;
+    std::condition_variable worker_cv_;
+    std::deque<std::function<void()>> worker_queue_;
+    bool worker_stop_ = false;
 };
 
 }  // namespace ca_host

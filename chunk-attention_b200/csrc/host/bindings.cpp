@@ -41,7 +41,8 @@ py::dict stats_to_dict(const ca_plan_stats& st) {
 PYBIND11_MODULE(chunk_attn_c, m) {
     py::class_<std::future<int>, std::shared_ptr<std::future<int>>>(m, "IntFuture", py::module_local())
       .def(py::init<>())
-      .def("get", &std::future<int>::get);
+      // the GIL is released while waiting: the worker may need it to drop a tensor reference
+      .def("get", &std::future<int>::get, py::call_guard<py::gil_scoped_release>());
 
     py::class_<Chunk>(m, "Chunk", py::module_local())
       .def_readonly("children", &Chunk::children, py::return_value_policy::reference)
@@ -75,6 +76,8 @@ PYBIND11_MODULE(chunk_attn_c, m) {
       .def("refresh_kernel_context", &Attention::refresh_kernel_context, py::arg("force") = false)
       .def("reserve", &Attention::reserve, py::return_value_policy::reference)
       .def("duplicate", &Attention::duplicate, py::arg("seq_idx"), py::arg("copies"))
+      .def("append_completion", &Attention::append_completion, py::arg("seq_idx"), py::arg("tokens"), py::arg("k"),
+           py::arg("v"))
       .def("remove_seq", &Attention::remove_seq, py::arg("seq_idx"))
       .def("clear", &Attention::clear)
       .def("get_trie", &Attention::get_trie, py::return_value_policy::reference)
@@ -134,6 +137,18 @@ PYBIND11_MODULE(chunk_attn_c, m) {
                return ids;
            },
            py::arg("seq_idx"), py::arg("copies"))
+      .def("append_completion",
+           [](PrefixTree& t, int seq_idx, const std::vector<int>& tokens) {
+               // ([(source chunk id, clone chunk id)], [(chunk id, row) of token i])
+               std::vector<std::pair<Chunk*, Chunk*>> pairs;
+               std::vector<std::pair<Chunk*, int>> slots;
+               t.append_completion(seq_idx, tokens, pairs, slots);
+               std::vector<std::pair<int, int>> p, s;
+               for (auto& x : pairs) p.emplace_back(x.first->id, x.second->id);
+               for (auto& x : slots) s.emplace_back(x.first->id, x.second);
+               return std::make_pair(p, s);
+           },
+           py::arg("seq_idx"), py::arg("tokens"))
       .def("clear", &PrefixTree::clear)
       .def("get_trie", &PrefixTree::root, py::return_value_policy::reference)
       .def_property_readonly("tails", &PrefixTree::tails, py::return_value_policy::reference)

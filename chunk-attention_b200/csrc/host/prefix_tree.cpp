@@ -120,6 +120,32 @@ void PrefixTree::duplicate(int seq_idx, int copies, std::vector<std::pair<Chunk*
     }
 }
 
+void PrefixTree::append_completion(int seq_idx, const std::vector<int>& tokens,
+                                   std::vector<std::pair<Chunk*, Chunk*>>& pairs,
+                                   std::vector<std::pair<Chunk*, int>>& slots) {
+    pairs.clear();
+    slots.clear();
+    if (seq_idx < 0 || seq_idx >= (int)tails_.size()) throw std::runtime_error("seq_idx out of range");
+    if (tokens.empty()) throw std::runtime_error("append_completion: at least one token is required");
+    const int n = (int)tokens.size();
+    // chunks needed before anything is touched: successors of tails that are full now, the clones,
+    // and successors of the forked leaves if this token fills them
+    int need = n - 1;
+    for (Chunk* tail : tails_) need += tail->full() ? 1 : 0;
+    const Chunk* leaf = tails_[seq_idx];
+    const int fill = leaf->full() ? 0 : leaf->n_tokens();
+    if (fill + 1 == chunk_size_) need += n;
+    if (pool_.max_chunks() - pool_.in_use() < need) throw std::runtime_error("ChunkAllocator: capacity reached");
+    reserve();
+    duplicate(seq_idx, n - 1, pairs);
+    for (int i = 0; i < n; i++) {
+        Chunk* tail = tails_[seq_idx + i];
+        slots.emplace_back(tail, tail->n_tokens());
+        tail->append_tokens(tokens, i, i + 1);
+    }
+    reserve();
+}
+
 void PrefixTree::clear() {
     while (!tails_.empty()) remove_seq((int)tails_.size() - 1);
 }

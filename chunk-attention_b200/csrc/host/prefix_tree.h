@@ -35,6 +35,13 @@ class PrefixTree {
     // Clone the leaf of `seq_idx` `copies` times as its next siblings (beam search); `pairs`
     // receives (source, clone) for the device copy.
     void duplicate(int seq_idx, int copies, std::vector<std::pair<Chunk*, Chunk*>>& pairs);
+    // Fork row `seq_idx` into tokens.size() rows, each continuing with its own token (one beam-search
+    // step): the source keeps its row and takes tokens[0], clones of its leaf follow as rows
+    // seq_idx + 1 ... and take tokens[1] ....  `pairs` receives (source, clone) for the device copy,
+    // `slots` the (chunk, row in chunk) token i's K/V must be written to.  Leaves that fill up get
+    // their empty successor.  Nothing is changed when the pool cannot hold the result.
+    void append_completion(int seq_idx, const std::vector<int>& tokens, std::vector<std::pair<Chunk*, Chunk*>>& pairs,
+                           std::vector<std::pair<Chunk*, int>>& slots);
     void clear();
 
     std::vector<ca_chunk_info> get_chunks() const;

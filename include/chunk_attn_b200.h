@@ -147,6 +147,16 @@ CA_API int ca_scatter_prefill(ca_context* ctx, const void* k, const void* v, int
                               int64_t stride_head, int first_token, int n_tokens,
                               const int32_t* chunk_ids, ca_stream stream);
 
+/* Write single token rows: token i of k / v goes to row rows[i] of chunk chunk_ids[i] (HOST
+ * arrays of n_tokens entries).  Used when a sequence forks into beams, each continuing with its
+ * own token in its own copy of the tail.  Invalidates the context's work list (the tails' fill
+ * counts changed unevenly): call ca_refresh_kernel_context before the next ca_attention.
+ * Replaces Chunk::append_tokens as driven by Attention::append_completion
+ * (cpp/chunk_attn/attention.cpp:227-261, chunk.cpp:63-81). */
+CA_API int ca_scatter_rows(ca_context* ctx, const void* k, const void* v, int64_t stride_token,
+                           int64_t stride_head, int n_tokens, const int32_t* chunk_ids, const int32_t* rows,
+                           ca_stream stream);
+
 /* Copy-on-write: clone whole chunks (all heads, K and V) src_ids[i] -> dst_ids[i].
  * src_ids, dst_ids: HOST arrays.  Replaces Chunk::deep_copy (cpp/chunk_attn/chunk.cpp:93-107). */
 CA_API int ca_copy_chunks(ca_context* ctx, const int32_t* src_ids, const int32_t* dst_ids, int n,

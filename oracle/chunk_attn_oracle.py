@@ -195,6 +195,28 @@ class Attention:
             node.parent.insert_child(pos + c, clone)
             self.tails.insert(seq_idx + 1 + c, clone)
 
+    def append_completion(self, seq_idx, tokens, k, v):
+        """One beam-search step: row `seq_idx` forks into len(tokens) rows, row seq_idx + i continuing
+        with tokens[i] and K/V k[i], v[i] ([n_tokens, n_heads, d_head]).
+
+        Intended meaning of cpp/chunk_attn/attention.cpp:227-261 ("duplicate a seq ... in beam
+        search", attention.h:43-44): copies of the leaf become its next siblings, every copy takes one
+        of the candidate tokens, leaves that fill up get their empty successor.  The reference's
+        function is not exported to Python and does not maintain the ancestors' sharer counts or its
+        row list, so there is no reference behaviour to pin this against; the check is the dense one
+        (every resulting row attends over its full token history).
+        """
+        if not tokens:
+            raise RuntimeError("append_completion: at least one token is required")
+        self.reserve()
+        self.duplicate(seq_idx, len(tokens) - 1)
+        k = np.asarray(k, np.float32).transpose(1, 0, 2)
+        v = np.asarray(v, np.float32).transpose(1, 0, 2)
+        for i in range(len(tokens)):
+            self.tails[seq_idx + i].append_tokens(tokens, k, v, i, i + 1)
+        self.reserve()
+        return seq_idx
+
     def clear(self):
         """Intended meaning of cpp/chunk_attn/attention.cpp:280-285: drop every sequence."""
         while self.tails:

@@ -304,8 +304,6 @@ def test_attention_class_matches_cabi_engine_and_reference_api():
         attn.forward(q=q.transpose(0, 1).contiguous().transpose(0, 1))
     with pytest.raises(RuntimeError, match="num of seqs is not equal to num of tokens"):
         attn.append_token(tokens=[1], k=nk[:1], v=nk[:1])
-    with pytest.raises(RuntimeError):
-        attn.add_seq_async(tokens=[1], k=nk[:1], v=nk[:1])
     # a second cache with the same configuration starts empty (one per layer in the model)
     attn2 = Attention(attn)
     assert attn2.get_trie().n_seqs == 0 and attn2.tails == []
