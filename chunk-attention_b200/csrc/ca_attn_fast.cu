@@ -801,20 +801,23 @@ __global__ void __launch_bounds__(NUM_THREADS, 2) attn_partial_kernel(const Part
 // (32 partials per pass, usually all of them), the maximum is found with shuffles, and the O rows
 // are then fetched eight at a time with the slot numbers passed around by shuffles.
 __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeParams p) {
-    // When launched as a programmatic dependent of the partial kernel, wait here until that
-    // kernel's results are visible; a no-op for an ordinary launch.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int pair = blockIdx.x * 4 + (threadIdx.x >> 5);
-    if (pair >= p.n_pairs) return;
     const int lane = threadIdx.x & 31;
-    const int b = __ldg(p.merge_off + pair), e = __ldg(p.merge_off + pair + 1);
-    // the first 32 partials stay in registers; longer lists are re-read pass by pass
-    int slot0 = -1;
-    float2 ml0 = make_float2(NEG_BIG, 0.f);
-    if (b + lane < e) {
-        slot0 = __ldg(p.merge_slots + b + lane);
-        ml0 = p.part_ml[slot0];
+    // The merge lists belong to the work list, which was uploaded before the partial kernel started:
+    // as a programmatic dependent this kernel reads them while that kernel is still draining, and
+    // only the partials themselves are read after the wait.
+    int b = 0, e = 0, slot0 = -1;
+    if (pair < p.n_pairs) {
+        b = __ldg(p.merge_off + pair);
+        e = __ldg(p.merge_off + pair + 1);
+        if (b + lane < e) slot0 = __ldg(p.merge_slots + b + lane);
     }
+    // wait until the partial kernel's results are visible; a no-op for an ordinary launch
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (pair >= p.n_pairs) return;
+    // the first 32 partials stay in registers; longer lists are re-read pass by pass
+    float2 ml0 = make_float2(NEG_BIG, 0.f);
+    if (slot0 >= 0) ml0 = p.part_ml[slot0];
     float mm = ml0.y > 0.f ? ml0.x : NEG_BIG;
     for (int i = b + 32 + lane; i < e; i += 32) {
         const float2 ml = p.part_ml[__ldg(p.merge_slots + i)];
