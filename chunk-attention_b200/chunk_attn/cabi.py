@@ -15,7 +15,7 @@ _LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "lib
 CA_OK = 0
 CA_ERR_INVALID, CA_ERR_CUDA, CA_ERR_STATE, CA_ERR_DEVICE_STATUS = -1, -2, -3, -4
 CA_DTYPE_F16, CA_DTYPE_F32 = 0, 1
-CA_OPT_SPLIT_PHASES, CA_OPT_NUM_CTAS, CA_OPT_SEQ_FIRST_TENSOR, CA_OPT_TRACE = 1, 2, 3, 4
+CA_OPT_SPLIT_PHASES, CA_OPT_NUM_CTAS, CA_OPT_SEQ_FIRST_TENSOR, CA_OPT_TRACE, CA_OPT_DEPENDENT_LAUNCH = 1, 2, 3, 4, 5
 PLAN_ITEMS = 0
 (PLAN_MERGE_OFF, PLAN_MERGE_SLOTS, PLAN_PATH_OFF, PLAN_PATH_CHUNKS, PLAN_PATH_TOKENS, PLAN_TAIL_CHUNK,
  PLAN_TAIL_TOKENS) = range(3, 10)

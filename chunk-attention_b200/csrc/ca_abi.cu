@@ -78,6 +78,7 @@ struct ca_context {
     bool opt_split = false;
     int opt_ctas = 0;
     bool opt_sf_tensor = true;
+    int opt_pdl = 3;
     unsigned long long* trace = nullptr;  // [kTraceCtas][4], allocated when tracing is switched on
     int trace_ctas = 0;                   // CTAs of the last traced launch
 
@@ -195,6 +196,10 @@ int ca_context_set_option(ca_context* c, int option, int64_t value) {
         c->opt_ctas = (int)value;
     } else if (option == CA_OPT_SEQ_FIRST_TENSOR) {
         c->opt_sf_tensor = value != 0;
+    } else if (option == CA_OPT_DEPENDENT_LAUNCH) {
+        if (value < 0 || value > 3) return fail(CA_ERR_INVALID, "dependent-launch mask out of range");
+        c->opt_pdl = (int)value;
+        return CA_OK;
     } else if (option == CA_OPT_TRACE) {
         DeviceGuard guard(c->device);
         if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
@@ -365,7 +370,7 @@ int ca_attn_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_st
         c->launch_parity ^= 1;
         const int n_ctas = c->plan.n_ctas < hi - lo ? c->plan.n_ctas : hi - lo;
         c->trace_ctas = n_ctas;
-        return ca::launch_attn_partials(p, n_ctas, stream);
+        return ca::launch_attn_partials(p, n_ctas, stream, (c->opt_pdl & 2) != 0);
     };
     const int n_items = (int)c->plan.items.size();
     if (!c->plan.split_phases) {
@@ -391,7 +396,7 @@ int ca_attn_merge(ca_context* c, void* out, int n_seqs, ca_stream stream_) {
     m.merge_slots = c->d_merge_slots;
     m.out = out;
     m.n_pairs = n_seqs * c->geo.n_heads;
-    CA_CUDA(ca::launch_attn_merge(m, static_cast<cudaStream_t>(stream_), true));
+    CA_CUDA(ca::launch_attn_merge(m, static_cast<cudaStream_t>(stream_), (c->opt_pdl & 1) != 0));
     return CA_OK;
 }
 
@@ -421,7 +426,7 @@ int ca_attention_to_peers(ca_context* c, const void* q, void* const* peer_out, i
     m.total_heads = total_heads;
     m.head_offset = head_offset;
     for (int i = 0; i < n_peers; i++) m.peer_out[i] = peer_out[i];
-    CA_CUDA(ca::launch_attn_merge(m, static_cast<cudaStream_t>(stream_), true));
+    CA_CUDA(ca::launch_attn_merge(m, static_cast<cudaStream_t>(stream_), (c->opt_pdl & 1) != 0));
     return CA_OK;
 }
 

@@ -732,6 +732,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 2) attn_partial_kernel(const Part
     }
     __syncthreads();
     // no block-wide barrier below this line: the warps run decoupled
+    // Launched as a programmatic dependent of whatever precedes it in the stream, the CTA has set
+    // itself up while that kernel was finishing; nothing in global memory has been touched so far.
+    // Every thread waits here until the predecessor's writes (queries, appended K/V rows, the
+    // previous step's merge still reading the partial buffers) are complete and visible.  A no-op
+    // for an ordinary launch.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // let the merge kernel (a programmatic dependent launch) be scheduled as soon as SMs drain
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
@@ -814,6 +820,10 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeParams p) {
     }
     // wait until the partial kernel's results are visible; a no-op for an ordinary launch
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // the partial kernel is complete: a following kernel launched as a programmatic dependent (the
+    // next step's partial kernel) may set itself up while the rows below are combined; it waits for
+    // this kernel's completion before it touches global memory
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (pair >= p.n_pairs) return;
     // the first 32 partials stay in registers; longer lists are re-read pass by pass
     float2 ml0 = make_float2(NEG_BIG, 0.f);
@@ -899,10 +909,26 @@ cudaError_t configure_fast_kernels() {
                                 cudaSharedmemCarveoutMaxShared);
 }
 
-cudaError_t launch_attn_partials(const PartialParams& p, int n_ctas, cudaStream_t stream) {
+cudaError_t launch_attn_partials(const PartialParams& p, int n_ctas, cudaStream_t stream, bool dependent_launch) {
     if (n_ctas <= 0) return cudaSuccess;
-    attn_partial_kernel<<<n_ctas, NUM_THREADS, SMEM_BYTES, stream>>>(p);
-    return cudaGetLastError();
+    static const bool pdl_disabled = std::getenv("CA_DISABLE_PDL") != nullptr;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_ctas);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (dependent_launch && !pdl_disabled) ? 1 : 0;
+    cudaError_t err = cudaLaunchKernelEx(&cfg, attn_partial_kernel, p);
+    if (err != cudaSuccess && cfg.numAttrs == 1) {
+        (void)cudaGetLastError();
+        cfg.numAttrs = 0;
+        err = cudaLaunchKernelEx(&cfg, attn_partial_kernel, p);
+    }
+    return err;
 }
 
 cudaError_t launch_attn_merge(const MergeParams& p, cudaStream_t stream, bool dependent_launch) {

@@ -46,7 +46,8 @@ struct PartialParams {
 
 // Persistent kernel: chunk-first and sequence-first items, both fed by one TMA ring per CTA.
 // grid = n_ctas (FAST_CTAS_PER_SM per SM).
-cudaError_t launch_attn_partials(const PartialParams& p, int n_ctas, cudaStream_t stream);
+// dependent_launch: allow the CTAs to be set up while the preceding kernel of the stream is finishing
+cudaError_t launch_attn_partials(const PartialParams& p, int n_ctas, cudaStream_t stream, bool dependent_launch = false);
 cudaError_t configure_fast_kernels();  // once per device before the first launch
 
 constexpr int MERGE_MAX_PEERS = 8;

@@ -94,6 +94,10 @@ CA_API void ca_context_destroy(ca_context* ctx);
 #define CA_OPT_SEQ_FIRST_TENSOR 3
 /* 1: the attention kernel records per-CTA nanosecond timestamps, read with ca_context_read_trace */
 #define CA_OPT_TRACE 4
+/* programmatic dependent launches: bit 0, the merge kernel is set up while the attention kernel
+ * drains; bit 1, the attention kernel is set up while the kernel before it in the stream finishes
+ * (it waits for that kernel's completion before it touches global memory).  Default 3. */
+#define CA_OPT_DEPENDENT_LAUNCH 5
 CA_API int ca_context_set_option(ca_context* ctx, int option, int64_t value);
 
 /* Rebuild and upload the work lists after the tree changed.
