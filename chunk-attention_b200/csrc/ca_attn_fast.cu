@@ -16,8 +16,8 @@
 // Both kinds read their K/V tiles from a ring of 32 KiB shared-memory stages, filled by a
 // producer warp with 1-D TMA bulk copies (cp.async.bulk + mbarrier transaction counts) that run
 // ahead across item boundaries.  Items (at most 8 tiles, cut by the host, ca_plan.h) are
-// self-scheduled: each CTA's producer draws the next item from a device counter two items ahead of
-// use and hands its description to the consumers through shared memory together with the item's
+// self-scheduled: each CTA's producer draws the next item from a device counter once the current
+// one is issued in full and hands its description to the consumers through shared memory together with the item's
 // first tile, so the split of the work follows what each SM actually achieves.  A CTA is one
 // consumer warpgroup (4 warps) plus a producer warpgroup; two CTAs share an SM so that one CTA's
 // item boundaries (queries, combining warps, storing a partial) hide behind the other CTA's
@@ -244,21 +244,19 @@ __device__ __forceinline__ bool producer_post(const PartialParams& p, Ring& rg, 
 __device__ __forceinline__ void producer_loop(const PartialParams& p, Ring& rg) {
     uint32_t issued = 0;
     bool ok = true;
-    // Items are drawn two ahead (the atomic's round trip) and described one ahead (the loads of the
-    // description), so neither latency is exposed while the current item streams.
     // The first two items of a CTA are fixed by its index, so that nothing waits for an atomic at
-    // start-up; the counter hands out the items after those of all CTAs.
+    // start-up; the counter hands out the items after those of all CTAs.  An item is drawn only
+    // after the previous one has been issued in full: by then the ring holds NUM_STAGES tiles in
+    // flight, which cover the round trips of the atomic and of the description, and no CTA sits on
+    // work it has claimed but not started while other CTAs run dry at the end of the list (drawing
+    // two items ahead left the last CTA 4 us behind the median one).
     const int n_fixed = 2 * (int)gridDim.x;
     int id0 = p.item_lo + (int)blockIdx.x;
-    int id1 = p.item_lo + (int)gridDim.x + (int)blockIdx.x;
+    int id1 = p.item_lo + (int)gridDim.x + (int)blockIdx.x;  // < 0: draw from the counter
     ItemView it{};
     ItemChunks ch{};
     if (id0 < p.item_hi) load_item(p.items, id0, it, ch);
     while (id0 < p.item_hi && ok) {
-        const int id2 = p.item_lo + n_fixed + atomicAdd(p.counter, 1);
-        ItemView it1{};
-        ItemChunks ch1{};
-        if (id1 < p.item_hi) load_item(p.items, id1, it1, ch1);
         // items of up to 16 rows get their query rows staged next to their first tile
         const bool stage_q = (it.flags >> ITEM_SPLITS_SHIFT) == NUM_CONSUMER_WARPS;
         bool first = true;
@@ -278,10 +276,9 @@ __device__ __forceinline__ void producer_loop(const PartialParams& p, Ring& rg) 
             ok = producer_post(p, rg, &it, false, nullptr, 0);
             issued += ok ? 1 : 0;
         }
-        id0 = id1;
-        id1 = id2;
-        it = it1;
-        ch = ch1;
+        id0 = id1 >= 0 ? id1 : p.item_lo + n_fixed + atomicAdd(p.counter, 1);
+        id1 = -1;
+        if (id0 < p.item_hi) load_item(p.items, id0, it, ch);
     }
     if (ok) {
         ItemView end_marker{};
