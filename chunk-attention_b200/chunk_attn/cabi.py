@@ -24,7 +24,7 @@ PLAN_ITEMS = 0
 EXPORTED = [
     "ca_last_error", "ca_version", "ca_chunk_bytes", "ca_tile_elem_offset", "ca_context_create",
     "ca_context_destroy", "ca_context_set_option", "ca_refresh_kernel_context", "ca_append_kv",
-    "ca_context_delta_tokens", "ca_attention", "ca_attention_to_peers", "ca_attn_partials", "ca_attn_merge",
+    "ca_context_delta_tokens", "ca_attention", "ca_attention_host", "ca_attention_to_peers", "ca_attn_partials", "ca_attn_merge",
     "ca_scatter_prefill", "ca_scatter_rows", "ca_copy_chunks", "ca_read_chunk", "ca_status_read", "ca_context_stats",
     "ca_context_read_trace",
     "ca_plan_build", "ca_plan_array", "ca_plan_stats_get", "ca_plan_destroy", "ca_attention_static",
@@ -71,6 +71,7 @@ def _load():
         "ca_append_kv": (i32, [vp, vp, vp, i32, vp]),
         "ca_context_delta_tokens": (i32, [vp]),
         "ca_attention": (i32, [vp, vp, vp, i32, i32, vp]),
+        "ca_attention_host": (i32, [vp, vp, vp, i32, i32, vp]),
         "ca_attention_to_peers": (i32, [vp, vp, C.POINTER(vp), i32, i32, i32, i32, vp]),
         "ca_attn_partials": (i32, [vp, vp, i32, i32, vp]),
         "ca_attn_merge": (i32, [vp, vp, i32, vp]),
@@ -174,6 +175,12 @@ class Context:
 
     def attention(self, q, out, partition=0):
         check(lib.ca_attention(self._h, q.data_ptr(), out.data_ptr(), q.shape[0], partition, self._stream()))
+
+    def attention_host(self, q_cpu, out_cpu, partition=0):
+        """q_cpu, out_cpu: contiguous CPU tensors (pinned or not); returns when out_cpu holds the result."""
+        assert not q_cpu.is_cuda and not out_cpu.is_cuda and q_cpu.is_contiguous() and out_cpu.is_contiguous()
+        check(lib.ca_attention_host(self._h, q_cpu.data_ptr(), out_cpu.data_ptr(), q_cpu.shape[0], partition,
+                                    self._stream()))
 
     def attention_to_peers(self, q, peer_ptrs, total_heads, head_offset):
         arr = (C.c_void_p * len(peer_ptrs))(*peer_ptrs)

@@ -107,6 +107,12 @@ struct ca_context {
     int* status = nullptr;
     int* counters = nullptr;  // two item counters: a launch draws from one and zeroes the other
     int launch_parity = 0;
+
+    // ca_attention_host: device copy of the queries, pinned stand-ins for pageable caller buffers
+    void* q_stage = nullptr;
+    void* host_q_stage = nullptr;
+    void* host_out_stage = nullptr;
+    size_t q_stage_cap = 0, host_q_cap = 0, host_out_cap = 0;
 };
 
 extern "C" {
@@ -184,6 +190,9 @@ void ca_context_destroy(ca_context* c) {
     if (c->trace) cudaFree(c->trace);
     if (c->status) cudaFree(c->status);
     if (c->counters) cudaFree(c->counters);
+    if (c->q_stage) cudaFree(c->q_stage);
+    if (c->host_q_stage) cudaFreeHost(c->host_q_stage);
+    if (c->host_out_stage) cudaFreeHost(c->host_out_stage);
     delete c;
 }
 
@@ -379,6 +388,72 @@ int ca_attn_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_st
         if (phases & 1) CA_CUDA(launch(0, c->plan.n_items_cf));
         if (phases & 2) CA_CUDA(launch(c->plan.n_items_cf, n_items));
     }
+    return CA_OK;
+}
+
+namespace {
+// true when the device can read / write the host range directly (page-locked and mapped);
+// *dev_ptr receives the address to use on the device
+bool device_view_of_host(const void* host_ptr, void** dev_ptr) {
+    cudaPointerAttributes attr{};
+    if (cudaPointerGetAttributes(&attr, host_ptr) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    if (attr.type != cudaMemoryTypeHost || attr.devicePointer == nullptr) return false;
+    *dev_ptr = attr.devicePointer;
+    return true;
+}
+}  // namespace
+
+int ca_attention_host(ca_context* c, const void* q_host, void* out_host, int n_seqs, int partition, ca_stream stream_) {
+    if (!c) return fail(CA_ERR_INVALID, "context is null");
+    if (!c->valid) return fail(CA_ERR_STATE, "work list is stale: call ca_refresh_kernel_context first");
+    if (n_seqs != c->plan.n_seqs) return fail(CA_ERR_INVALID, "n_seqs differs from the refreshed work list");
+    if (partition < 0 || partition > 2) return fail(CA_ERR_INVALID, "Unsupported partition type");
+    if (n_seqs == 0) return CA_OK;
+    if (!q_host || !out_host) return fail(CA_ERR_INVALID, "q or out is null");
+    DeviceGuard guard(c->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const size_t bytes = (size_t)n_seqs * c->geo.n_heads * c->geo.d_head * c->geo.esize;
+    if (bytes > c->q_stage_cap) {
+        if (c->q_stage) CA_CUDA(cudaFree(c->q_stage));
+        c->q_stage = nullptr;
+        c->q_stage_cap = 0;
+        CA_CUDA(cudaMalloc(&c->q_stage, align_up(bytes * 2, 4096)));
+        c->q_stage_cap = align_up(bytes * 2, 4096);
+    }
+    auto grow_host = [&](void*& buf, size_t& cap) -> cudaError_t {
+        if (bytes <= cap) return cudaSuccess;
+        if (buf) cudaFreeHost(buf);
+        buf = nullptr;
+        cap = 0;
+        cudaError_t e = cudaMallocHost(&buf, align_up(bytes * 2, 4096));
+        if (e == cudaSuccess) cap = align_up(bytes * 2, 4096);
+        return e;
+    };
+    // queries: one copy into device memory (every item re-reads its rows, so they must not stay
+    // behind the bus); a pageable source goes through a pinned stand-in first
+    void* unused = nullptr;
+    const void* q_src = q_host;
+    if (!device_view_of_host(q_host, &unused)) {
+        CA_CUDA(grow_host(c->host_q_stage, c->host_q_cap));
+        std::memcpy(c->host_q_stage, q_host, bytes);
+        q_src = c->host_q_stage;
+    }
+    CA_CUDA(cudaMemcpyAsync(c->q_stage, q_src, bytes, cudaMemcpyHostToDevice, stream));
+    // output: the last kernel stores its rows straight into the caller's page-locked buffer
+    void* out_dev = nullptr;
+    const bool direct = device_view_of_host(out_host, &out_dev) && reinterpret_cast<uintptr_t>(out_dev) % 16 == 0;
+    if (!direct) {
+        CA_CUDA(grow_host(c->host_out_stage, c->host_out_cap));
+        if (!device_view_of_host(c->host_out_stage, &out_dev)) return fail(CA_ERR_CUDA, "pinned staging buffer is not mapped");
+    }
+    int rc = ca_attention(c, c->q_stage, out_dev, n_seqs, partition, stream_);
+    if (rc != CA_OK) return rc;
+    CA_CUDA(cudaStreamSynchronize(stream));
+    if (!direct) std::memcpy(out_host, c->host_out_stage, bytes);
     return CA_OK;
 }
 

@@ -258,6 +258,28 @@ torch::Tensor Attention::forward(torch::Tensor q, int partition) {
     return output;
 }
 
+torch::Tensor Attention::forward_host(torch::Tensor q, c10::optional<torch::Tensor> out, int partition) {
+    const auto st = c10::typeMetaToScalarType(options_.dtype());
+    if (q.is_cuda()) throw std::runtime_error("forward_host: q must be a CPU tensor (use forward for device tensors)");
+    if (!q.is_contiguous()) throw std::runtime_error("q is not contiguous");
+    if (q.dim() != 3 || q.size(1) != n_heads_ || q.size(2) != d_head_ || q.scalar_type() != st)
+        throw std::runtime_error("forward_host: q must be [n_seqs, n_heads, d_head] with the dtype of the cache");
+    if (q.size(0) != (int64_t)tree_->n_seqs()) throw std::runtime_error("forward: one query row per live sequence is required");
+    if (partition < 0 || partition > 2) throw std::runtime_error("Unsupported partition type");
+    torch::Tensor result;
+    if (out.has_value()) {
+        result = *out;
+        if (result.is_cuda() || !result.is_contiguous() || result.sizes() != q.sizes() || result.scalar_type() != st)
+            throw std::runtime_error("forward_host: out must be a contiguous CPU tensor shaped and typed like q");
+    } else {
+        result = torch::empty(q.sizes(), torch::TensorOptions().dtype(st).device(torch::kCPU).pinned_memory(true));
+    }
+    c10::cuda::CUDAGuard guard(options_.device());
+    refresh_kernel_context(false);
+    check_rc(ca_attention_host(ctx_, q.data_ptr(), result.data_ptr(), (int)q.size(0), partition, stream()), "forward_host");
+    return result;
+}
+
 void Attention::forward_to_peers(torch::Tensor q, const std::vector<int64_t>& peer_out_ptrs, int total_heads,
                                  int head_offset) {
     if (!q.is_contiguous()) throw std::runtime_error("q is not contiguous");

@@ -51,6 +51,10 @@ class Attention {
     // Returns seq_idx.
     int append_completion(int seq_idx, const std::vector<int>& tokens, torch::Tensor k, torch::Tensor v);
     torch::Tensor forward(torch::Tensor q, int partition = 0);
+    // forward for queries in host memory: returns a CPU tensor (written into `out` when given).  Pinned
+    // tensors are used in place, the result rows are stored into host memory by the last kernel, and
+    // the call returns when they are there.
+    torch::Tensor forward_host(torch::Tensor q, c10::optional<torch::Tensor> out, int partition = 0);
     // head-sharded forward: rows are written into every rank's full-width output buffer (device
     // addresses this GPU can reach), this cache's heads landing at head_offset of total_heads
     void forward_to_peers(torch::Tensor q, const std::vector<int64_t>& peer_out_ptrs, int total_heads, int head_offset);

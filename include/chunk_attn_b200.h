@@ -121,6 +121,15 @@ CA_API int ca_context_delta_tokens(const ca_context* ctx);
 CA_API int ca_attention(ca_context* ctx, const void* q, void* out, int n_seqs, int partition,
                         ca_stream stream);
 
+/* The same step for a caller whose queries and result live in HOST memory: copies q to the device,
+ * runs ca_attention, has the last kernel store the result rows directly into `out_host` and waits
+ * for the stream.  Page-locked buffers (cudaHostAlloc / cudaHostRegister / torch pin_memory) are
+ * used in place; pageable ones are staged through pinned buffers of the context.  On return
+ * out_host holds the result.  No counterpart in the reference, whose forward takes device tensors
+ * (cpp/chunk_attn/attention.cpp:374-397); a caller with host data would wrap it in two copies. */
+CA_API int ca_attention_host(ca_context* ctx, const void* q_host, void* out_host, int n_seqs, int partition,
+                             ca_stream stream);
+
 /* Head-sharded variant of ca_attention (one process per GPU, this context holds n_heads of
  * total_heads, starting at head_offset): the merge kernel writes every output row straight into
  * each rank's full-width buffer peer_out[i], fp16 [n_seqs, total_heads, d_head], with plain stores
