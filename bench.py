@@ -607,8 +607,8 @@ def run_b200(args):
             roof = {"bound": "hbm", "kernel": "attn_partial_kernel", "achieved": achieved, "peak": peak,
                     "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch from the ncu capture summarised
-                    # in profiles/attn_partial_kernel_cfg2.md (302.98 MB + 10.5 MB); only that workload was captured
-                    "traffic": 313.5e6 if (name == "cfg2" and world == 1) else None,
+                    # in profiles/attn_partial_kernel_cfg2.md (302.97 MB read + 10.1 MB written); only that workload was captured
+                    "traffic": 313.0e6 if (name == "cfg2" and world == 1) else None,
                     "algorithmic_bytes_per_launch": ukv_local,
                     "kernel_ms": {"partials_mean": dur_ms, "partials_min": min(kern["partials"]),
                                   "merge_mean": statistics.mean(kern["merge"])}}
