@@ -14,6 +14,7 @@ import threading
 
 import torch
 
+from ..logger import logger
 from .sequence import Sequence
 
 
@@ -91,6 +92,7 @@ class ModelHost:
                 for kv_cache in self.kv_caches:
                     kv_cache.remove_seq(idx - n_removed)
                 n_removed += 1
+                logger.debug("finished the seq %s", seq.id)
                 seq.set_result_ready()
             else:
                 kept.append(seq)
@@ -102,6 +104,7 @@ class ModelHost:
         self.retire_finished()
         arrived = self.get_new_requests()
         if arrived:
+            logger.debug("prefill of %d new seqs, %d running", len(arrived), len(self.running_seqs))
             new_tokens = self.model_obj(arrived, self.kv_caches, prefill=True)
             for seq, tok in zip(arrived, new_tokens):
                 seq.append(tok)
@@ -135,6 +138,7 @@ class ModelHost:
 
     def _fail_all(self, error, record):
         if record:
+            logger.error("model host failed: %r", error)
             self.failure = error
             self.stopped = True
         for seq in self.running_seqs:

@@ -201,3 +201,11 @@ def test_step_api_without_a_thread():
     assert a.result_ready.is_set() and a.tokens == rollout([1, 2, 3, 4, 5, 6], 2)
     host.step()
     assert b.result_ready.is_set() and b.tokens == rollout([1, 2, 3, 4, 9], 3)
+
+
+def test_helper_modules_of_the_reference_package_exist():
+    import chunk_attn.nvtx as nvtx
+    from chunk_attn.logger import logger
+    nvtx.range_push("x")
+    nvtx.range_pop()
+    assert logger.name == "ChunkAttn"
