@@ -27,7 +27,7 @@ EXPORTED = [
     "ca_context_delta_tokens", "ca_attention", "ca_attention_host", "ca_attention_to_peers", "ca_attn_partials", "ca_attn_merge",
     "ca_scatter_prefill", "ca_scatter_rows", "ca_copy_chunks", "ca_read_chunk", "ca_status_read", "ca_context_stats",
     "ca_context_read_trace",
-    "ca_plan_build", "ca_plan_array", "ca_plan_stats_get", "ca_plan_destroy", "ca_attention_static",
+    "ca_plan_build", "ca_plan_build_for_context", "ca_refresh_from_plan", "ca_plan_array", "ca_plan_stats_get", "ca_plan_destroy", "ca_attention_static",
     "ca_rms_norm", "ca_fused_add_rms_norm", "ca_rotary_embedding",
 ]
 CA_STATIC_MAX_SLOTS = 16384
@@ -83,6 +83,8 @@ def _load():
         "ca_context_stats": (i32, [vp, C.POINTER(PlanStats)]),
         "ca_context_read_trace": (i32, [vp, C.POINTER(C.c_uint64), i32, C.POINTER(i32), vp]),
         "ca_plan_build": (i32, [C.POINTER(vp), C.POINTER(ChunkInfo), i32, i32, i32, i32, i32, i32, i64, i32, i32]),
+        "ca_plan_build_for_context": (i32, [vp, C.POINTER(vp), C.POINTER(ChunkInfo), i32, i32]),
+        "ca_refresh_from_plan": (i32, [vp, vp, vp]),
         "ca_plan_array": (i32, [vp, i32, C.POINTER(C.POINTER(C.c_int32)), C.POINTER(i64)]),
         "ca_plan_stats_get": (i32, [vp, C.POINTER(PlanStats)]),
         "ca_plan_destroy": (None, [vp]),

@@ -60,6 +60,11 @@ void set_last_error(const std::string& msg) { g_last_error = msg; }
 
 struct ca_plan {
     ca::Plan plan;
+    // what the plan was built for (checked when it is uploaded into a context)
+    int64_t max_chunks = INT64_MAX;
+    bool fast = true;
+    int d_head = ca::FAST_D;
+    int esize = 2;
 };
 
 namespace {
@@ -82,7 +87,13 @@ struct ca_context {
     unsigned long long* trace = nullptr;  // [kTraceCtas][4], allocated when tracing is switched on
     int trace_ctas = 0;                   // CTAs of the last traced launch
 
-    ca::Plan plan;
+    ca::Plan plan;  // scratch of ca_refresh_kernel_context (vectors keep their capacity)
+    // what the launches need to know about the work list that is on the device
+    struct {
+        int n_seqs = 0, n_items = 0, n_items_cf = 0, n_ctas = 1;
+        bool split_phases = false;
+        ca_plan_stats stats{};
+    } meta;
     bool valid = false;
     int delta_tokens = 0;
     int max_tail_tokens = 0;
@@ -227,6 +238,8 @@ int ca_context_set_option(ca_context* c, int option, int64_t value) {
     return CA_OK;
 }
 
+static int upload_plan(ca_context* c, const ca::Plan& pl, cudaStream_t stream);
+
 int ca_refresh_kernel_context(ca_context* c, const ca_chunk_info* infos, int n_infos, int n_seqs, ca_stream stream_) {
     if (!c) return fail(CA_ERR_INVALID, "context is null");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -238,7 +251,45 @@ int ca_refresh_kernel_context(ca_context* c, const ca_chunk_info* infos, int n_i
                                      c->tpp_threshold, n_ctas, c->max_chunks, c->opt_split, c->geo.d_head,
                                      c->geo.esize, c->fast, c->opt_sf_tensor);
     if (!err.empty()) return fail(CA_ERR_INVALID, "work list rejected: " + err);
-    const ca::Plan& pl = c->plan;
+    return upload_plan(c, c->plan, stream);
+}
+
+int ca_plan_build_for_context(const ca_context* c, ca_plan** out, const ca_chunk_info* infos, int n_infos, int n_seqs) {
+    if (!c || !out) return fail(CA_ERR_INVALID, "null argument");
+    ca_plan* p = *out;  // an existing plan is rebuilt in place and keeps its buffers
+    if (!p) p = new (std::nothrow) ca_plan();
+    if (!p) return fail(CA_ERR_INVALID, "out of host memory");
+    const int n_ctas = c->opt_ctas > 0 ? c->opt_ctas : c->num_sms * ca::FAST_CTAS_PER_SM;
+    std::string err = ca::build_plan(p->plan, infos, n_infos, n_seqs, c->geo.n_heads, c->geo.chunk_size, c->tpp_threshold,
+                                     n_ctas, c->max_chunks, c->opt_split, c->geo.d_head, c->geo.esize, c->fast,
+                                     c->opt_sf_tensor);
+    if (!err.empty()) {
+        if (!*out) delete p;  // a caller-owned plan is left to the caller (its contents are unspecified now)
+        return fail(CA_ERR_INVALID, "work list rejected: " + err);
+    }
+    p->max_chunks = c->max_chunks;
+    p->fast = c->fast;
+    p->d_head = c->geo.d_head;
+    p->esize = c->geo.esize;
+    *out = p;
+    return CA_OK;
+}
+
+int ca_refresh_from_plan(ca_context* c, const ca_plan* plan, ca_stream stream_) {
+    if (!c || !plan) return fail(CA_ERR_INVALID, "null argument");
+    const ca::Plan& pl = plan->plan;
+    const int n_ctas = c->opt_ctas > 0 ? c->opt_ctas : c->num_sms * ca::FAST_CTAS_PER_SM;
+    if (pl.n_heads != c->geo.n_heads || pl.chunk_size != c->geo.chunk_size || plan->d_head != c->geo.d_head ||
+        plan->esize != c->geo.esize || plan->fast != c->fast || plan->max_chunks > c->max_chunks ||
+        pl.split_phases != c->opt_split || pl.tpp_threshold != c->tpp_threshold || (c->fast && pl.n_ctas > n_ctas))
+        return fail(CA_ERR_INVALID, "the plan was built for a different geometry, pool size or set of options");
+    DeviceGuard guard(c->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    c->valid = false;
+    return upload_plan(c, pl, static_cast<cudaStream_t>(stream_));
+}
+
+static int upload_plan(ca_context* c, const ca::Plan& pl, cudaStream_t stream) {
 
     // pack every table into one staging buffer
     struct Part { const void* src; size_t bytes; size_t off; };
@@ -308,6 +359,12 @@ int ca_refresh_kernel_context(ca_context* c, const ca_chunk_info* infos, int n_i
     c->max_tail_tokens = 0;
     for (int32_t t : pl.tail_tokens) c->max_tail_tokens = t > c->max_tail_tokens ? t : c->max_tail_tokens;
     c->delta_tokens = 0;
+    c->meta.n_seqs = pl.n_seqs;
+    c->meta.n_items = (int)pl.items.size();
+    c->meta.n_items_cf = pl.n_items_cf;
+    c->meta.n_ctas = pl.n_ctas;
+    c->meta.split_phases = pl.split_phases;
+    c->meta.stats = pl.stats;
     c->valid = true;
     return CA_OK;
 }
@@ -317,7 +374,7 @@ int ca_context_delta_tokens(const ca_context* c) { return c ? c->delta_tokens : 
 int ca_append_kv(ca_context* c, const void* k, const void* v, int n_seqs, ca_stream stream_) {
     if (!c) return fail(CA_ERR_INVALID, "context is null");
     if (!c->valid) return fail(CA_ERR_STATE, "work list is stale: call ca_refresh_kernel_context first");
-    if (n_seqs != c->plan.n_seqs) return fail(CA_ERR_INVALID, "n_seqs differs from the refreshed work list");
+    if (n_seqs != c->meta.n_seqs) return fail(CA_ERR_INVALID, "n_seqs differs from the refreshed work list");
     if (n_seqs == 0) return CA_OK;
     if (!k || !v) return fail(CA_ERR_INVALID, "k or v is null");
     if (c->max_tail_tokens + c->delta_tokens >= c->geo.chunk_size)
@@ -342,7 +399,7 @@ int ca_append_kv(ca_context* c, const void* k, const void* v, int n_seqs, ca_str
 static int check_attention_args(ca_context* c, const void* q, int n_seqs) {
     if (!c) return fail(CA_ERR_INVALID, "context is null");
     if (!c->valid) return fail(CA_ERR_STATE, "work list is stale: call ca_refresh_kernel_context first");
-    if (n_seqs != c->plan.n_seqs) return fail(CA_ERR_INVALID, "n_seqs differs from the refreshed work list");
+    if (n_seqs != c->meta.n_seqs) return fail(CA_ERR_INVALID, "n_seqs differs from the refreshed work list");
     if (n_seqs > 0 && !q) return fail(CA_ERR_INVALID, "q is null");
     if (reinterpret_cast<uintptr_t>(q) % 16 != 0 && c->fast) return fail(CA_ERR_INVALID, "q must be 16-byte aligned");
     return CA_OK;
@@ -353,7 +410,7 @@ int ca_attn_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_st
     if (rc != CA_OK) return rc;
     if (!c->fast) return fail(CA_ERR_INVALID, "partials exist only for fp16 / d_head 128 / chunk_size 64");
     if (phases < 1 || phases > 3) return fail(CA_ERR_INVALID, "phases must be 1, 2 or 3");
-    if (phases != 3 && !c->plan.split_phases) return fail(CA_ERR_STATE, "single phases need CA_OPT_SPLIT_PHASES");
+    if (phases != 3 && !c->meta.split_phases) return fail(CA_ERR_STATE, "single phases need CA_OPT_SPLIT_PHASES");
     if (n_seqs == 0) return CA_OK;
     DeviceGuard guard(c->device);
     if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
@@ -377,16 +434,16 @@ int ca_attn_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_st
         p.counter = c->counters + c->launch_parity;
         p.counter_next = c->counters + (c->launch_parity ^ 1);
         c->launch_parity ^= 1;
-        const int n_ctas = c->plan.n_ctas < hi - lo ? c->plan.n_ctas : hi - lo;
+        const int n_ctas = c->meta.n_ctas < hi - lo ? c->meta.n_ctas : hi - lo;
         c->trace_ctas = n_ctas;
         return ca::launch_attn_partials(p, n_ctas, stream, (c->opt_pdl & 2) != 0);
     };
-    const int n_items = (int)c->plan.items.size();
-    if (!c->plan.split_phases) {
+    const int n_items = c->meta.n_items;
+    if (!c->meta.split_phases) {
         CA_CUDA(launch(0, n_items));
     } else {
-        if (phases & 1) CA_CUDA(launch(0, c->plan.n_items_cf));
-        if (phases & 2) CA_CUDA(launch(c->plan.n_items_cf, n_items));
+        if (phases & 1) CA_CUDA(launch(0, c->meta.n_items_cf));
+        if (phases & 2) CA_CUDA(launch(c->meta.n_items_cf, n_items));
     }
     return CA_OK;
 }
@@ -409,7 +466,7 @@ bool device_view_of_host(const void* host_ptr, void** dev_ptr) {
 int ca_attention_host(ca_context* c, const void* q_host, void* out_host, int n_seqs, int partition, ca_stream stream_) {
     if (!c) return fail(CA_ERR_INVALID, "context is null");
     if (!c->valid) return fail(CA_ERR_STATE, "work list is stale: call ca_refresh_kernel_context first");
-    if (n_seqs != c->plan.n_seqs) return fail(CA_ERR_INVALID, "n_seqs differs from the refreshed work list");
+    if (n_seqs != c->meta.n_seqs) return fail(CA_ERR_INVALID, "n_seqs differs from the refreshed work list");
     if (partition < 0 || partition > 2) return fail(CA_ERR_INVALID, "Unsupported partition type");
     if (n_seqs == 0) return CA_OK;
     if (!q_host || !out_host) return fail(CA_ERR_INVALID, "q or out is null");
@@ -676,7 +733,7 @@ int ca_context_read_trace(ca_context* c, uint64_t* out, int max_ctas, int* n_cta
 int ca_context_stats(const ca_context* c, ca_plan_stats* out) {
     if (!c || !out) return fail(CA_ERR_INVALID, "null argument");
     if (!c->valid) return fail(CA_ERR_STATE, "work list is stale");
-    *out = c->plan.stats;
+    *out = c->meta.stats;
     return CA_OK;
 }
 

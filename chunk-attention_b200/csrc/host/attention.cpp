@@ -3,6 +3,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 
+#include <cstring>
 #include <iostream>
 #include <stdexcept>
 
@@ -27,6 +28,7 @@ Attention::Attention(Attention& other)
   : n_heads_(other.n_heads_), d_head_(other.d_head_), chunk_size_(other.chunk_size_), memory_mb_(other.memory_mb_),
     tpp_threshold_(other.tpp_threshold_), share_prefix_(other.share_prefix_), options_(other.options_) {
     init();
+    shared_plan_ = other.shared_plan_;  // same configuration, same sequence of tree operations: same work lists
 }
 
 void Attention::init() {
@@ -56,6 +58,11 @@ void Attention::init() {
                                pool_.data_ptr(), max_chunks_, tpp_threshold_),
              "chunk_attn: context");
     valid_ = false;
+    shared_plan_ = std::make_shared<SharedPlan>();
+}
+
+Attention::SharedPlan::~SharedPlan() {
+    if (plan) ca_plan_destroy(plan);
 }
 
 Attention::~Attention() {
@@ -203,8 +210,20 @@ void Attention::refresh_kernel_context(bool force) {
     if (!force && valid_) return;
     std::vector<ca_chunk_info> infos = tree_->get_chunks();
     c10::cuda::CUDAGuard guard(options_.device());
-    check_rc(ca_refresh_kernel_context(ctx_, infos.data(), (int)infos.size(), tree_->n_seqs(), stream()),
-             "refresh_kernel_context");
+    SharedPlan& sp = *shared_plan_;
+    const bool same = sp.plan != nullptr && sp.n_seqs == tree_->n_seqs() && sp.infos.size() == infos.size() &&
+                      (infos.empty() || std::memcmp(sp.infos.data(), infos.data(), infos.size() * sizeof(ca_chunk_info)) == 0);
+    if (!same) {
+        sp.n_seqs = -1;  // nothing to reuse if the rebuild below is refused
+        check_rc(ca_plan_build_for_context(ctx_, &sp.plan, infos.data(), (int)infos.size(), tree_->n_seqs()),
+                 "refresh_kernel_context");
+        sp.infos.swap(infos);
+        sp.n_seqs = tree_->n_seqs();
+        sp.builds++;
+    } else {
+        sp.reuses++;
+    }
+    check_rc(ca_refresh_from_plan(ctx_, sp.plan, stream()), "refresh_kernel_context");
     valid_ = true;
 }
 
@@ -312,6 +331,7 @@ ca_plan_stats Attention::plan_stats() {
 void Attention::set_option(int option, int64_t value) {
     check_rc(ca_context_set_option(ctx_, option, value), "set_option");
     valid_ = false;
+    shared_plan_ = std::make_shared<SharedPlan>();  // its work lists now differ from its siblings'
 }
 
 void Attention::attn_partials(torch::Tensor q, int phases) {

@@ -68,6 +68,8 @@ class Attention {
     ca_plan_stats plan_stats();
     void set_option(int option, int64_t value);
     int device_status();
+    // (plans built, plans reused) by this cache and the caches it shares its work lists with
+    std::pair<int64_t, int64_t> plan_sharing() const { return {shared_plan_->builds, shared_plan_->reuses}; }
     // the two launches of forward(), separately (per-kernel timing)
     void attn_partials(torch::Tensor q, int phases);
     void attn_merge(torch::Tensor out);
@@ -87,6 +89,18 @@ class Attention {
     std::unique_ptr<PrefixTree> tree_;
     ca_context* ctx_ = nullptr;
     bool valid_ = false;
+
+    // The work list of the current tree, shared by the caches made from one another with
+    // Attention(other) (a model's layers): whoever refreshes first after a tree change plans, the
+    // others find their chunk list identical and only upload.
+    struct SharedPlan {
+        std::vector<ca_chunk_info> infos;
+        int n_seqs = -1;
+        ca_plan* plan = nullptr;
+        int64_t builds = 0, reuses = 0;
+        ~SharedPlan();
+    };
+    std::shared_ptr<SharedPlan> shared_plan_;
 
     // add_seq_async: one worker thread, started on first use, runs the queued insertions in order
     void worker_loop();

@@ -88,6 +88,7 @@ PYBIND11_MODULE(chunk_attn_c, m) {
       .def("plan_stats", [](Attention& a) { return stats_to_dict(a.plan_stats()); })
       .def("set_option", &Attention::set_option, py::arg("option"), py::arg("value"))
       .def("device_status", &Attention::device_status)
+      .def("plan_sharing", &Attention::plan_sharing)
       // blocks until the result is in host memory: other Python threads run meanwhile
       .def("forward_host", &Attention::forward_host, py::arg("q"), py::arg("out") = py::none(), py::arg("partition") = 0,
            py::call_guard<py::gil_scoped_release>())

@@ -284,6 +284,16 @@ CA_API int ca_plan_build(ca_plan** out, const ca_chunk_info* infos, int n_infos,
                          int64_t max_chunks, int split_phases, int seq_first_tensor);
 CA_API int ca_plan_array(const ca_plan* plan, int which, const int32_t** data, int64_t* count);
 CA_API int ca_plan_stats_get(const ca_plan* plan, ca_plan_stats* out);
+/* One work list for several contexts.  The caches of a model's layers see the same tree at every step, so
+ * their work lists are identical: build the list once with the parameters of one context (geometry,
+ * options, CTA count) and upload it into each of them.  ca_refresh_from_plan is ca_refresh_kernel_context
+ * without the planning; it refuses a plan built for another geometry, pool size or set of options.  The plan
+ * may be destroyed as soon as the call returns.  *out == NULL makes a new plan; otherwise the plan *out points
+ * to is rebuilt in place (its buffers are reused; after a failed rebuild its contents are unspecified).  No counterpart in the reference, which rebuilds per layer
+ * (src/chunk_attn/models/llama_hf/modeling_llama.py:101-106). */
+CA_API int ca_plan_build_for_context(const ca_context* ctx, ca_plan** out, const ca_chunk_info* infos, int n_infos,
+                                     int n_seqs);
+CA_API int ca_refresh_from_plan(ca_context* ctx, const ca_plan* plan, ca_stream stream);
 CA_API void ca_plan_destroy(ca_plan* plan);
 
 #ifdef __cplusplus

@@ -135,3 +135,45 @@ def test_ragged_prefill_ignores_padding():
     torch.testing.assert_close(both[0], alone[0], atol=2e-3, rtol=0)
     ref = dense_logits(model, short, model.model.cos_sin_cache)[-1]
     assert (both[0].float() - ref).abs().max().item() < LOGIT_TOL
+
+
+def test_layers_share_their_work_lists():
+    """Caches made with Attention(other) plan once per tree change: the first layer to refresh builds the
+    work list, the others find their chunk lists identical and only upload it."""
+    import chunk_attn
+    first = chunk_attn.Attention(n_heads=4, d_head=128, chunk_size=64, memory_mb=32, dtype=torch.float16,
+                                 device=torch.device(DEV))
+    layers = [first] + [chunk_attn.Attention(first) for _ in range(3)]
+    alone = chunk_attn.Attention(n_heads=4, d_head=128, chunk_size=64, memory_mb=32, dtype=torch.float16,
+                                 device=torch.device(DEV))
+    g = torch.Generator().manual_seed(0)
+    shared = list(range(130))
+    ks = [torch.randn(140, 4, 128, generator=g).half().to(DEV) for _ in range(5)]  # one K/V set per cache
+    for s in range(3):
+        toks = shared + [1000 * (s + 1) + j for j in range(10)]
+        for c, k in zip(layers + [alone], ks):
+            c.add_seq(tokens=toks, k=k, v=k)
+    q = torch.randn(3, 4, 128, generator=g).half().to(DEV)
+    outs = [c.forward(q=q) for c in layers]
+    assert first.plan_sharing() == (1, 3)          # built once, reused by the three other layers
+    assert alone.plan_sharing() == (0, 0) and alone.forward(q=q) is not None and alone.plan_sharing() == (1, 0)
+    # every layer computed with its own K/V: same values as a cache that planned for itself
+    for c, k, o in zip(layers, ks, outs):
+        solo = chunk_attn.Attention(n_heads=4, d_head=128, chunk_size=64, memory_mb=32, dtype=torch.float16,
+                                    device=torch.device(DEV))
+        for s in range(3):
+            solo.add_seq(tokens=shared + [1000 * (s + 1) + j for j in range(10)], k=k, v=k)
+        assert torch.equal(solo.forward(q=q), o)
+    # a decode step does not touch the tree shape: no new plan; filling the tails (64 steps later) makes one
+    nk = torch.randn(3, 4, 128, generator=g).half().to(DEV)
+    for c in layers:
+        c.append_token(tokens=[7, 8, 9], k=nk, v=nk)
+        c.forward(q=q)
+    assert first.plan_sharing() == (1, 3)
+    # a cache whose options change plans for itself from then on
+    layers[2].set_option(chunk_attn.cabi.CA_OPT_SEQ_FIRST_TENSOR, 0)
+    for c in layers:
+        c.remove_seq(0)
+        c.forward(q=q[1:].contiguous())
+    assert layers[2].plan_sharing() == (1, 0)
+    assert first.plan_sharing() == (2, 5)
