@@ -607,8 +607,13 @@ def run_b200(args):
             roof = {"bound": "hbm", "kernel": "attn_partial_kernel", "achieved": achieved, "peak": peak,
                     "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch from the ncu capture summarised
-                    # in profiles/attn_partial_kernel_cfg2.md (302.97 MB read + 10.1 MB written); only that workload was captured
-                    "traffic": 313.0e6 if (name == "cfg2" and world == 1) else None,
+                    # in profiles/attn_partial_kernel_cfg2.md (302.97 MB read + 10.1 MB written).  The other
+                    # workloads hold too much on the device to capture: their figure is that capture scaled by
+                    # the unique K/V bytes of a launch (reads are the K/V once, the partial rows written grow with
+                    # them), and traffic_source says so.
+                    "traffic": 313.0e6 if (name == "cfg2" and world == 1) else ukv_local * (313.0e6 / 301989888),
+                    "traffic_source": "ncu capture of this workload" if (name == "cfg2" and world == 1)
+                    else "scaled from the config-2 capture by unique K/V bytes per launch",
                     "algorithmic_bytes_per_launch": ukv_local,
                     "kernel_ms": {"partials_mean": dur_ms, "partials_min": min(kern["partials"]),
                                   "merge_mean": statistics.mean(kern["merge"])}}
