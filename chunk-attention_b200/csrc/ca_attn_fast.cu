@@ -822,9 +822,22 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeParams p) {
     // this kernel's completion before it touches global memory
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (pair >= p.n_pairs) return;
-    // the first 32 partials stay in registers; longer lists are re-read pass by pass
+    // The first 32 partials stay in registers; longer lists are re-read pass by pass.  The O rows of
+    // the first 16 partials are requested together with the (max, sum) pairs, before the weights are
+    // known, so the usual row (a dozen partials) costs ONE round trip after the wait instead of two;
+    // a partial without tokens has no O row (its slot holds stale data), so its row is discarded by
+    // a select, not by a multiplication with zero.
+    constexpr int FIRST = 16;
     float2 ml0 = make_float2(NEG_BIG, 0.f);
     if (slot0 >= 0) ml0 = p.part_ml[slot0];
+    float4 v0[FIRST];
+    const int n0 = min(FIRST, e - b);
+#pragma unroll
+    for (int u = 0; u < FIRST; u++) {
+        const int sk = __shfl_sync(0xffffffffu, slot0, u);
+        v0[u] = (u < n0) ? *reinterpret_cast<const float4*>(p.part_o + (size_t)sk * FAST_D + 4 * lane)
+                         : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     float mm = ml0.y > 0.f ? ml0.x : NEG_BIG;
     for (int i = b + 32 + lane; i < e; i += 32) {
         const float2 ml = p.part_ml[__ldg(p.merge_slots + i)];
@@ -854,7 +867,20 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeParams p) {
             slot = -1;
         }
         const int n = min(32, e - base);
-        for (int k0 = 0; k0 < n; k0 += 8) {
+        int k_begin = 0;
+        if (base == b) {  // the rows requested ahead
+#pragma unroll
+            for (int u = 0; u < FIRST; u++) {
+                const float wu = __shfl_sync(0xffffffffu, w, u);
+                const bool live = wu != 0.f;
+                acc.x = fmaf(wu, live ? v0[u].x : 0.f, acc.x);
+                acc.y = fmaf(wu, live ? v0[u].y : 0.f, acc.y);
+                acc.z = fmaf(wu, live ? v0[u].z : 0.f, acc.z);
+                acc.w = fmaf(wu, live ? v0[u].w : 0.f, acc.w);
+            }
+            k_begin = FIRST;
+        }
+        for (int k0 = k_begin; k0 < n; k0 += 8) {
             float4 v[8];
             float wk[8];
 #pragma unroll
