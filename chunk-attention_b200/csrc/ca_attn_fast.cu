@@ -803,7 +803,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 2) attn_partial_kernel(const Part
 // so it is organised to pay each round trip once: a lane looks up one partial's slot, max and sum
 // (32 partials per pass, usually all of them), the maximum is found with shuffles, and the O rows
 // are then fetched eight at a time with the slot numbers passed around by shuffles.
-__global__ void __launch_bounds__(128) attn_merge_kernel(const MergeParams p) {
+// FIRST: O rows requested ahead of the weights (registers: 4 per row).  Three instances, chosen so that
+// the whole grid is resident at once: 16 rows ahead (3 CTAs per SM), 8 ahead (5 per SM), none ahead
+// (two round trips, 72 registers, 7 per SM) for large batches, where a second wave of CTAs would cost
+// more than the round trip saved.
+template <int FIRST, int MIN_CTAS>
+__global__ void __launch_bounds__(128, MIN_CTAS) attn_merge_kernel(const MergeParams p) {
     const int pair = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     // The merge lists belong to the work list, which was uploaded before the partial kernel started:
@@ -827,16 +832,17 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeParams p) {
     // known, so the usual row (a dozen partials) costs ONE round trip after the wait instead of two;
     // a partial without tokens has no O row (its slot holds stale data), so its row is discarded by
     // a select, not by a multiplication with zero.
-    constexpr int FIRST = 16;
     float2 ml0 = make_float2(NEG_BIG, 0.f);
     if (slot0 >= 0) ml0 = p.part_ml[slot0];
-    float4 v0[FIRST];
-    const int n0 = min(FIRST, e - b);
+    float4 v0[FIRST > 0 ? FIRST : 1];
+    if (FIRST > 0) {
+        const int n0 = min(FIRST, e - b);
 #pragma unroll
-    for (int u = 0; u < FIRST; u++) {
-        const int sk = __shfl_sync(0xffffffffu, slot0, u);
-        v0[u] = (u < n0) ? *reinterpret_cast<const float4*>(p.part_o + (size_t)sk * FAST_D + 4 * lane)
-                         : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int u = 0; u < FIRST; u++) {
+            const int sk = __shfl_sync(0xffffffffu, slot0, u);
+            v0[u] = (u < n0) ? *reinterpret_cast<const float4*>(p.part_o + (size_t)sk * FAST_D + 4 * lane)
+                             : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
     }
     float mm = ml0.y > 0.f ? ml0.x : NEG_BIG;
     for (int i = b + 32 + lane; i < e; i += 32) {
@@ -868,7 +874,7 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeParams p) {
         }
         const int n = min(32, e - base);
         int k_begin = 0;
-        if (base == b) {  // the rows requested ahead
+        if (FIRST > 0 && base == b) {  // the rows requested ahead
 #pragma unroll
             for (int u = 0; u < FIRST; u++) {
                 const float wu = __shfl_sync(0xffffffffu, w, u);
@@ -967,12 +973,22 @@ cudaError_t launch_attn_merge(const MergeParams& p, cudaStream_t stream, bool de
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (dependent_launch && !pdl_disabled) ? 1 : 0;
-    cudaError_t err = cudaLaunchKernelEx(&cfg, attn_merge_kernel, p);
+    // pick the instance whose single wave holds the grid
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int grid = (int)cfg.gridDim.x;
+    auto launch = [&]() {
+        if (grid <= 3 * sms) return cudaLaunchKernelEx(&cfg, attn_merge_kernel<16, 3>, p);
+        if (grid <= 5 * sms) return cudaLaunchKernelEx(&cfg, attn_merge_kernel<8, 5>, p);
+        return cudaLaunchKernelEx(&cfg, attn_merge_kernel<0, 7>, p);
+    };
+    cudaError_t err = launch();
     if (err != cudaSuccess && cfg.numAttrs == 1) {
         // the stream or driver refused the programmatic launch: fall back to a plain ordered launch
         (void)cudaGetLastError();
         cfg.numAttrs = 0;
-        err = cudaLaunchKernelEx(&cfg, attn_merge_kernel, p);
+        err = launch();
     }
     return err;
 }
