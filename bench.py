@@ -382,7 +382,7 @@ def time_reference_cuda(name, dev, steps, warmup):
         return {"us_per_step": None, "note": "oracle/_ref/cuda is not built"}
     w = make_workload(name, total_heads(name), "cpu" if name == "cfg2" else dev)
     if w.n_seqs > 128:
-        return {"us_per_step": None, "note": "the reference's chunk-first kernel supports at most 128 rows"}
+        return time_reference_cuda_standins(ref, w, dev, max(3, min(steps, 10)))
     chunk_bytes = w.n_heads * 2 * 64 * 128 * 2
     n_chunks = W.unique_kv_bytes(w) // chunk_bytes + w.n_seqs + 8
     ra = ref.Attention(n_heads=w.n_heads, d_head=128, chunk_size=64, memory_mb=(n_chunks * chunk_bytes >> 20) + 2,
@@ -402,6 +402,64 @@ def time_reference_cuda(name, dev, steps, warmup):
     torch.cuda.synchronize()
     return {"us_per_step": e0.elapsed_time(e1) / steps * 1e3, "steps": steps,
             "note": "reference CUDA kernels recompiled for sm_100a, same inputs, same GPU, same run"}
+
+
+def time_reference_cuda_standins(ref, w, dev, steps):
+    """The reference's chunk-first kernel exists for batches of 16 to 128 rows only
+    (cpp/chunk_attn/kernel_cuda.cu:1166-1187).  For a larger batch two stand-ins are timed: (a) the batch
+    cut into caches of at most 128 sequences run one after the other (the shared prefix is then stored and
+    read once per cache), (b) one cache with tpp_threshold above the batch size, i.e. its sequence-first
+    kernel alone (the shared prefix is read once per sequence)."""
+    import dataclasses
+    import torch
+    from chunk_attn import workloads as W
+    chunk_bytes = w.n_heads * 2 * 64 * 128 * 2
+    out = {"us_per_step": None, "note": "the reference's chunk-first kernel supports at most 128 rows: stand-ins timed"}
+
+    def timed(fn):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps * 1e3
+
+    def padded_q(q):
+        buf = torch.zeros(q.shape[0] + 160, w.n_heads, 128, device=dev, dtype=torch.float16)
+        buf[:q.shape[0]] = q.to(dev, torch.float16)
+        return buf[:q.shape[0]]
+
+    try:
+        parts = []
+        for lo in range(0, w.n_seqs, 128):
+            sub = dataclasses.replace(w, seqs=w.seqs[lo:lo + 128], q=w.q[lo:lo + 128])
+            n_chunks = W.unique_kv_bytes(sub) // chunk_bytes + sub.n_seqs + 8
+            ra = ref.Attention(n_heads=w.n_heads, d_head=128, chunk_size=64, memory_mb=(n_chunks * chunk_bytes >> 20) + 2,
+                               dtype=torch.float16, device=dev)
+            rows = W.populate(ra, sub, device=dev, dtype=torch.float16)
+            parts.append((ra, padded_q(sub.q[rows])))
+        out["split_into_caches_of_128_us_per_step"] = timed(lambda: [ra.forward(q) for ra, q in parts])
+        del parts
+        torch.cuda.empty_cache()
+    except Exception as exc:  # reported, never a gate
+        out["split_into_caches_of_128_us_per_step"] = "failed: %s" % str(exc)[:160]
+    try:
+        n_chunks = W.unique_kv_bytes(w) // chunk_bytes + w.n_seqs + 8
+        ra = ref.Attention(n_heads=w.n_heads, d_head=128, chunk_size=64, memory_mb=(n_chunks * chunk_bytes >> 20) + 2,
+                           tpp_threshold=w.n_seqs, dtype=torch.float16, device=dev)
+        rows = W.populate(ra, w, device=dev, dtype=torch.float16)
+        q = padded_q(w.q[rows])
+        out["sequence_first_only_us_per_step"] = timed(lambda: ra.forward(q))
+        del ra
+        torch.cuda.empty_cache()
+    except Exception as exc:
+        out["sequence_first_only_us_per_step"] = "failed: %s" % str(exc)[:160]
+    out["steps"] = steps
+    return out
 
 
 # ---- this engine --------------------------------------------------------------------------------------------------
