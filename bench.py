@@ -349,7 +349,29 @@ def time_reference_cpu(name, steps, warmup, max_seconds=150.0):
     us = dt * 1e6 * scale_up
     sample = "%s in fp32, %d of %d heads%s, %d timed forwards (partition 0, chunk-first) after %d warm-up" % (
         name, heads, heads_full, " (time x%g)" % scale_up if scale_up != 1 else "", n, max(1, min(warmup, 3)))
-    return {"value": us, "unit": "us", "cores": cores, "kind": kind, "sample": sample}, n
+    res = {"value": us, "unit": "us", "cores": cores, "kind": kind, "sample": sample, "cpu_model": cpu_model()}
+    if kind == "reference":  # its sequence-first-only path as well, a few forwards
+        try:
+            attn.forward(q, 2)
+            m = max(1, min(n, 5))
+            t0 = time.perf_counter()
+            for _ in range(m):
+                attn.forward(q, 2)
+            res["partition2_sequence_first_us"] = (time.perf_counter() - t0) / m * 1e6 * scale_up
+        except Exception as exc:  # reported, never a gate
+            res["partition2_sequence_first_us"] = "failed: %s" % str(exc)[:120]
+    return res, n
+
+
+def cpu_model():
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.lower().startswith("model name"):
+                    return line.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
 
 
 def run_reference_arm(args):
