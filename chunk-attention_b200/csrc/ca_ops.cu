@@ -128,6 +128,57 @@ __global__ void rotary_kernel(const int64_t* __restrict__ positions, T* __restri
     }
 }
 
+// The same rotation, 16 bytes at a time.  NeoX layout: a thread takes granule u of the x half of a head and
+// the matching granule of the y half (and of the cos and sin halves of the table row).  GPT-J layout: a
+// granule holds EPG / 2 interleaved (x, y) pairs and needs half a granule each of cos and sin.  Element
+// arithmetic is that of rotary_kernel, so the results are bit-identical.
+template <typename T, bool NEOX>
+__global__ void rotary_vec_kernel(const int64_t* __restrict__ positions, T* __restrict__ query, T* __restrict__ key,
+                                  const T* __restrict__ cos_sin_cache, int rot_dim, int64_t q_stride, int64_t k_stride,
+                                  int n_heads, int n_kv_heads, int head_size) {
+    constexpr int EPG = 16 / sizeof(T);
+    struct alignas(16) Pack { T v[EPG]; };
+    struct alignas(8) HalfPack { T v[EPG / 2]; };
+    const int half_rot = rot_dim / 2;
+    const T* cs = cos_sin_cache + positions[blockIdx.x] * rot_dim;
+    const int units_per_head = NEOX ? half_rot / EPG : rot_dim / EPG;
+    const int nq = n_heads * units_per_head, nk = n_kv_heads * units_per_head;
+    for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
+        const bool is_q = i < nq;
+        const int j = is_q ? i : i - nq;
+        const int head = j / units_per_head, u = j - head * units_per_head;
+        T* base = is_q ? query + (size_t)blockIdx.x * q_stride + (size_t)head * head_size
+                       : key + (size_t)blockIdx.x * k_stride + (size_t)head * head_size;
+        if (NEOX) {
+            Pack* xp = reinterpret_cast<Pack*>(base + u * EPG);
+            Pack* yp = reinterpret_cast<Pack*>(base + half_rot + u * EPG);
+            const Pack c = *reinterpret_cast<const Pack*>(cs + u * EPG);
+            const Pack sn = *reinterpret_cast<const Pack*>(cs + half_rot + u * EPG);
+            const Pack x = *xp, y = *yp;
+            Pack xo, yo;
+#pragma unroll
+            for (int k = 0; k < EPG; k++) {
+                xo.v[k] = Elem<T>::rot_x(x.v[k], y.v[k], c.v[k], sn.v[k]);
+                yo.v[k] = Elem<T>::rot_y(x.v[k], y.v[k], c.v[k], sn.v[k]);
+            }
+            *xp = xo;
+            *yp = yo;
+        } else {
+            Pack* pp = reinterpret_cast<Pack*>(base + u * EPG);
+            const HalfPack c = *reinterpret_cast<const HalfPack*>(cs + u * (EPG / 2));
+            const HalfPack sn = *reinterpret_cast<const HalfPack*>(cs + half_rot + u * (EPG / 2));
+            const Pack v = *pp;
+            Pack o;
+#pragma unroll
+            for (int k = 0; k < EPG / 2; k++) {
+                o.v[2 * k] = Elem<T>::rot_x(v.v[2 * k], v.v[2 * k + 1], c.v[k], sn.v[k]);
+                o.v[2 * k + 1] = Elem<T>::rot_y(v.v[2 * k], v.v[2 * k + 1], c.v[k], sn.v[k]);
+            }
+            *pp = o;
+        }
+    }
+}
+
 int threads_for(int work) {
     int t = ((work + 31) / 32) * 32;
     return t < 32 ? 32 : (t > 1024 ? 1024 : t);
@@ -204,21 +255,46 @@ int ca_rotary_embedding(const int64_t* positions, void* query, void* key, const 
         return ca::ops_fail(CA_ERR_INVALID, "rotary_embedding: bad shape");
     if (num_tokens == 0) return CA_OK;
     if (!positions || !query || !key || !cos_sin_cache) return ca::ops_fail(CA_ERR_INVALID, "rotary_embedding: null pointer");
-    const int threads = ca::threads_for((num_heads + num_kv_heads) * rot_dim / 2 < 512 ? (num_heads + num_kv_heads) * rot_dim / 2 : 512);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int n = (int)num_tokens;
+    // 16-byte path: every granule a thread touches must be 16-byte aligned (8 for the half granules of
+    // cos / sin in the GPT-J layout)
+    const int es = dtype == CA_DTYPE_F16 ? 2 : 4;
+    const int epg = 16 / es;
+    auto mult = [](int64_t v, int64_t m) { return v % m == 0; };
+    const bool vec = (dtype == CA_DTYPE_F16 || dtype == CA_DTYPE_F32) &&
+                     mult(reinterpret_cast<uintptr_t>(query), 16) && mult(reinterpret_cast<uintptr_t>(key), 16) &&
+                     mult(reinterpret_cast<uintptr_t>(cos_sin_cache), 16) && mult(query_stride * es, 16) &&
+                     mult(key_stride * es, 16) && mult((int64_t)head_size * es, 16) && mult((int64_t)rot_dim * es, 16) &&
+                     (is_neox ? mult(rot_dim / 2, epg) : mult(rot_dim / 2, epg / 2) && mult((int64_t)(rot_dim / 2) * es, 8));
+    const int units = vec ? (num_heads + num_kv_heads) * (is_neox ? rot_dim / 2 / epg : rot_dim / epg)
+                          : (num_heads + num_kv_heads) * rot_dim / 2;
+    const int threads = ca::threads_for(units < 512 ? units : 512);
+#define CA_ROTV(T, NEOX)                                                                                            \
+    ca::rotary_vec_kernel<T, NEOX><<<n, threads, 0, s>>>(positions, static_cast<T*>(query), static_cast<T*>(key),    \
+                                                         static_cast<const T*>(cos_sin_cache), rot_dim, query_stride, \
+                                                         key_stride, num_heads, num_kv_heads, head_size)
 #define CA_ROT(T, NEOX)                                                                                             \
     ca::rotary_kernel<T, NEOX><<<n, threads, 0, s>>>(positions, static_cast<T*>(query), static_cast<T*>(key),        \
                                                      static_cast<const T*>(cos_sin_cache), rot_dim, query_stride,    \
                                                      key_stride, num_heads, num_kv_heads, head_size)
     if (dtype == CA_DTYPE_F16) {
-        if (is_neox) CA_ROT(__half, true); else CA_ROT(__half, false);
+        if (vec) {
+            if (is_neox) CA_ROTV(__half, true); else CA_ROTV(__half, false);
+        } else {
+            if (is_neox) CA_ROT(__half, true); else CA_ROT(__half, false);
+        }
     } else if (dtype == CA_DTYPE_F32) {
-        if (is_neox) CA_ROT(float, true); else CA_ROT(float, false);
+        if (vec) {
+            if (is_neox) CA_ROTV(float, true); else CA_ROTV(float, false);
+        } else {
+            if (is_neox) CA_ROT(float, true); else CA_ROT(float, false);
+        }
     } else {
         return ca::ops_fail(CA_ERR_INVALID, "rotary_embedding: fp16 and fp32 only");
     }
 #undef CA_ROT
+#undef CA_ROTV
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return ca::ops_fail(CA_ERR_CUDA, cudaGetErrorString(e));
     return CA_OK;
