@@ -585,6 +585,33 @@ def run_b200(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
 
+    # N > 1: where the step's time beyond the local attention goes (max over ranks each)
+    breakdown = None
+    if world > 1:
+        def timed_loop(fn):
+            for _ in range(3):
+                fn()
+            sync_all()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(K):
+                fn()
+            b.record()
+            sync_all()
+            t = torch.tensor([a.elapsed_time(b) / K * 1e3], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+
+        breakdown = {"local_forward_no_gather_us": timed_loop(lambda: attn.forward(q, gather=False))}
+        if attn.gather_mode == "p2p":
+            ql = attn._mine(q).contiguous()
+            bufs = attn._symm_buffers(ql.shape[0], ql.dtype, ql.device)
+            # rows stored into every rank's buffer, no barrier after the step (nobody reads the rows here)
+            breakdown["rows_stored_into_peers_no_barrier_us"] = timed_loop(
+                lambda: attn.local.forward_to_peers(q=ql, peer_out_ptrs=bufs[0][2], total_heads=attn.n_heads,
+                                                    head_offset=attn.rank * attn.h_local))
+            breakdown["barrier_alone_us"] = timed_loop(lambda: bufs[0][1].barrier(channel=0))
+
     # per-kernel durations, CUDA events on the launching stream around each launch of the same steps
     kern = {"partials": [], "merge": [], "chunk_first": [], "seq_first": []}
     if stats["fast_path"]:
@@ -727,6 +754,7 @@ def run_b200(args):
                 "e2e": {"value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": q_host.numel() * 2,
                         "d2h_bytes_per_step": out_host.numel() * 2, "call": e2e_call,
                         "via_forward_and_two_copies_us": e2e_alt},
+                "multi_gpu_breakdown": breakdown,
                 "gpu_launches": K * stats["kernels_per_step"],
                 "clocks": clocks, "device_status": status}
         if single:
