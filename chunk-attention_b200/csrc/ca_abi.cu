@@ -528,6 +528,7 @@ int ca_attn_merge(ca_context* c, void* out, int n_seqs, ca_stream stream_) {
     m.merge_slots = c->d_merge_slots;
     m.out = out;
     m.n_pairs = n_seqs * c->geo.n_heads;
+    m.n_slots_total = c->meta.stats.n_slots;
     CA_CUDA(ca::launch_attn_merge(m, static_cast<cudaStream_t>(stream_), (c->opt_pdl & 1) != 0));
     return CA_OK;
 }
@@ -553,6 +554,7 @@ int ca_attention_to_peers(ca_context* c, const void* q, void* const* peer_out, i
     m.merge_slots = c->d_merge_slots;
     m.out = nullptr;
     m.n_pairs = n_seqs * c->geo.n_heads;
+    m.n_slots_total = c->meta.stats.n_slots;
     m.n_heads = c->geo.n_heads;
     m.n_peers = n_peers;
     m.total_heads = total_heads;

@@ -429,6 +429,11 @@ __device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView&
             have_q = true;
         }
         // only a private tail (a one-row item, TS = 4) can be partially filled
+        if (STAGED_Q && tok0 >= nt) {
+            // none of this warp's tokens exists in the tile: its state stays as it is
+            consumer_release(rg, lane);
+            continue;
+        }
         const bool partial = STAGED_Q && (tok0 + TW > nt);
         if (partial) {
             // Absent tokens: the bulk copy did not fill their rows, so they hold stale bytes.  Their
@@ -807,26 +812,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 2) attn_partial_kernel(const Part
 // the whole grid is resident at once: 16 rows ahead (3 CTAs per SM), 8 ahead (5 per SM), none ahead
 // (two round trips, 72 registers, 7 per SM) for large batches, where a second wave of CTAs would cost
 // more than the round trip saved.
-template <int FIRST, int MIN_CTAS>
-__global__ void __launch_bounds__(128, MIN_CTAS) attn_merge_kernel(const MergeParams p) {
-    const int pair = blockIdx.x * 4 + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    // The merge lists belong to the work list, which was uploaded before the partial kernel started:
-    // as a programmatic dependent this kernel reads them while that kernel is still draining, and
-    // only the partials themselves are read after the wait.
-    int b = 0, e = 0, slot0 = -1;
-    if (pair < p.n_pairs) {
-        b = __ldg(p.merge_off + pair);
-        e = __ldg(p.merge_off + pair + 1);
-        if (b + lane < e) slot0 = __ldg(p.merge_slots + b + lane);
-    }
-    // wait until the partial kernel's results are visible; a no-op for an ordinary launch
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    // the partial kernel is complete: a following kernel launched as a programmatic dependent (the
-    // next step's partial kernel) may set itself up while the rows below are combined; it waits for
-    // this kernel's completion before it touches global memory
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    if (pair >= p.n_pairs) return;
+// The un-normalised combination of the partials merge_slots[b .. e) by one warp: on return mm is their
+// maximum, acc this lane's four output elements weighted by 2^(m_i - mm), ll the warp-wide sum of the
+// weighted sums.  slot0: this lane's slot among the first 32 (-1: none), read by the caller.
+template <int FIRST>
+__device__ __forceinline__ void merge_list(const MergeParams& p, int lane, int b, int e, int slot0, float& mm, float& ll,
+                                           float4& acc) {
     // The first 32 partials stay in registers; longer lists are re-read pass by pass.  The O rows of
     // the first 16 partials are requested together with the (max, sum) pairs, before the weights are
     // known, so the usual row (a dozen partials) costs ONE round trip after the wait instead of two;
@@ -844,7 +835,7 @@ __global__ void __launch_bounds__(128, MIN_CTAS) attn_merge_kernel(const MergePa
                              : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
-    float mm = ml0.y > 0.f ? ml0.x : NEG_BIG;
+    mm = ml0.y > 0.f ? ml0.x : NEG_BIG;
     for (int i = b + 32 + lane; i < e; i += 32) {
         const float2 ml = p.part_ml[__ldg(p.merge_slots + i)];
         if (ml.y > 0.f) mm = fmaxf(mm, ml.x);
@@ -852,8 +843,8 @@ __global__ void __launch_bounds__(128, MIN_CTAS) attn_merge_kernel(const MergePa
 #pragma unroll
     for (int off = 16; off >= 1; off >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, off));
 
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    float ll = 0.f;
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    ll = 0.f;
     for (int base = b; base < e; base += 32) {
         int slot = slot0;
         float2 ml = ml0;
@@ -909,7 +900,10 @@ __global__ void __launch_bounds__(128, MIN_CTAS) attn_merge_kernel(const MergePa
     }
 #pragma unroll
     for (int off = 16; off >= 1; off >>= 1) ll += __shfl_xor_sync(0xffffffffu, ll, off);
-    const float inv = ll > 0.f ? 1.f / ll : 0.f;  // a row with no token yields zeros
+}
+
+// fp16 output row of a pair: to `out`, or into every rank's full-width buffer
+__device__ __forceinline__ void store_row(const MergeParams& p, int pair, int lane, const float4& acc, float inv) {
     const __half2 h01 = __floats2half2_rn(acc.x * inv, acc.y * inv);
     const __half2 h23 = __floats2half2_rn(acc.z * inv, acc.w * inv);
     uint2 packed;
@@ -926,6 +920,74 @@ __global__ void __launch_bounds__(128, MIN_CTAS) attn_merge_kernel(const MergePa
         for (int i = 0; i < MERGE_MAX_PEERS; i++)
             if (i < p.n_peers) *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.peer_out[i]) + off) = packed;
     }
+}
+
+template <int FIRST, int MIN_CTAS>
+__global__ void __launch_bounds__(128, MIN_CTAS) attn_merge_kernel(const MergeParams p) {
+    const int pair = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    // The merge lists belong to the work list, which was uploaded before the partial kernel started:
+    // as a programmatic dependent this kernel reads them while that kernel is still draining, and
+    // only the partials themselves are read after the wait.
+    int b = 0, e = 0, slot0 = -1;
+    if (pair < p.n_pairs) {
+        b = __ldg(p.merge_off + pair);
+        e = __ldg(p.merge_off + pair + 1);
+        if (b + lane < e) slot0 = __ldg(p.merge_slots + b + lane);
+    }
+    // wait until the partial kernel's results are visible; a no-op for an ordinary launch
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // the partial kernel is complete: a following kernel launched as a programmatic dependent (the
+    // next step's partial kernel) may set itself up while the rows below are combined; it waits for
+    // this kernel's completion before it touches global memory
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (pair >= p.n_pairs) return;
+    float mm, ll;
+    float4 acc;
+    merge_list<FIRST>(p, lane, b, e, slot0, mm, ll, acc);
+    store_row(p, pair, lane, acc, ll > 0.f ? 1.f / ll : 0.f);  // a row with no token yields zeros
+}
+
+// Few rows with long lists (one long sequence cut into many pieces, a long shared prefix under a
+// handful of sequences): one CTA per (row, head), each of its 4 warps combines a quarter of the list
+// and the quarters are combined through shared memory.
+__global__ void __launch_bounds__(128, 3) attn_merge_wide_kernel(const MergeParams p) {
+    __shared__ float4 s_acc[4][32];
+    __shared__ float2 s_ml[4];
+    const int pair = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b0 = __ldg(p.merge_off + pair), e0 = __ldg(p.merge_off + pair + 1);
+    const int per = (e0 - b0 + 3) >> 2;
+    const int b = min(e0, b0 + warp * per), e = min(e0, b + per);
+    const int slot0 = b + lane < e ? __ldg(p.merge_slots + b + lane) : -1;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    float mm, ll;
+    float4 acc;
+    merge_list<16>(p, lane, b, e, slot0, mm, ll, acc);
+    s_acc[warp][lane] = acc;
+    if (lane == 0) s_ml[warp] = make_float2(mm, ll);
+    __syncthreads();
+    if (warp != 0) return;
+    float top = NEG_BIG;
+#pragma unroll
+    for (int w = 0; w < 4; w++)
+        if (s_ml[w].y > 0.f) top = fmaxf(top, s_ml[w].x);
+    float4 out = make_float4(0.f, 0.f, 0.f, 0.f);
+    float sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+        if (s_ml[w].y > 0.f) {  // a quarter without tokens contributes nothing
+            const float wgt = fast_exp2(s_ml[w].x - top);
+            const float4 a = s_acc[w][lane];
+            out.x = fmaf(wgt, a.x, out.x);
+            out.y = fmaf(wgt, a.y, out.y);
+            out.z = fmaf(wgt, a.z, out.z);
+            out.w = fmaf(wgt, a.w, out.w);
+            sum = fmaf(wgt, s_ml[w].y, sum);
+        }
+    }
+    store_row(p, pair, lane, out, sum > 0.f ? 1.f / sum : 0.f);
 }
 
 }  // namespace
@@ -978,7 +1040,11 @@ cudaError_t launch_attn_merge(const MergeParams& p, cudaStream_t stream, bool de
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int grid = (int)cfg.gridDim.x;
+    // long lists under few rows: a CTA per row instead of a warp per row (a couple of waves at most)
+    const bool wide = p.n_pairs <= 8 * sms && p.n_slots_total > 48LL * p.n_pairs;
+    if (wide) cfg.gridDim = dim3(p.n_pairs);
     auto launch = [&]() {
+        if (wide) return cudaLaunchKernelEx(&cfg, attn_merge_wide_kernel, p);
         if (grid <= 3 * sms) return cudaLaunchKernelEx(&cfg, attn_merge_kernel<16, 3>, p);
         if (grid <= 5 * sms) return cudaLaunchKernelEx(&cfg, attn_merge_kernel<8, 5>, p);
         return cudaLaunchKernelEx(&cfg, attn_merge_kernel<0, 7>, p);

@@ -58,6 +58,7 @@ struct MergeParams {
     const int32_t* merge_slots;
     void* out;                   // fp16 [n_rows, n_heads, 128]; unused when n_peers > 0
     int n_pairs;                 // n_rows * n_heads
+    long long n_slots_total = 0; // length of merge_slots (picks the kernel instance)
     // Head-sharded output written straight into every rank's full-width buffer (peer memory over
     // NVLink): row s, local head h goes to peer_out[i] + ((s * total_heads) + head_offset + h) * 128.
     int n_heads = 0;             // local heads (needed to split a pair index when n_peers > 0)

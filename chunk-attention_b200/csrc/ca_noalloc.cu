@@ -134,6 +134,7 @@ int ca_attention_static(const void* pool, int n_heads, const void* q, void* out,
     m.merge_slots = merge_slots;
     m.out = out;
     m.n_pairs = n_seqs * n_heads;
+    m.n_slots_total = n_slots;
     e = ca::launch_attn_merge(m, stream, true);
     if (e != cudaSuccess) return fail(CA_ERR_CUDA, std::string("merge kernel launch: ") + cudaGetErrorString(e));
     return CA_OK;
