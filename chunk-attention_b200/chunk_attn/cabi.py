@@ -42,7 +42,7 @@ class PlanStats(C.Structure):
     _fields_ = [("unique_kv_bytes", C.c_int64), ("n_chunks", C.c_int32), ("n_shared_chunks", C.c_int32),
                 ("n_runs", C.c_int32), ("n_items", C.c_int32), ("n_slots", C.c_int32),
                 ("n_ctas", C.c_int32), ("fast_path", C.c_int32), ("kernels_per_step", C.c_int32),
-                ("n_items_cf", C.c_int32)]
+                ("n_items_cf", C.c_int32), ("n_items_short", C.c_int32)]
 
     def as_dict(self):
         return {f: getattr(self, f) for f, _ in self._fields_}

@@ -90,7 +90,7 @@ struct ca_context {
     ca::Plan plan;  // scratch of ca_refresh_kernel_context (vectors keep their capacity)
     // what the launches need to know about the work list that is on the device
     struct {
-        int n_seqs = 0, n_items = 0, n_items_cf = 0, n_ctas = 1;
+        int n_seqs = 0, n_items = 0, n_items_cf = 0, n_items_short = 0, n_ctas = 1;
         bool split_phases = false;
         ca_plan_stats stats{};
     } meta;
@@ -362,6 +362,7 @@ static int upload_plan(ca_context* c, const ca::Plan& pl, cudaStream_t stream) {
     c->meta.n_seqs = pl.n_seqs;
     c->meta.n_items = (int)pl.items.size();
     c->meta.n_items_cf = pl.n_items_cf;
+    c->meta.n_items_short = pl.n_items_short;
     c->meta.n_ctas = pl.n_ctas;
     c->meta.split_phases = pl.split_phases;
     c->meta.stats = pl.stats;
@@ -438,7 +439,14 @@ int ca_attn_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_st
         c->trace_ctas = n_ctas;
         return ca::launch_attn_partials(p, n_ctas, stream, (c->opt_pdl & 2) != 0);
     };
-    const int n_items = c->meta.n_items;
+    // the short private tails (the last n_items_short items) have a kernel of their own, launched first so
+    // that the persistent kernel's tail leads straight into the merge
+    const int n_items = c->meta.n_items - c->meta.n_items_short;
+    if (c->meta.n_items_short > 0 && (phases & 2)) {
+        p.item_lo = n_items;
+        p.item_hi = c->meta.n_items;
+        CA_CUDA(ca::launch_attn_short_tails(p, stream, (c->opt_pdl & 2) != 0));
+    }
     if (!c->meta.split_phases) {
         CA_CUDA(launch(0, n_items));
     } else {

@@ -812,6 +812,104 @@ __global__ void __launch_bounds__(NUM_THREADS, 2) attn_partial_kernel(const Part
 // the whole grid is resident at once: 16 rows ahead (3 CTAs per SM), 8 ahead (5 per SM), none ahead
 // (two round trips, 72 registers, 7 per SM) for large batches, where a second wave of CTAs would cost
 // more than the round trip saved.
+// ---- short private tails ---------------------------------------------------------------------------------
+// A (sequence, head) whose private part is a single, usually partly filled, chunk is too small an item
+// for the persistent kernel (an item costs its warps the same whatever it holds).  When a batch has
+// many of them the planner puts them at the end of the item list and this kernel walks them instead:
+// one WARP per item, straight from global memory.  A half-warp reads one K row per load (coalesced, the
+// query granule of each lane in registers) and sums the products over its 16 lanes, maximum and sum come
+// from shuffles, and in P.V each lane owns four output elements (coalesced 8-byte reads along a V row).  The result is an ordinary partial (max and sum in log2
+// units, un-normalised O), combined with the row's other partials by the merge kernel.
+constexpr int SHORT_WARPS = 8;
+
+__global__ void __launch_bounds__(SHORT_WARPS * 32) attn_short_tails_kernel(const PartialParams p) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int idx = p.item_lo + (int)blockIdx.x * SHORT_WARPS + warp;
+    if (idx >= p.item_hi) return;
+    const int4 d0 = __ldg(p.items + 4 * idx), d1 = __ldg(p.items + 4 * idx + 1);
+    const int head = d0.y, row = d0.z, slot = d1.x, flags = d1.y, chunk = d1.w;
+    const int nt = min(FAST_C, d1.z + ((flags & ITEM_FLAG_TAIL) ? p.delta_tokens : 0));
+    if (nt <= 0) {  // an empty reserved tail
+        if (lane == 0) p.part_ml[slot] = make_float2(NEG_BIG, 0.f);
+        return;
+    }
+    // A half-warp reads one 256-byte K row per load, lane & 15 = granule: each lane keeps its granule of
+    // the query (pre-scaled to log2 units) in registers.
+    const int g16 = lane & 15, half = lane >> 4;
+    float qf[8];
+    {
+        const __half* q = reinterpret_cast<const __half*>(p.q) + ((size_t)row * p.n_heads + head) * FAST_D + 8 * g16;
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(q));
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const float2 f = __half22float2(h[k]);
+            qf[2 * k] = f.x * p.scale_log2;
+            qf[2 * k + 1] = f.y * p.scale_log2;
+        }
+    }
+    const uint8_t* ktile = p.pool + ((size_t)chunk * p.n_heads + head) * (size_t)FAST_STAGE_BYTES;
+    const uint8_t* vtile = ktile + FAST_TILE_BYTES;
+
+    // Scores in log2 units.  Step i of round r: the lower half-warp takes token 32 r + i, the upper one
+    // token 32 r + 16 + i (two coalesced rows per load); after the 16-lane sum the lane whose number is
+    // the token's (mod 32) keeps the score, so lane j ends up owning tokens j and j + 32.
+    float sc[2] = {NEG_BIG, NEG_BIG};
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        if (32 * r < nt) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const int t = 32 * r + 16 * half + i;
+                float acc = 0.f;
+                if (t < nt) {
+                    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(ktile + t * (FAST_D * 2) + ((g16 ^ (t & 7)) << 4)));
+                    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const float2 f = __half22float2(h[k]);
+                        acc = fmaf(qf[2 * k], f.x, acc);
+                        acc = fmaf(qf[2 * k + 1], f.y, acc);
+                    }
+                }
+#pragma unroll
+                for (int off = 8; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+                if (g16 == i && t < nt) sc[r] = acc;
+            }
+        }
+    }
+    float m = fmaxf(sc[0], sc[1]);
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    const float p0 = lane < nt ? fast_exp2(sc[0] - m) : 0.f;
+    const float p1 = lane + 32 < nt ? fast_exp2(sc[1] - m) : 0.f;
+    float l = p0 + p1;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+
+    // O = P V: this lane's four output elements are 8 bytes of granule lane / 2 of every V row
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int gran = lane >> 1, sub = (lane & 1) << 3;
+    auto add_row = [&](int t, float pw) {
+        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(vtile + t * (FAST_D * 2) + ((gran ^ (t & 7)) << 4) + sub));
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+        const float2 a = __half22float2(h[0]), b = __half22float2(h[1]);
+        acc.x = fmaf(pw, a.x, acc.x);
+        acc.y = fmaf(pw, a.y, acc.y);
+        acc.z = fmaf(pw, b.x, acc.z);
+        acc.w = fmaf(pw, b.y, acc.w);
+    };
+    const int n_lo = min(nt, 32);
+#pragma unroll 4
+    for (int t = 0; t < n_lo; t++) add_row(t, __shfl_sync(0xffffffffu, p0, t));
+#pragma unroll 4
+    for (int t = 32; t < nt; t++) add_row(t, __shfl_sync(0xffffffffu, p1, t - 32));
+    *reinterpret_cast<float4*>(p.part_o + (size_t)slot * FAST_D + 4 * lane) = acc;
+    if (lane == 0) p.part_ml[slot] = make_float2(m, l);
+}
+
 // The un-normalised combination of the partials merge_slots[b .. e) by one warp: on return mm is their
 // maximum, acc this lane's four output elements weighted by 2^(m_i - mm), ll the warp-wide sum of the
 // weighted sums.  slot0: this lane's slot among the first 32 (-1: none), read by the caller.
@@ -1018,6 +1116,29 @@ cudaError_t launch_attn_partials(const PartialParams& p, int n_ctas, cudaStream_
         (void)cudaGetLastError();
         cfg.numAttrs = 0;
         err = cudaLaunchKernelEx(&cfg, attn_partial_kernel, p);
+    }
+    return err;
+}
+
+cudaError_t launch_attn_short_tails(const PartialParams& p, cudaStream_t stream, bool dependent_launch) {
+    const int n = p.item_hi - p.item_lo;
+    if (n <= 0) return cudaSuccess;
+    static const bool pdl_disabled = std::getenv("CA_DISABLE_PDL") != nullptr;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((n + SHORT_WARPS - 1) / SHORT_WARPS);
+    cfg.blockDim = dim3(SHORT_WARPS * 32);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (dependent_launch && !pdl_disabled) ? 1 : 0;
+    cudaError_t err = cudaLaunchKernelEx(&cfg, attn_short_tails_kernel, p);
+    if (err != cudaSuccess && cfg.numAttrs == 1) {
+        (void)cudaGetLastError();
+        cfg.numAttrs = 0;
+        err = cudaLaunchKernelEx(&cfg, attn_short_tails_kernel, p);
     }
     return err;
 }

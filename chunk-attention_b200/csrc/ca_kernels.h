@@ -48,6 +48,8 @@ struct PartialParams {
 // grid = n_ctas (FAST_CTAS_PER_SM per SM).
 // dependent_launch: allow the CTAs to be set up while the preceding kernel of the stream is finishing
 cudaError_t launch_attn_partials(const PartialParams& p, int n_ctas, cudaStream_t stream, bool dependent_launch = false);
+// one warp per item over items [item_lo, item_hi): single-tile one-row items only (short private tails)
+cudaError_t launch_attn_short_tails(const PartialParams& p, cudaStream_t stream, bool dependent_launch = false);
 cudaError_t configure_fast_kernels();  // once per device before the first launch
 
 constexpr int MERGE_MAX_PEERS = 8;

@@ -24,8 +24,12 @@ std::string fmt(const char* f, long a = 0, long b = 0, long c = 0) {
 // Cut the units [ubegin, uend) into items.  Guided self-scheduling: an item takes
 // remaining_tiles / n_ctas tiles, clamped to [1, MAX_TILES_PER_ITEM], so the list starts with
 // full-size items and ends with single tiles.
-void cut_units(Plan& plan, const std::vector<Unit>& units, size_t ubegin, size_t uend, int n_ctas, int32_t& n_slots) {
-    int64_t remaining = 0;
+void cut_units(Plan& plan, const std::vector<Unit>& units, size_t ubegin, size_t uend, int n_ctas, int32_t& n_slots,
+               int64_t tiles_elsewhere = 0) {
+    // tiles_elsewhere: work of the same step that other kernels do (the short tails); counting it keeps
+    // the pieces of shared runs long - every piece of a run costs a partial row per sharer, so they
+    // are not tapered down to single tiles for the sake of the last microsecond
+    int64_t remaining = tiles_elsewhere;
     for (size_t u = ubegin; u < uend; u++) remaining += units[u].n_chunks;
     for (size_t u = ubegin; u < uend; u++) {
         const Unit& un = units[u];
@@ -68,6 +72,7 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
     plan.tail_chunk.clear();
     plan.tail_tokens.clear();
     plan.n_items_cf = 0;
+    plan.n_items_short = 0;
     plan.n_ctas = 1;
     plan.stats = ca_plan_stats{};
     if (n_infos < 0 || n_seqs < 0 || n_heads <= 0 || chunk_size <= 0 || n_ctas <= 0)
@@ -181,6 +186,21 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
         }
     }
     const size_t n_units_cf = units.size();
+    // Sequences whose private part is a single chunk (a short tail).  When there are many of them they
+    // are not walked by the persistent kernel, where an item costs the same whatever its size, but by
+    // a kernel of their own with one warp per (sequence, head); their items go to the end of the list.
+    std::vector<Unit> short_units;
+    bool route_short = false;
+    if (seq_first_tensor) {
+        int64_t n_short = 0;
+        for (int s = 0; s < n_seqs; s++) {
+            int n_priv = 0;
+            for (int32_t p = plan.path_off[s]; p < plan.path_off[s + 1]; p++) n_priv += shared[path_info[p]] ? 0 : 1;
+            n_short += n_priv == 1 ? n_heads : 0;
+        }
+        route_short = n_short > n_ctas;
+        if (route_short) short_units.reserve((size_t)n_short);
+    }
     for (int s = 0; s < n_seqs; s++) {
         const int32_t* priv = priv_arena.data() + priv_arena.size();
         int32_t n_priv = 0;
@@ -193,8 +213,9 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
         for (int32_t p = plan.path_off[s]; p + 1 < plan.path_off[s + 1]; p++)
             if (!shared[path_info[p]] && plan.path_tokens[p] != chunk_size)
                 return fmt("row %ld has a partially filled chunk that is not its tail", s);
+        std::vector<Unit>& dst = (route_short && n_priv == 1) ? short_units : units;
         for (int h = 0; h < n_heads; h++)
-            units.push_back(Unit{priv, n_priv, h, s, 1, seq_first_tensor ? 4 : 0, plan.tail_tokens[s], true});
+            dst.push_back(Unit{priv, n_priv, h, s, 1, seq_first_tensor ? 4 : 0, plan.tail_tokens[s], true});
     }
 
     // ---- items ---------------------------------------------------------------------------------------------
@@ -204,8 +225,9 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
         for (const Unit& u : units) tiles += u.n_chunks;
         plan.items.reserve((size_t)(tiles / 4 + units.size() + 4 * (size_t)n_ctas));
     }
+    const int64_t short_tiles = (int64_t)short_units.size();
     if (!split_phases) {
-        cut_units(plan, units, 0, units.size(), n_ctas, n_slots);
+        cut_units(plan, units, 0, units.size(), n_ctas, n_slots, short_tiles);
         plan.n_items_cf = 0;
         for (const PlanItem& it : plan.items) plan.n_items_cf += it.n_rows > 1 ? 1 : 0;
         plan.stats.kernels_per_step = 2;
@@ -217,6 +239,21 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
         plan.stats.kernels_per_step = (plan.n_items_cf > 0 ? 1 : 0) + 2;
     }
     plan.n_ctas = (int)std::min<int64_t>(n_ctas, std::max<int64_t>(1, (int64_t)plan.items.size()));
+    // the short tails: one single-tile item each, after the persistent kernel's items
+    plan.n_items_short = (int)short_units.size();
+    for (const Unit& un : short_units) {
+        plan.items.emplace_back();
+        PlanItem& it = plan.items.back();
+        it.n_tiles = 1;
+        it.head = un.head;
+        it.row_begin = un.row_begin;
+        it.n_rows = 1;
+        it.slot_base = n_slots++;
+        it.flags = ITEM_FLAG_TAIL | (un.splits << ITEM_SPLITS_SHIFT);
+        it.last_tokens = un.last_tokens;
+        it.chunk[0] = un.chunks[0];
+    }
+    if (plan.n_items_short > 0) plan.stats.kernels_per_step += 1;
 
     // ---- merge lists -------------------------------------------------------------------------------------
     for (const PlanItem& it : plan.items) {
@@ -241,6 +278,7 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
     }
     plan.stats.n_items = (int)plan.items.size();
     plan.stats.n_items_cf = plan.n_items_cf;
+    plan.stats.n_items_short = plan.n_items_short;
     plan.stats.n_slots = n_slots;
     plan.stats.n_ctas = plan.n_ctas;
     return "";

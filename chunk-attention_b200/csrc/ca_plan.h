@@ -50,8 +50,9 @@ static_assert(sizeof(PlanItem) == 64, "PlanItem is read on the device as four in
 struct Plan {
     int n_seqs = 0, n_heads = 0, chunk_size = 0, tpp_threshold = 1, n_ctas = 1;
     bool split_phases = false;
-    std::vector<PlanItem> items;          // chunk-first items first
+    std::vector<PlanItem> items;          // chunk-first items first, short tails last
     int n_items_cf = 0;                   // how many of them are chunk-first items
+    int n_items_short = 0;                // how many at the END of the list are short tails for the warp-per-item kernel
     std::vector<int32_t> merge_off, merge_slots;
     std::vector<int32_t> path_off, path_chunks, path_tokens;
     std::vector<int32_t> tail_chunk, tail_tokens;

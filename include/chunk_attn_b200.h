@@ -203,6 +203,8 @@ typedef struct ca_plan_stats {
     int32_t fast_path;         /* 1 when the tensor-core/TMA kernels serve this geometry          */
     int32_t kernels_per_step;  /* launches one ca_attention call makes                            */
     int32_t n_items_cf;        /* how many items are chunk-first items (they come first)          */
+    int32_t n_items_short;     /* how many items, at the end of the list, are short private tails
+                                  walked by the warp-per-item kernel instead of the persistent one */
 } ca_plan_stats;
 CA_API int ca_context_stats(const ca_context* ctx, ca_plan_stats* out);
 
