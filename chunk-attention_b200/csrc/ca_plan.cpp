@@ -198,7 +198,7 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
             for (int32_t p = plan.path_off[s]; p < plan.path_off[s + 1]; p++) n_priv += shared[path_info[p]] ? 0 : 1;
             n_short += n_priv == 1 ? n_heads : 0;
         }
-        route_short = n_short > n_ctas;
+        route_short = n_short > 4 * (int64_t)n_ctas;  // fewer are cheaper inside the persistent kernel than a launch of their own
         if (route_short) short_units.reserve((size_t)n_short);
     }
     for (int s = 0; s < n_seqs; s++) {

@@ -134,3 +134,26 @@ def test_one_very_long_sequence_and_short_neighbours():
     for _ in range(3):
         m.append_all()
     m.check()
+
+
+def test_many_short_tails_take_the_warp_per_item_kernel():
+    """400 rows whose private part is a fraction of one chunk: their items go to the warp-per-item kernel
+    (plan_stats n_items_short), through appended tokens without a rebuild and across the chunk boundary."""
+    m = Mirror(4, 13, memory_mb=512)
+    rnd = random.Random(13)
+    m.add(None, 0, 256 + 3)
+    for _ in range(399):
+        m.add(0, 256, rnd.randint(1, 60))
+    m.check()
+    st = m.attn.plan_stats()
+    assert st["n_items_short"] >= 390 * 4 and st["kernels_per_step"] == 3
+    for step in range(70):  # every tail fills up and gets a successor on the way
+        m.append_all()
+        if step % 10 == 9:
+            m.check()
+    # rows without any shared prefix, all short: the persistent kernel has nothing to do
+    m2 = Mirror(4, 14, memory_mb=512)
+    for _ in range(320):
+        m2.add(None, 0, rnd.randint(1, 64))
+    m2.check()
+    assert m2.attn.plan_stats()["n_items_short"] >= 300 * 4  # (a row of exactly 64 tokens has a full chunk + an empty tail)

@@ -190,11 +190,11 @@ def test_rejects_bad_work_lists():
 
 def test_short_tails_go_to_the_end_of_the_list_when_there_are_many():
     """Private parts of a single chunk become single-tile items after the persistent kernel's items as soon as
-    there are more of them than CTAs; the merge lists do not care who writes a slot."""
+    there are more of them than four per CTA; the merge lists do not care who writes a slot."""
     H, d = 2, 8
     spec = shared_spec(6, 2 * C, 5) + shared_spec(2, 2 * C, 3 * C + 7, base=0)  # 6 short tails, 2 long private parts
     ora = build_tree(spec, H, d)
-    plan, _ = check(ora, H, d, n_ctas=4)          # 12 short items > 4 CTAs: routed
+    plan, _ = check(ora, H, d, n_ctas=2)          # 12 short items > 4 x 2 CTAs: routed
     st = plan.stats()
     items = plan.items()
     assert st["n_items_short"] == 6 * H and st["kernels_per_step"] == 3
@@ -203,7 +203,7 @@ def test_short_tails_go_to_the_end_of_the_list_when_there_are_many():
     assert sorted((int(r[2]), int(r[1])) for r in tail) == [(s, h) for s in range(6) for h in range(H)]
     main = items[:-st["n_items_short"]]
     assert not any(int(r[3]) == 1 and int(r[2]) < 6 for r in main)                     # none of them is walked twice
-    plan2, _ = check(ora, H, d, n_ctas=64)        # 12 short items <= 64 CTAs: they stay in the main list
+    plan2, _ = check(ora, H, d, n_ctas=64)        # 12 short items <= 4 x 64 CTAs: they stay in the main list
     assert plan2.stats()["n_items_short"] == 0 and plan2.stats()["kernels_per_step"] == 2
-    plan3, _ = check(ora, H, d, n_ctas=4, seq_first_tensor=False)   # the CUDA-core option keeps its own walk
+    plan3, _ = check(ora, H, d, n_ctas=2, seq_first_tensor=False)   # the CUDA-core option keeps its own walk
     assert plan3.stats()["n_items_short"] == 0
