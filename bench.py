@@ -12,7 +12,8 @@ Workloads (synthetic, seeded; chunk_attn/workloads.py):
          K/V, larger than the 126 MB L2, so nothing needs flushing between steps)
   N > 1  cfg5: H64 split evenly over the ranks, 256 sequences = 4096 shared + 1024 unique tokens,
          output all-gathered (NCCL); strong scaling: total work is fixed
-`--workload` overrides the choice (cfg2, cfg5, cfg3_s<shared>, cfg4, llama: the decoder loop).
+`--workload` overrides the choice (cfg2, cfg5, cfg3_s<shared>, cfg4, short<n_seqs>: a 1024-token common
+prompt with 20-token private suffixes, llama: the decoder loop).
 """
 import argparse
 import json
@@ -65,6 +66,9 @@ def describe(name, n_gpus):
     if name == "cfg5":
         return ("cfg5: H64 (H/%d per GPU) d128 c64 fp16, 256 seqs x (4096 shared + 1024 unique tokens), "
                 "1 query/seq, output all-gathered" % n_gpus)
+    if name.startswith("short"):
+        return ("%s: H32 d128 c64 fp16, %s seqs x (1024 shared + 20 unique tokens): a long common prompt with short "
+                "private suffixes" % (name, name[5:] or "256"))
     return "%s: H32 d128 c64 fp16, 64 seqs, context 4096, shared prefix %s" % (name, name.split("_s")[-1])
 
 
@@ -78,6 +82,9 @@ def make_workload(name, n_heads_local, gen_device, rank=0):
         return w
     if name.startswith("cfg3_s"):
         return W.config3(int(name[6:]), n_heads=n_heads_local, gen_device=gen_device)
+    if name.startswith("short"):  # short<n_seqs>: not one of the five configurations; the short-suffix serving shape
+        return W.single_level(name, n_heads_local, 128, 64, __import__("torch").float16, int(name[5:] or 256), 1024, 20,
+                              5, 0.5, gen_device)
     raise SystemExit("unknown workload " + name)
 
 
