@@ -4,6 +4,7 @@ token, so every request's output is known in advance and the batch order can be 
 trees' row order at every step."""
 import random
 import threading
+import time
 
 import pytest
 
@@ -182,8 +183,10 @@ def test_stop_cancels_running_sequences_and_cleans_the_caches():
     host, caches = make_host()
     host.start()
     s = host.predict_async([1, 2, 3], 10 ** 9)
-    while host.n_decode_steps < 3:
-        pass
+    deadline = time.monotonic() + 20
+    while host.n_decode_steps < 3 and host.failure is None:
+        assert time.monotonic() < deadline, "the worker made no progress"
+        time.sleep(0.001)
     host.stop()
     with pytest.raises(RuntimeError, match="stopped before"):
         s.get_result(timeout=5)
