@@ -16,6 +16,8 @@ CA_OK = 0
 CA_ERR_INVALID, CA_ERR_CUDA, CA_ERR_STATE, CA_ERR_DEVICE_STATUS = -1, -2, -3, -4
 CA_DTYPE_F16, CA_DTYPE_F32 = 0, 1
 CA_OPT_SPLIT_PHASES, CA_OPT_NUM_CTAS, CA_OPT_SEQ_FIRST_TENSOR, CA_OPT_TRACE, CA_OPT_DEPENDENT_LAUNCH = 1, 2, 3, 4, 5
+CA_OPT_WAIT_LIMIT_CYCLES, CA_OPT_TEST_WITHHOLD_ITEM = 7, 8
+STATUS_FULL_WAIT_TIMEOUT, STATUS_EMPTY_WAIT_TIMEOUT, STATUS_DRAIN_TIMEOUT, STATUS_BAD_WORK_LIST, STATUS_BAD_POSITION = 1, 2, 3, 4, 5
 PLAN_ITEMS = 0
 (PLAN_MERGE_OFF, PLAN_MERGE_SLOTS, PLAN_PATH_OFF, PLAN_PATH_CHUNKS, PLAN_PATH_TOKENS, PLAN_TAIL_CHUNK,
  PLAN_TAIL_TOKENS) = range(3, 10)
@@ -25,9 +27,9 @@ EXPORTED = [
     "ca_last_error", "ca_version", "ca_chunk_bytes", "ca_tile_elem_offset", "ca_context_create",
     "ca_context_destroy", "ca_context_set_option", "ca_refresh_kernel_context", "ca_append_kv",
     "ca_context_delta_tokens", "ca_attention", "ca_attention_host", "ca_attention_to_peers", "ca_attn_partials", "ca_attn_merge",
-    "ca_scatter_prefill", "ca_scatter_rows", "ca_copy_chunks", "ca_read_chunk", "ca_status_read", "ca_context_stats",
+    "ca_scatter_prefill", "ca_scatter_rows", "ca_copy_chunks", "ca_read_chunk", "ca_status_read", "ca_status_clear", "ca_context_stats",
     "ca_context_read_trace",
-    "ca_plan_build", "ca_plan_build_for_context", "ca_refresh_from_plan", "ca_plan_array", "ca_plan_stats_get", "ca_plan_destroy", "ca_attention_static",
+    "ca_plan_build", "ca_plan_build_for_context", "ca_refresh_from_plan", "ca_plan_array", "ca_plan_stats_get", "ca_plan_destroy", "ca_attention_static", "ca_attention_static_status",
     "ca_rms_norm", "ca_fused_add_rms_norm", "ca_rotary_embedding",
 ]
 CA_STATIC_MAX_SLOTS = 16384
@@ -80,6 +82,7 @@ def _load():
         "ca_copy_chunks": (i32, [vp, C.POINTER(C.c_int32), C.POINTER(C.c_int32), i32, vp]),
         "ca_read_chunk": (i32, [vp, i32, i32, vp, vp, vp]),
         "ca_status_read": (i32, [vp, vp, C.POINTER(C.c_int32)]),
+        "ca_status_clear": (i32, [vp, vp]),
         "ca_context_stats": (i32, [vp, C.POINTER(PlanStats)]),
         "ca_context_read_trace": (i32, [vp, C.POINTER(C.c_uint64), i32, C.POINTER(i32), vp]),
         "ca_plan_build": (i32, [C.POINTER(vp), C.POINTER(ChunkInfo), i32, i32, i32, i32, i32, i32, i64, i32, i32]),
@@ -90,8 +93,9 @@ def _load():
         "ca_plan_destroy": (None, [vp]),
         "ca_rms_norm": (i32, [vp, vp, vp, C.c_float, i64, i32, i32, vp]),
         "ca_fused_add_rms_norm": (i32, [vp, vp, vp, C.c_float, i64, i32, i32, vp]),
-        "ca_rotary_embedding": (i32, [vp, vp, vp, vp, i32, i64, i64, i32, i32, i32, i64, i32, i32, vp]),
+        "ca_rotary_embedding": (i32, [vp, vp, vp, vp, i32, i64, i64, i32, i32, i32, i64, i32, i32, i64, vp, vp]),
         "ca_attention_static": (i32, [vp, i32, vp, vp, i32, vp, i32, i32, vp, vp, i32, i32, vp, vp]),
+        "ca_attention_static_status": (i32, [C.POINTER(C.c_int32), vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -220,6 +224,15 @@ class Context:
         st = C.c_int32()
         check(lib.ca_status_read(self._h, self._stream(), C.byref(st)))
         return st.value
+
+    def status_raw(self):
+        """(return code, status word): CA_ERR_DEVICE_STATUS with the kernel's code when a kernel reported one."""
+        st = C.c_int32()
+        rc = lib.ca_status_read(self._h, self._stream(), C.byref(st))
+        return rc, st.value
+
+    def status_clear(self):
+        check(lib.ca_status_clear(self._h, self._stream()))
 
     def stats(self):
         st = PlanStats()

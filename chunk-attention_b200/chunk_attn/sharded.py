@@ -11,8 +11,15 @@ on every rank, in one of two ways:
                  stream: compute and gather in a single kernel, no collective call and no permute.
 The reference itself is single-device (no torch.distributed anywhere in it).
 """
+import time
+
 import torch
 import torch.distributed as dist
+
+
+class PeerLost(RuntimeError):
+    """A rank of the group left, or did not reach the step within the time allowed.  Raised on the HOST, before
+    anything of the step is launched, so no kernel or collective is left waiting for the missing rank."""
 
 
 class HeadShardedAttention:
@@ -37,6 +44,52 @@ class HeadShardedAttention:
             raise ValueError("gather must be 'nccl' or 'p2p'")
         self.gather_mode = gather if self.world > 1 else "nccl"
         self._symm = None      # (tensor [rows, H, d], handle, peer pointers)
+        # host-side liveness check (off unless check_peers / peer_timeout_s is used)
+        self.peer_timeout_s = None
+        self._hb_store = None
+        self._hb_step = 0
+        self._hb_prefix = "ca_hb"
+
+    # ---- failure detection: on the host, between steps -----------------------------------------------------
+    def enable_peer_check(self, timeout_s, store=None, prefix="ca_hb"):
+        """From now on every forward() first makes sure, through the process group's key-value store, that all
+        ranks have reached the same step and that none has left; a missing rank raises PeerLost after
+        `timeout_s` instead of leaving this rank's kernels (or its next collective) waiting on the device.
+        Costs one store round trip per step, so it is meant for serving loops where a step is milliseconds."""
+        if self.world == 1:
+            return
+        self._hb_store = store if store is not None else dist.distributed_c10d._get_default_store()
+        self.peer_timeout_s = float(timeout_s)
+        self._hb_prefix = prefix
+        self._hb_step = 0
+
+    def check_peers(self):
+        """One liveness round (called by forward() when enabled): announce this rank's arrival at the step, then
+        wait until every rank has arrived.  Raises PeerLost when a rank has announced its departure with leave()
+        or when the wait runs out."""
+        if self._hb_store is None:
+            return
+        st, step = self._hb_store, self._hb_step
+        self._hb_step += 1
+        key = "%s/step/%d" % (self._hb_prefix, step)
+        st.add(key, 1)
+        deadline = time.monotonic() + self.peer_timeout_s
+        while True:
+            if st.add("%s/left" % self._hb_prefix, 0) > 0:
+                raise PeerLost("a rank left the group before step %d" % step)
+            arrived = st.add(key, 0)
+            if arrived >= self.world:
+                return
+            if time.monotonic() > deadline:
+                raise PeerLost("only %d of %d ranks reached step %d within %.1f s" %
+                               (arrived, self.world, step, self.peer_timeout_s))
+            time.sleep(0.0005)
+
+    def leave(self):
+        """Announce that this rank stops taking part.  Call it between steps, with none of this rank's kernels or
+        collectives in flight; the other ranks learn of it at their next check_peers()."""
+        if self._hb_store is not None:
+            self._hb_store.add("%s/left" % self._hb_prefix, 1)
 
     def _mine(self, t):
         """Accept full-width [*, H, d] tensors (sliced here) or already-local [*, H/G, d] ones."""
@@ -93,6 +146,12 @@ class HeadShardedAttention:
         return self._symm
 
     def forward(self, q, partition=0, gather=True):
+        """Attention of this rank's head slice; with gather=True the full-width [n_seqs, H, d] result on every rank.
+        The gathered tensor is a view of a buffer this object reuses: with gather="nccl" it is overwritten by the
+        next forward(), with gather="p2p" by the next-but-one (two buffers alternate and peers store into them),
+        and it is only ordered against work on the stream forward() was called on.  Clone it to keep it."""
+        if gather:
+            self.check_peers()
         if gather and self.gather_mode == "p2p" and partition != 2:
             ql = self._mine(q).contiguous()
             # Buffer k & 1 for step k.  When a rank passes the barrier of step k + 1, every rank's stream

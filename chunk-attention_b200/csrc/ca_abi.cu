@@ -84,6 +84,8 @@ struct ca_context {
     int opt_ctas = 0;
     bool opt_sf_tensor = true;
     int opt_pdl = 3;
+    long long opt_wait_limit = ca::DEFAULT_WAIT_LIMIT_CYCLES;
+    int opt_withhold_item = -1;
     unsigned long long* trace = nullptr;  // [kTraceCtas][4], allocated when tracing is switched on
     int trace_ctas = 0;                   // CTAs of the last traced launch
 
@@ -91,6 +93,7 @@ struct ca_context {
     // what the launches need to know about the work list that is on the device
     struct {
         int n_seqs = 0, n_items = 0, n_items_cf = 0, n_items_short = 0, n_ctas = 1;
+        int64_t n_merge_slots = 0;  // entries of merge_slots
         bool split_phases = false;
         ca_plan_stats stats{};
     } meta;
@@ -219,6 +222,13 @@ int ca_context_set_option(ca_context* c, int option, int64_t value) {
     } else if (option == CA_OPT_DEPENDENT_LAUNCH) {
         if (value < 0 || value > 3) return fail(CA_ERR_INVALID, "dependent-launch mask out of range");
         c->opt_pdl = (int)value;
+        return CA_OK;
+    } else if (option == CA_OPT_WAIT_LIMIT_CYCLES) {
+        if (value < 1000) return fail(CA_ERR_INVALID, "wait limit below 1000 cycles");
+        c->opt_wait_limit = value;
+        return CA_OK;
+    } else if (option == CA_OPT_TEST_WITHHOLD_ITEM) {
+        c->opt_withhold_item = value < 0 ? -1 : (int)value;
         return CA_OK;
     } else if (option == CA_OPT_TRACE) {
         DeviceGuard guard(c->device);
@@ -364,6 +374,7 @@ static int upload_plan(ca_context* c, const ca::Plan& pl, cudaStream_t stream) {
     c->meta.n_items_cf = pl.n_items_cf;
     c->meta.n_items_short = pl.n_items_short;
     c->meta.n_ctas = pl.n_ctas;
+    c->meta.n_merge_slots = (int64_t)pl.merge_slots.size();
     c->meta.split_phases = pl.split_phases;
     c->meta.stats = pl.stats;
     c->valid = true;
@@ -427,6 +438,11 @@ int ca_attn_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_st
     p.scale_log2 = 1.4426950408889634f / std::sqrt((float)c->geo.d_head);
     p.status = c->status;
     p.trace = c->trace;
+    p.n_slots = c->meta.stats.n_slots;
+    p.n_seqs = n_seqs;
+    p.max_chunks = (int)(c->max_chunks < INT32_MAX ? c->max_chunks : INT32_MAX);
+    p.wait_limit = c->opt_wait_limit;
+    p.withhold_item = c->opt_withhold_item;
     // one launch per range of items; every launch draws from the counter the previous launch zeroed
     auto launch = [&](int lo, int hi) -> cudaError_t {
         if (hi <= lo) return cudaSuccess;
@@ -434,10 +450,12 @@ int ca_attn_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_st
         p.item_hi = hi;
         p.counter = c->counters + c->launch_parity;
         p.counter_next = c->counters + (c->launch_parity ^ 1);
-        c->launch_parity ^= 1;
         const int n_ctas = c->meta.n_ctas < hi - lo ? c->meta.n_ctas : hi - lo;
         c->trace_ctas = n_ctas;
-        return ca::launch_attn_partials(p, n_ctas, stream, (c->opt_pdl & 2) != 0);
+        const cudaError_t e = ca::launch_attn_partials(p, n_ctas, stream, (c->opt_pdl & 2) != 0);
+        // the counters change roles only once the launch that zeroes the other one is really in the stream
+        if (e == cudaSuccess) c->launch_parity ^= 1;
+        return e;
     };
     // the short private tails (the last n_items_short items) have a kernel of their own, launched first so
     // that the persistent kernel's tail leads straight into the merge
@@ -536,7 +554,9 @@ int ca_attn_merge(ca_context* c, void* out, int n_seqs, ca_stream stream_) {
     m.merge_slots = c->d_merge_slots;
     m.out = out;
     m.n_pairs = n_seqs * c->geo.n_heads;
-    m.n_slots_total = c->meta.stats.n_slots;
+    m.n_slots_total = (long long)c->meta.n_merge_slots;
+    m.n_slots = c->meta.stats.n_slots;
+    m.status = c->status;
     CA_CUDA(ca::launch_attn_merge(m, static_cast<cudaStream_t>(stream_), (c->opt_pdl & 1) != 0));
     return CA_OK;
 }
@@ -562,7 +582,9 @@ int ca_attention_to_peers(ca_context* c, const void* q, void* const* peer_out, i
     m.merge_slots = c->d_merge_slots;
     m.out = nullptr;
     m.n_pairs = n_seqs * c->geo.n_heads;
-    m.n_slots_total = c->meta.stats.n_slots;
+    m.n_slots_total = (long long)c->meta.n_merge_slots;
+    m.n_slots = c->meta.stats.n_slots;
+    m.status = c->status;
     m.n_heads = c->geo.n_heads;
     m.n_peers = n_peers;
     m.total_heads = total_heads;
@@ -724,6 +746,14 @@ int ca_status_read(ca_context* c, ca_stream stream_, int32_t* status) {
     CA_CUDA(cudaStreamSynchronize(stream));
     *status = host;
     if (host != 0) return fail(CA_ERR_DEVICE_STATUS, "a kernel gave up a bounded wait, status " + std::to_string(host));
+    return CA_OK;
+}
+
+int ca_status_clear(ca_context* c, ca_stream stream_) {
+    if (!c) return fail(CA_ERR_INVALID, "context is null");
+    DeviceGuard guard(c->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    CA_CUDA(cudaMemsetAsync(c->status, 0, sizeof(int), static_cast<cudaStream_t>(stream_)));
     return CA_OK;
 }
 

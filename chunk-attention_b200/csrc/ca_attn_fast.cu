@@ -61,7 +61,6 @@ constexpr int SMEM_BAR_OFFSET = SMEM_SCRATCH_OFFSET + SCRATCH_BYTES;
 constexpr int SMEM_BYTES = SMEM_BAR_OFFSET + NUM_BARRIERS * 8 + 16;
 // two CTAs per SM: 228 KiB per SM, 1 KiB of it reserved per resident CTA
 static_assert(2 * (SMEM_BYTES + 1024) <= 233472, "two CTAs do not fit in one SM's shared memory");
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // about two seconds
 constexpr float NEG_BIG = -1.0e30f;
 
 struct ItemView {
@@ -90,6 +89,26 @@ __device__ __forceinline__ int tile_tokens(const ItemView& it, int j, int delta)
     return t < FAST_C ? t : FAST_C;
 }
 
+// Every index an item carries, checked against the bounds the launch was given (a bound of 0 is unchecked).
+// The work list may come from device memory the host never saw (ca_attention_static), so nothing in it is
+// trusted: an item that fails is skipped and the status word says so.
+__device__ __forceinline__ bool item_in_bounds(const PartialParams& p, const ItemView& it, const ItemChunks& ch) {
+    const int splits = it.flags >> ITEM_SPLITS_SHIFT;
+    const int slots = it.n_rows == 1 ? 1 : it.n_rows * (splits > 1 ? splits : 1);
+    const int max_rows = splits == 4 ? 16 : (splits == 2 ? 32 : (splits == 1 ? MAX_ROWS_PER_ITEM : (splits == 0 ? 1 : 0)));
+    bool ok = it.n_tiles >= 1 && it.n_tiles <= MAX_TILES_PER_ITEM && it.n_rows >= 1 && it.n_rows <= max_rows &&
+              it.head >= 0 && it.head < p.n_heads && it.row_begin >= 0 && it.slot_base >= 0 && it.last_tokens >= 0 &&
+              it.last_tokens <= FAST_C;
+    if (p.n_slots > 0) ok = ok && it.slot_base + slots <= p.n_slots;
+    if (p.n_seqs > 0) ok = ok && it.row_begin + it.n_rows <= p.n_seqs;
+    if (ok && p.max_chunks > 0) {
+#pragma unroll
+        for (int j = 0; j < MAX_TILES_PER_ITEM; j++)
+            if (j < it.n_tiles) ok = ok && ch.c[j] >= 0 && ch.c[j] < p.max_chunks;
+    }
+    return ok;
+}
+
 // ---- PTX wrappers ---------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -115,11 +134,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return done != 0;
 }
 // Wait for the phase with the given parity to complete; false when the bound ran out.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+        if (clock64() - t0 > limit) return false;
     }
     return true;
 }
@@ -187,6 +206,7 @@ struct Ring {
     uint32_t empty_bar;   // NUM_STAGES barriers, consumers -> producer (count NUM_CONSUMER_WARPS)
     uint32_t stage;
     uint32_t phase;
+    long long wait_limit;     // cycles a wait may take before the kernel gives up
     bool timed;               // tracing on: accumulate stall cycles
     long long wait_cycles;    // cycles spent waiting on ring barriers
     long long tail_cycles;    // consumers: cycles spent combining warps and storing partials
@@ -213,7 +233,7 @@ __device__ __forceinline__ uint32_t desc_addr(const Ring& rg, uint32_t stage) {
 __device__ __forceinline__ bool producer_post(const PartialParams& p, Ring& rg, const ItemView* desc, bool stage_q,
                                               const uint8_t* src, uint32_t bytes) {
     const long long t0 = rg.timed ? clock64() : 0;
-    const bool ok = mbar_wait_bounded(rg.empty_bar + 8 * rg.stage, rg.phase ^ 1);
+    const bool ok = mbar_wait_bounded(rg.empty_bar + 8 * rg.stage, rg.phase ^ 1, rg.wait_limit);
     if (rg.timed) rg.wait_cycles += clock64() - t0;
     if (!ok) return false;
     const uint32_t bar = rg.full_bar + 8 * rg.stage;
@@ -255,32 +275,43 @@ __device__ __forceinline__ void producer_loop(const PartialParams& p, Ring& rg) 
     int id1 = p.item_lo + (int)gridDim.x + (int)blockIdx.x;  // < 0: draw from the counter
     ItemView it{};
     ItemChunks ch{};
+    bool withheld = false;
     if (id0 < p.item_hi) load_item(p.items, id0, it, ch);
     while (id0 < p.item_hi && ok) {
-        // items of up to 16 rows get their query rows staged next to their first tile
-        const bool stage_q = (it.flags >> ITEM_SPLITS_SHIFT) == NUM_CONSUMER_WARPS;
-        bool first = true;
+        if (id0 == p.withhold_item) {
+            // failure-path test: this CTA's consumers are never told about the item (nor about the end of the
+            // list), so their bounded wait runs out
+            withheld = true;
+            break;
+        }
+        if (!item_in_bounds(p, it, ch)) {
+            report(p.status, STATUS_BAD_WORK_LIST);  // skipped: its partial rows keep whatever they held
+        } else {
+            // items of up to 16 rows get their query rows staged next to their first tile
+            const bool stage_q = (it.flags >> ITEM_SPLITS_SHIFT) == NUM_CONSUMER_WARPS;
+            bool first = true;
 #pragma unroll
-        for (int j = 0; j < 9; j++) {
-            if (j < it.n_tiles && ok) {
-                const int nt = tile_tokens(it, j, p.delta_tokens);
-                if (nt > 0) {
-                    const uint8_t* src = p.pool + ((size_t)ch.c[j] * p.n_heads + it.head) * (size_t)FAST_STAGE_BYTES;
-                    ok = producer_post(p, rg, first ? &it : nullptr, stage_q, src, (uint32_t)nt * (FAST_D * 2));
-                    issued += ok ? 1 : 0;
-                    first = false;
+            for (int j = 0; j < 9; j++) {
+                if (j < it.n_tiles && ok) {
+                    const int nt = tile_tokens(it, j, p.delta_tokens);
+                    if (nt > 0) {
+                        const uint8_t* src = p.pool + ((size_t)ch.c[j] * p.n_heads + it.head) * (size_t)FAST_STAGE_BYTES;
+                        ok = producer_post(p, rg, first ? &it : nullptr, stage_q, src, (uint32_t)nt * (FAST_D * 2));
+                        issued += ok ? 1 : 0;
+                        first = false;
+                    }
                 }
             }
-        }
-        if (first && ok) {  // no token in the whole item: the description still has to travel
-            ok = producer_post(p, rg, &it, false, nullptr, 0);
-            issued += ok ? 1 : 0;
+            if (first && ok) {  // no token in the whole item: the description still has to travel
+                ok = producer_post(p, rg, &it, false, nullptr, 0);
+                issued += ok ? 1 : 0;
+            }
         }
         id0 = id1 >= 0 ? id1 : p.item_lo + n_fixed + atomicAdd(p.counter, 1);
         id1 = -1;
         if (id0 < p.item_hi) load_item(p.items, id0, it, ch);
     }
-    if (ok) {
+    if (ok && !withheld) {
         ItemView end_marker{};
         end_marker.end = 1;
         ok = producer_post(p, rg, &end_marker, false, nullptr, 0);
@@ -291,7 +322,7 @@ __device__ __forceinline__ void producer_loop(const PartialParams& p, Ring& rg) 
     // (bounded) for the completion of the last fills, newest NUM_STAGES at most.
     const uint32_t n_check = issued < (uint32_t)NUM_STAGES ? issued : (uint32_t)NUM_STAGES;
     for (uint32_t f = issued - n_check; f < issued; f++) {
-        if (!mbar_wait_bounded(rg.full_bar + 8 * (f % NUM_STAGES), (f / NUM_STAGES) & 1)) {
+        if (!mbar_wait_bounded(rg.full_bar + 8 * (f % NUM_STAGES), (f / NUM_STAGES) & 1, rg.wait_limit)) {
             report(p.status, STATUS_DRAIN_TIMEOUT);
             break;
         }
@@ -301,7 +332,7 @@ __device__ __forceinline__ void producer_loop(const PartialParams& p, Ring& rg) 
 // ---- consumers ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ bool consumer_wait_full(Ring& rg) {
     const long long t0 = rg.timed ? clock64() : 0;
-    const bool ok = mbar_wait_bounded(rg.full_bar + 8 * rg.stage, rg.phase);
+    const bool ok = mbar_wait_bounded(rg.full_bar + 8 * rg.stage, rg.phase, rg.wait_limit);
     if (rg.timed) rg.wait_cycles += clock64() - t0;
     return __all_sync(0xffffffffu, ok);
 }
@@ -321,7 +352,7 @@ __device__ __forceinline__ bool combine_row_and_store(const PartialParams& p, co
     const long long t0 = rg.timed ? clock64() : 0;
     __syncwarp();
     if (lane == 0) mbar_arrive(merge_bar);
-    bool ok = mbar_wait_bounded(merge_bar, row_items & 1);
+    bool ok = mbar_wait_bounded(merge_bar, row_items & 1, rg.wait_limit);
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) return false;
     {
@@ -717,6 +748,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 2) attn_partial_kernel(const Part
     rg.empty_bar = smem_u32(bars + NUM_STAGES);
     rg.stage = 0;
     rg.phase = 0;
+    rg.wait_limit = p.wait_limit;
     rg.timed = p.trace != nullptr;
     rg.wait_cycles = 0;
     rg.tail_cycles = 0;
@@ -830,6 +862,11 @@ __global__ void __launch_bounds__(SHORT_WARPS * 32) attn_short_tails_kernel(cons
     if (idx >= p.item_hi) return;
     const int4 d0 = __ldg(p.items + 4 * idx), d1 = __ldg(p.items + 4 * idx + 1);
     const int head = d0.y, row = d0.z, slot = d1.x, flags = d1.y, chunk = d1.w;
+    if (head < 0 || head >= p.n_heads || row < 0 || slot < 0 || chunk < 0 || d1.z < 0 || (p.n_slots > 0 && slot >= p.n_slots) ||
+        (p.n_seqs > 0 && row >= p.n_seqs) || (p.max_chunks > 0 && chunk >= p.max_chunks)) {
+        if (lane == 0) report(p.status, STATUS_BAD_WORK_LIST);  // skipped
+        return;
+    }
     const int nt = min(FAST_C, d1.z + ((flags & ITEM_FLAG_TAIL) ? p.delta_tokens : 0));
     if (nt <= 0) {  // an empty reserved tail
         if (lane == 0) p.part_ml[slot] = make_float2(NEG_BIG, 0.f);
@@ -913,6 +950,22 @@ __global__ void __launch_bounds__(SHORT_WARPS * 32) attn_short_tails_kernel(cons
 // The un-normalised combination of the partials merge_slots[b .. e) by one warp: on return mm is their
 // maximum, acc this lane's four output elements weighted by 2^(m_i - mm), ll the warp-wide sum of the
 // weighted sums.  slot0: this lane's slot among the first 32 (-1: none), read by the caller.
+// A slot number from a merge list, or -1 (and the status word set) when it lies outside the partial rows.
+__device__ __forceinline__ int checked_slot(const MergeParams& p, int slot) {
+    if (p.n_slots > 0 && (slot < 0 || slot >= p.n_slots)) {
+        if (p.status) atomicCAS(p.status, STATUS_OK, STATUS_BAD_WORK_LIST);
+        return -1;
+    }
+    return slot;
+}
+// The bounds [b, e) of a pair's list inside merge_slots; an impossible pair of offsets yields an empty list.
+__device__ __forceinline__ void checked_bounds(const MergeParams& p, int& b, int& e) {
+    if (p.n_slots > 0 && (b < 0 || e < b || e > p.n_slots_total)) {
+        if (p.status) atomicCAS(p.status, STATUS_OK, STATUS_BAD_WORK_LIST);
+        b = e = 0;
+    }
+}
+
 template <int FIRST>
 __device__ __forceinline__ void merge_list(const MergeParams& p, int lane, int b, int e, int slot0, float& mm, float& ll,
                                            float4& acc) {
@@ -929,13 +982,15 @@ __device__ __forceinline__ void merge_list(const MergeParams& p, int lane, int b
 #pragma unroll
         for (int u = 0; u < FIRST; u++) {
             const int sk = __shfl_sync(0xffffffffu, slot0, u);
-            v0[u] = (u < n0) ? *reinterpret_cast<const float4*>(p.part_o + (size_t)sk * FAST_D + 4 * lane)
-                             : make_float4(0.f, 0.f, 0.f, 0.f);
+            v0[u] = (u < n0 && sk >= 0) ? *reinterpret_cast<const float4*>(p.part_o + (size_t)sk * FAST_D + 4 * lane)
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
     mm = ml0.y > 0.f ? ml0.x : NEG_BIG;
     for (int i = b + 32 + lane; i < e; i += 32) {
-        const float2 ml = p.part_ml[__ldg(p.merge_slots + i)];
+        const int si = checked_slot(p, __ldg(p.merge_slots + i));
+        if (si < 0) continue;
+        const float2 ml = p.part_ml[si];
         if (ml.y > 0.f) mm = fmaxf(mm, ml.x);
     }
 #pragma unroll
@@ -950,8 +1005,8 @@ __device__ __forceinline__ void merge_list(const MergeParams& p, int lane, int b
             slot = -1;
             ml = make_float2(NEG_BIG, 0.f);
             if (base + lane < e) {
-                slot = __ldg(p.merge_slots + base + lane);
-                ml = p.part_ml[slot];
+                slot = checked_slot(p, __ldg(p.merge_slots + base + lane));
+                if (slot >= 0) ml = p.part_ml[slot];
             }
         }
         float w = 0.f;
@@ -1031,7 +1086,8 @@ __global__ void __launch_bounds__(128, MIN_CTAS) attn_merge_kernel(const MergePa
     if (pair < p.n_pairs) {
         b = __ldg(p.merge_off + pair);
         e = __ldg(p.merge_off + pair + 1);
-        if (b + lane < e) slot0 = __ldg(p.merge_slots + b + lane);
+        checked_bounds(p, b, e);
+        if (b + lane < e) slot0 = checked_slot(p, __ldg(p.merge_slots + b + lane));
     }
     // wait until the partial kernel's results are visible; a no-op for an ordinary launch
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -1054,10 +1110,11 @@ __global__ void __launch_bounds__(128, 3) attn_merge_wide_kernel(const MergePara
     __shared__ float2 s_ml[4];
     const int pair = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b0 = __ldg(p.merge_off + pair), e0 = __ldg(p.merge_off + pair + 1);
+    int b0 = __ldg(p.merge_off + pair), e0 = __ldg(p.merge_off + pair + 1);
+    checked_bounds(p, b0, e0);
     const int per = (e0 - b0 + 3) >> 2;
     const int b = min(e0, b0 + warp * per), e = min(e0, b + per);
-    const int slot0 = b + lane < e ? __ldg(p.merge_slots + b + lane) : -1;
+    const int slot0 = b + lane < e ? checked_slot(p, __ldg(p.merge_slots + b + lane)) : -1;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     float mm, ll;

@@ -16,6 +16,9 @@ constexpr int STATUS_OK = 0;
 constexpr int STATUS_FULL_WAIT_TIMEOUT = 1;   // a consumer warp gave up waiting for a tile
 constexpr int STATUS_EMPTY_WAIT_TIMEOUT = 2;  // the producer gave up waiting for a free stage
 constexpr int STATUS_DRAIN_TIMEOUT = 3;       // copies still in flight at kernel exit
+constexpr int STATUS_BAD_WORK_LIST = 4;       // an item or merge entry named a slot, row, head or chunk out of range: skipped
+constexpr int STATUS_BAD_POSITION = 5;        // rotary embedding: a position outside the cos/sin table: row skipped
+constexpr long long DEFAULT_WAIT_LIMIT_CYCLES = 4000000000LL;  // about two seconds of SM clock
 
 // ---- fast path: fp16, d_head 128, chunk_size 64 -----------------------------------------------
 constexpr int FAST_D = 128;
@@ -39,6 +42,13 @@ struct PartialParams {
     int delta_tokens;            // tokens appended to every tail since the plan was built
     float scale_log2;            // log2(e) / sqrt(d_head)
     int* status;
+    // Bounds every index of the work list is checked against on the device (an item that fails is skipped and
+    // STATUS_BAD_WORK_LIST is recorded); 0 switches the corresponding check off.
+    int n_slots = 0;             // partial rows behind part_o / part_ml
+    int n_seqs = 0;              // rows of q
+    int max_chunks = 0;          // chunks in the pool
+    long long wait_limit = DEFAULT_WAIT_LIMIT_CYCLES;  // SM cycles a wait on a ring barrier may take
+    int withhold_item = -1;      // failure-path tests only: the producer that draws this item stops feeding its CTA
     unsigned long long* trace = nullptr;  // optional [n_ctas][8], null = off: ns timestamps of start,
                                  // producer end, first and last consumer warp end; then cycles: warp 0 waiting for
                                  // tiles, warp 0 combining/storing partials, producer waiting for free stages, warp 0 total
@@ -68,6 +78,8 @@ struct MergeParams {
     int total_heads = 0;
     int head_offset = 0;
     void* peer_out[MERGE_MAX_PEERS] = {};
+    int n_slots = 0;             // partial rows behind part_o / part_ml; a list entry outside [0, n_slots) is skipped
+    int* status = nullptr;       // and STATUS_BAD_WORK_LIST recorded here (0 / null: unchecked)
 };
 cudaError_t launch_attn_merge(const MergeParams& p, cudaStream_t stream, bool dependent_launch);
 

@@ -30,10 +30,12 @@ constexpr int kMaxDevices = 64;
 // Partial outputs [kMaxSlots][128] fp32, then (max, sum) pairs [kMaxSlots].  In HOST code this name
 // is only a handle for cudaGetSymbolAddress, never an address a kernel can use.
 static __device__ __align__(256) unsigned char g_static_scratch[kPartOBytes + kPartMlBytes];
-// Kernel status word used when the caller passes none; cleared at the start of every call.
+// Kernel status word used when the caller passes none; cleared at the start of every call and readable with
+// ca_attention_static_status.
 static __device__ int g_static_status;
-// The two item counters of the self-scheduling kernel: a launch draws from one and zeroes the other
-// for the launch after it.  Zero when the library is loaded.
+// The item counter the self-scheduling kernel draws from, and a spare word the kernel zeroes for "the
+// launch after it" (the ordinary entry point alternates two counters that way; here every call zeroes its
+// own counter on the stream, so a call does not depend on how the one before it ended).
 static __device__ int g_static_counters[2];
 
 struct DeviceSetup {
@@ -41,7 +43,6 @@ struct DeviceSetup {
     unsigned char* scratch = nullptr;  // device address of g_static_scratch on this device
     int* status = nullptr;             // device address of g_static_status on this device
     int* counters = nullptr;           // device address of g_static_counters on this device
-    int parity = 0;                    // which counter the next launch draws from
 };
 DeviceSetup g_setup[kMaxDevices];
 std::mutex g_setup_mutex;
@@ -100,11 +101,12 @@ int ca_attention_static(const void* pool, int n_heads, const void* q, void* out,
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     int* status_word = status ? status : su.status;
     // The scratch keeps whatever the previous call left in it.  No partial row has to start at
-    // zero: every row a merge list names is written by this call before it is read.  The status
-    // word does have to start at zero, because kernels only ever set it; so does the item counter
-    // this launch draws from, which the previous launch zeroed (the library image zeroes both for
-    // the first one).
+    // zero: every row a merge list names is written by this call before it is read.  Two words do
+    // have to start at zero and are cleared here, on the stream, by every call: the status word
+    // (kernels only ever set it) and the item counter the launch draws from (a call therefore
+    // does not depend on how the previous one ended: a failed launch, or the same call replayed).
     e = cudaMemsetAsync(status_word, 0, sizeof(int), stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(su.counters, 0, 2 * sizeof(int), stream);
     if (e != cudaSuccess) return fail(CA_ERR_CUDA, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
 
     ca::PartialParams p;
@@ -114,17 +116,18 @@ int ca_attention_static(const void* pool, int n_heads, const void* q, void* out,
     p.items = reinterpret_cast<const int4*>(items);
     p.item_lo = 0;
     p.item_hi = n_items;
-    {
-        std::lock_guard<std::mutex> lock(g_setup_mutex);
-        p.counter = su.counters + su.parity;
-        p.counter_next = su.counters + (su.parity ^ 1);
-        su.parity ^= 1;
-    }
+    p.counter = su.counters;
+    p.counter_next = su.counters + 1;
     p.part_o = reinterpret_cast<float*>(su.scratch);
     p.part_ml = reinterpret_cast<float2*>(su.scratch + kPartOBytes);
     p.delta_tokens = delta_tokens;
     p.scale_log2 = 1.4426950408889634f / std::sqrt((float)ca::FAST_D);
     p.status = status_word;
+    // The work list lives in device memory the host never saw: the kernels check every slot, row and head
+    // it names against these sizes, skip what falls outside and report STATUS_BAD_WORK_LIST (4).  The pool's
+    // size is not known here, so chunk numbers are taken as they come (max_chunks = 0).
+    p.n_slots = n_slots;
+    p.n_seqs = n_seqs;
     e = ca::launch_attn_partials(p, n_ctas < n_items ? n_ctas : n_items, stream);
     if (e != cudaSuccess) return fail(CA_ERR_CUDA, std::string("partial kernel launch: ") + cudaGetErrorString(e));
     ca::MergeParams m;
@@ -135,9 +138,29 @@ int ca_attention_static(const void* pool, int n_heads, const void* q, void* out,
     m.out = out;
     m.n_pairs = n_seqs * n_heads;
     m.n_slots_total = n_slots;
+    m.n_slots = n_slots;
+    m.status = status_word;
     e = ca::launch_attn_merge(m, stream, true);
     if (e != cudaSuccess) return fail(CA_ERR_CUDA, std::string("merge kernel launch: ") + cudaGetErrorString(e));
     return CA_OK;
+}
+
+int ca_attention_static_status(int32_t* status, ca_stream stream_) {
+    if (!status) return fail(CA_ERR_INVALID, "status is null");
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return fail(CA_ERR_CUDA, std::string("cudaGetDevice: ") + cudaGetErrorString(e));
+    if (device < 0 || device >= kMaxDevices || !g_setup[device].done) {
+        *status = 0;  // no call has run on this device yet
+        return CA_OK;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int32_t host = 0;
+    e = cudaMemcpyAsync(&host, g_setup[device].status, sizeof(int32_t), cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return fail(CA_ERR_CUDA, std::string("reading the status word: ") + cudaGetErrorString(e));
+    *status = host;
+    return host == 0 ? CA_OK : fail(CA_ERR_DEVICE_STATUS, "a kernel of ca_attention_static reported status " + std::to_string(host));
 }
 
 }  // extern "C"

@@ -175,9 +175,14 @@ __global__ void __launch_bounds__(256) rms_norm_warp_kernel(T* __restrict__ out,
 template <typename T, bool NEOX>
 __global__ void rotary_kernel(const int64_t* __restrict__ positions, T* __restrict__ query, T* __restrict__ key,
                               const T* __restrict__ cos_sin_cache, int rot_dim, int64_t q_stride, int64_t k_stride,
-                              int n_heads, int n_kv_heads, int head_size) {
+                              int n_heads, int n_kv_heads, int head_size, int64_t max_position, int* status) {
     const int half_rot = rot_dim / 2;
-    const T* cs = cos_sin_cache + positions[blockIdx.x] * rot_dim;  // [cos(half_rot) | sin(half_rot)]
+    const int64_t pos = positions[blockIdx.x];
+    if (max_position > 0 && (pos < 0 || pos >= max_position)) {  // outside the table: leave the token as it is
+        if (status && threadIdx.x == 0) atomicCAS(status, 0, 5);
+        return;
+    }
+    const T* cs = cos_sin_cache + pos * rot_dim;  // [cos(half_rot) | sin(half_rot)]
     const int nq = n_heads * half_rot, nk = n_kv_heads * half_rot;
     for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
         const bool is_q = i < nq;
@@ -200,12 +205,17 @@ __global__ void rotary_kernel(const int64_t* __restrict__ positions, T* __restri
 template <typename T, bool NEOX>
 __global__ void rotary_vec_kernel(const int64_t* __restrict__ positions, T* __restrict__ query, T* __restrict__ key,
                                   const T* __restrict__ cos_sin_cache, int rot_dim, int64_t q_stride, int64_t k_stride,
-                                  int n_heads, int n_kv_heads, int head_size) {
+                                  int n_heads, int n_kv_heads, int head_size, int64_t max_position, int* status) {
     constexpr int EPG = 16 / sizeof(T);
     struct alignas(16) Pack { T v[EPG]; };
     struct alignas(8) HalfPack { T v[EPG / 2]; };
     const int half_rot = rot_dim / 2;
-    const T* cs = cos_sin_cache + positions[blockIdx.x] * rot_dim;
+    const int64_t pos = positions[blockIdx.x];
+    if (max_position > 0 && (pos < 0 || pos >= max_position)) {  // outside the table: leave the token as it is
+        if (status && threadIdx.x == 0) atomicCAS(status, 0, 5);
+        return;
+    }
+    const T* cs = cos_sin_cache + pos * rot_dim;
     const int units_per_head = NEOX ? half_rot / EPG : rot_dim / EPG;
     const int nq = n_heads * units_per_head, nk = n_kv_heads * units_per_head;
     for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
@@ -329,7 +339,8 @@ int ca_fused_add_rms_norm(void* input, void* residual, const void* weight, float
 
 int ca_rotary_embedding(const int64_t* positions, void* query, void* key, const void* cos_sin_cache, int rot_dim,
                         int64_t query_stride, int64_t key_stride, int num_heads, int num_kv_heads, int head_size,
-                        int64_t num_tokens, int is_neox, int dtype, ca_stream stream) {
+                        int64_t num_tokens, int is_neox, int dtype, int64_t max_position, int32_t* status,
+                        ca_stream stream) {
     if (num_tokens < 0 || rot_dim <= 0 || rot_dim % 2 || rot_dim > head_size || num_heads < 0 || num_kv_heads < 0)
         return ca::ops_fail(CA_ERR_INVALID, "rotary_embedding: bad shape");
     if (num_tokens == 0) return CA_OK;
@@ -352,11 +363,12 @@ int ca_rotary_embedding(const int64_t* positions, void* query, void* key, const 
 #define CA_ROTV(T, NEOX)                                                                                            \
     ca::rotary_vec_kernel<T, NEOX><<<n, threads, 0, s>>>(positions, static_cast<T*>(query), static_cast<T*>(key),    \
                                                          static_cast<const T*>(cos_sin_cache), rot_dim, query_stride, \
-                                                         key_stride, num_heads, num_kv_heads, head_size)
+                                                         key_stride, num_heads, num_kv_heads, head_size, max_position, status)
 #define CA_ROT(T, NEOX)                                                                                             \
     ca::rotary_kernel<T, NEOX><<<n, threads, 0, s>>>(positions, static_cast<T*>(query), static_cast<T*>(key),        \
                                                      static_cast<const T*>(cos_sin_cache), rot_dim, query_stride,    \
-                                                     key_stride, num_heads, num_kv_heads, head_size)
+                                                     key_stride, num_heads, num_kv_heads, head_size, max_position,  \
+                                                     status)
     if (dtype == CA_DTYPE_F16) {
         if (vec) {
             if (is_neox) CA_ROTV(__half, true); else CA_ROTV(__half, false);

@@ -8,6 +8,8 @@
 #include <pybind11/pybind11.h>
 #include <torch/extension.h>
 
+#include <map>
+#include <mutex>
 #include <stdexcept>
 
 #include "../../../include/chunk_attn_b200.h"
@@ -54,6 +56,19 @@ void fused_add_rms_norm(torch::Tensor& input, torch::Tensor& residual, torch::Te
              "fused_add_rms_norm");
 }
 
+// One int32 status word per device, made on first use: rotary_embedding skips tokens whose position lies
+// outside the cos/sin table (the reference reads past the table) and records it here.
+torch::Tensor status_tensor(torch::Device device) {
+    static std::mutex mu;
+    static std::map<int, torch::Tensor> words;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = words.find(device.index());
+    if (it == words.end())
+        it = words.emplace(device.index(), torch::zeros({1}, torch::TensorOptions().dtype(torch::kInt32).device(device))).first;
+    return it->second;
+}
+int32_t* rotary_status_word(torch::Device device) { return status_tensor(device).data_ptr<int32_t>(); }
+
 void rotary_embedding(torch::Tensor& positions, torch::Tensor& query, torch::Tensor& key, int head_size,
                       torch::Tensor& cos_sin_cache, bool is_neox) {
     need(query.is_cuda() && key.is_cuda() && positions.is_cuda() && cos_sin_cache.is_cuda(),
@@ -78,14 +93,28 @@ void rotary_embedding(torch::Tensor& positions, torch::Tensor& query, torch::Ten
     check_rc(ca_rotary_embedding(positions.data_ptr<int64_t>(), query.data_ptr(), key.data_ptr(), cos_sin_cache.data_ptr(),
                                  (int)cos_sin_cache.size(1), query.stride(-2), key.stride(-2), (int)(query.size(-1) / head_size),
                                  (int)(key.size(-1) / head_size), head_size, num_tokens, is_neox ? 1 : 0,
-                                 dtype_of(query, "rotary_embedding"), stream_of(query)),
+                                 dtype_of(query, "rotary_embedding"), cos_sin_cache.size(0),
+                                 rotary_status_word(query.device()), stream_of(query)),
              "rotary_embedding");
+}
+
+// 0 when every position seen since the last call lay inside its cos/sin table, else 5; clears the word.
+// Synchronises the current stream.
+int rotary_embedding_status(torch::Device device) {
+    torch::Tensor word = status_tensor(device);
+    const int v = word.item<int>();
+    if (v != 0) word.zero_();
+    return v;
 }
 
 }  // namespace
 
 void init_ops(pybind11::module& m) {
     m.def("rotary_embedding", &rotary_embedding, "Apply GPT-NeoX or GPT-J style rotary embedding to query and key");
+    m.def("rotary_embedding_status", [](pybind11::object device) {
+              return rotary_embedding_status(torch::python::detail::py_object_to_device(device));
+          }, pybind11::arg("device"),
+          "0, or 5 when rotary_embedding skipped a token whose position lay outside cos_sin_cache since the last call");
     m.def("rms_norm", &rms_norm, "Apply Root Mean Square (RMS) Normalization to the input tensor.");
     m.def("fused_add_rms_norm", &fused_add_rms_norm, "In-place fused Add and RMS Normalization");
 }

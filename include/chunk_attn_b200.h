@@ -98,6 +98,13 @@ CA_API void ca_context_destroy(ca_context* ctx);
  * drains; bit 1, the attention kernel is set up while the kernel before it in the stream finishes
  * (it waits for that kernel's completion before it touches global memory).  Default 3. */
 #define CA_OPT_DEPENDENT_LAUNCH 5
+/* SM cycles a kernel may wait on one of its internal barriers before it gives up, records a status code
+ * (ca_status_read) and returns; default 4e9, about two seconds.  The waits exist so that a lost copy or a
+ * damaged work list ends in an error code instead of a hung GPU. */
+#define CA_OPT_WAIT_LIMIT_CYCLES 7
+/* Failure-path tests only: the CTA that draws item `value` of the next launches stops feeding its consumer
+ * warps, whose bounded wait then runs out (status 1).  -1 (default) switches it off. */
+#define CA_OPT_TEST_WITHHOLD_ITEM 8
 CA_API int ca_context_set_option(ca_context* ctx, int option, int64_t value);
 
 /* Rebuild and upload the work lists after the tree changed.
@@ -179,9 +186,14 @@ CA_API int ca_copy_chunks(ca_context* ctx, const int32_t* src_ids, const int32_t
 CA_API int ca_read_chunk(ca_context* ctx, int chunk_id, int n_tokens, void* k_out, void* v_out,
                          ca_stream stream);
 
-/* Device status word written by kernels whose bounded waits ran out (0 = clean).  Synchronises
- * the stream. */
+/* Device status word (0 = clean; first failure wins): 1 a consumer warp gave up waiting for a tile, 2 the
+ * producer gave up waiting for a free stage, 3 copies still in flight at kernel exit, 4 an item or merge
+ * entry of the work list named a slot, row, head or chunk out of range and was skipped (every index is
+ * checked on the device against the sizes the context knows).  Synchronises the stream; returns
+ * CA_ERR_DEVICE_STATUS when the word is not 0.  ca_status_clear zeroes it (stream-ordered) so that the
+ * context can be used again after a reported failure. */
 CA_API int ca_status_read(ca_context* ctx, ca_stream stream, int32_t* status);
+CA_API int ca_status_clear(ca_context* ctx, ca_stream stream);
 
 /* Per-CTA timestamps of the last attention launch when CA_OPT_TRACE is on (diagnostics): for CTA i,
  * out[8i..8i+3] = start, producer warp end, first consumer warp end, last consumer warp end, in ns
@@ -219,7 +231,10 @@ CA_API int ca_context_stats(const ca_context* ctx, ca_plan_stats* out);
  * ca_rotary_embedding: rotates the first rot_dim elements of every head of query and key in place by the
  *   angle of the token's position; cos_sin_cache is [max_position, rot_dim] = [cos | sin] per position;
  *   query_stride / key_stride are the element strides between tokens; is_neox pairs (i, i + rot_dim/2),
- *   otherwise (2i, 2i + 1) (replaces vllm::rotary_embedding, cpp/chunk_attn/pos_encoding_kernels.cu:94-139). */
+ *   otherwise (2i, 2i + 1) (replaces vllm::rotary_embedding, cpp/chunk_attn/pos_encoding_kernels.cu:94-139).
+ *   max_position is the number of rows of cos_sin_cache: a token whose position lies outside [0, max_position)
+ *   is left unrotated and, when `status` (an optional device word, first failure wins) is given, 5 is
+ *   stored there; the reference reads past its table in that case.  max_position <= 0 switches the check off. */
 CA_API int ca_rms_norm(void* out, const void* input, const void* weight, float epsilon, int64_t num_tokens,
                        int hidden_size, int dtype, ca_stream stream);
 CA_API int ca_fused_add_rms_norm(void* input, void* residual, const void* weight, float epsilon,
@@ -227,7 +242,7 @@ CA_API int ca_fused_add_rms_norm(void* input, void* residual, const void* weight
 CA_API int ca_rotary_embedding(const int64_t* positions, void* query, void* key, const void* cos_sin_cache,
                                int rot_dim, int64_t query_stride, int64_t key_stride, int num_heads,
                                int num_kv_heads, int head_size, int64_t num_tokens, int is_neox, int dtype,
-                               ca_stream stream);
+                               int64_t max_position, int32_t* status, ca_stream stream);
 
 /* ---- allocation-free decode step ---------------------------------------------------------------
  * No counterpart in the reference: this entry point exists for callers that cannot allocate device
@@ -252,21 +267,35 @@ CA_API int ca_rotary_embedding(const int64_t* positions, void* query, void* key,
  *   n_slots         ca_plan_stats.n_slots of that plan; above CA_STATIC_MAX_SLOTS the call is refused
  *                   with CA_ERR_INVALID and a message naming both numbers
  *   delta_tokens    tokens appended to every tail since the plan was built
- *   status          optional device word for the kernels' bounded-wait status (0 = clean); NULL
- *                   selects a word inside the library.  It is cleared at the start of each call.
+ *   status          optional device word for the kernels' status (0 = clean, codes as for ca_status_read);
+ *                   NULL selects a word inside the library, read back with ca_attention_static_status.
+ *                   It is cleared at the start of each call.
+ *
+ * The work list is read from device memory the host cannot inspect, so the kernels check it: an item or merge
+ * entry that names a partial row >= n_slots, a row >= n_seqs or a head >= n_heads is skipped and status 4 is
+ * recorded (the output rows concerned are then wrong, but nothing outside the scratch, q or out is touched).
+ * Chunk numbers cannot be checked here, because the pool's size is not an argument: a work list built for
+ * another pool is the caller's responsibility.
  *
  * The first call on a device looks up the device address of the scratch (cudaGetSymbolAddress)
- * and sets the kernel's shared-memory attribute; make that first call before any stream capture.
+ * and sets the kernel's shared-memory attribute; make that first call before any stream capture, and, since the
+ * library image with its 8.1 MiB array is mapped onto the device when the library's first kernel or symbol is
+ * touched (CUDA loads modules lazily), before the host framework has taken all of the GPU's memory.
  * All calls on a device share the one scratch array, which still holds the previous call's
  * partial rows when the next call starts (none of them needs clearing: every row a merge list names
- * is rewritten first; the two item counters next to them are the exception, and each launch zeroes
- * the one the next launch will use).  Two calls that overlap on the GPU (different streams, or different threads)
+ * is rewritten first; the status word and the item counter of the self-scheduling kernel do, and every call
+ * clears them on its stream before its kernels run, so a call does not depend on how the previous one ended).
+ * delta_tokens is an argument of the launch: a recorded call replays with the value it was recorded with.
+ * Two calls that overlap on the GPU (different streams, or different threads)
  * therefore race on it: keep calls on one device stream-ordered. */
 #define CA_STATIC_MAX_SLOTS 16384
 CA_API int ca_attention_static(const void* pool, int n_heads, const void* q, void* out, int n_seqs,
                                const int32_t* items, int n_items, int n_ctas, const int32_t* merge_off,
                                const int32_t* merge_slots, int n_slots, int delta_tokens,
                                int32_t* status, ca_stream stream);
+/* The library's own status word of ca_attention_static calls made with status = NULL on the current device
+ * (synchronises the stream).  No counterpart in the reference. */
+CA_API int ca_attention_static_status(int32_t* status, ca_stream stream);
 
 /* ---- host-only planner (no GPU needed) -------------------------------------------------------
  * The work-list builder used by ca_refresh_kernel_context, exposed so that it can be checked on

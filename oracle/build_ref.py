@@ -129,7 +129,8 @@ def build_cuda(ref, force=False):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("CHUNK_ATTN_REFERENCE_TREE"), required="CHUNK_ATTN_REFERENCE_TREE" not in os.environ,
+                    help="source tree of the unmodified reference (or set CHUNK_ATTN_REFERENCE_TREE)")
     ap.add_argument("--cuda", action="store_true")
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()

@@ -20,7 +20,7 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, os.path.join(ROOT, "oracle"))
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 from ref_loader import load_reference  # noqa: E402
-from workloads import random_trace, tails_shape, tree_shape  # noqa: E402
+from tree_traces import random_trace, tails_shape, tree_shape  # noqa: E402
 
 
 def run_case(ref, name, H, d, C, ops, seed):

@@ -71,7 +71,7 @@ def round_to(x, dtype):
 
 def oracle_for(workload, dtype=None):
     """Oracle populated with the workload's values rounded to the engine's dtype."""
-    from chunk_attn import workloads as W
+    import synthetic_workloads as W
     dtype = dtype or workload.dtype
     ora = OracleAttention(workload.n_heads, workload.d_head, workload.chunk_size)
     rows = []

@@ -1,0 +1,54 @@
+"""Failure paths of the attention kernels, exercised without faulting, trapping or hanging the GPU: every wait in
+the kernels is bounded, and on expiry a kernel records a status code, unwinds and returns, leaving the context
+usable.  The wait is made to run out by a test-only option that makes one CTA's producer stop feeding its
+consumer warps (a flag that nothing sets), with the limit lowered to about a millisecond."""
+import pytest
+import torch
+
+from chunk_attn import cabi
+import synthetic_workloads as W
+from gpu_helpers import CabiEngine, max_abs, oracle_for, round_to
+
+pytestmark = pytest.mark.gpu
+
+TOL_F16 = 1e-3
+
+
+def test_wait_that_runs_out_is_reported_and_the_context_survives():
+    w = W.single_level("failure", 4, 128, 64, torch.float16, 9, 5 * 64, 2 * 64 + 11, 77, 0.5)
+    eng = CabiEngine(4, 128, 64, torch.float16, max_chunks=128)
+    ora, orows = oracle_for(w)
+    rows = W.populate(eng, w)
+    assert rows == orows
+    q = round_to(w.q[rows], torch.float16)
+    ref = ora.forward(q.numpy(), 0)
+    assert max_abs(eng.forward(q).float().cpu().numpy(), ref) < TOL_F16
+    assert eng.ctx.status() == 0
+
+    # one CTA's consumers are never handed their first item: their wait runs out after ~1 ms of SM clock
+    eng.ctx.set_option(cabi.CA_OPT_WAIT_LIMIT_CYCLES, 2_000_000)
+    eng.ctx.set_option(cabi.CA_OPT_TEST_WITHHOLD_ITEM, 0)
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    eng.forward(q)
+    t1.record()
+    torch.cuda.synchronize()                      # the kernel returned by itself
+    assert t0.elapsed_time(t1) < 500.0            # ms: nowhere near the default two-second limit
+    rc, word = eng.ctx.status_raw()
+    assert rc == cabi.CA_ERR_DEVICE_STATUS and word == cabi.STATUS_FULL_WAIT_TIMEOUT
+    assert b"status 1" in cabi.lib.ca_last_error()
+
+    # the same context, cleared, computes the next ordinary step correctly
+    eng.ctx.set_option(cabi.CA_OPT_TEST_WITHHOLD_ITEM, -1)
+    eng.ctx.set_option(cabi.CA_OPT_WAIT_LIMIT_CYCLES, 4_000_000_000)
+    eng.ctx.status_clear()
+    for _ in range(2):
+        assert max_abs(eng.forward(q).float().cpu().numpy(), ref) < TOL_F16
+    assert eng.ctx.status() == 0
+
+
+def test_option_ranges():
+    eng = CabiEngine(2, 128, 64, torch.float16, max_chunks=8)
+    with pytest.raises(cabi.CAError):
+        eng.ctx.set_option(cabi.CA_OPT_WAIT_LIMIT_CYCLES, 10)   # a limit this short would fail ordinary waits

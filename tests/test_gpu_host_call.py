@@ -3,7 +3,8 @@ place, pageable ones staged), bit-identical to the device-tensor call."""
 import pytest
 import torch
 
-from chunk_attn import Attention, cabi, workloads as W
+from chunk_attn import Attention, cabi
+import synthetic_workloads as W
 from gpu_helpers import CabiEngine
 
 pytestmark = pytest.mark.gpu

@@ -12,7 +12,8 @@ import numpy as np
 import pytest
 import torch
 
-from chunk_attn import Attention, cabi, workloads as W
+from chunk_attn import Attention, cabi
+import synthetic_workloads as W
 from chunk_attn_oracle import dense_forward
 from gpu_helpers import CabiEngine, max_abs, oracle_for, round_to
 from ref_loader import load_reference
@@ -336,7 +337,7 @@ def test_default_dtype_and_device_resolution():
 
 
 # ---- full-size properties where the oracle would take too long ---------------------------------------------
-@pytest.mark.parametrize("shared", [0, 2048, 4096])
+@pytest.mark.parametrize("shared", [0, 1024, 2048, 3072, 4096])
 def test_config3_properties(shared):
     # batch 64, context 4096: (a) the tensor-core path and the independent sequence-first kernel
     # agree; (b) sampled (row, head) pairs match dense fp64 attention computed from the inputs;
@@ -360,6 +361,98 @@ def test_config3_properties(shared):
         ref = torch.softmax(s, 0) @ v
         assert (out[r, h].double() - ref).abs().max().item() < TOL_F16
     assert attn.device_status() == 0
+
+
+def dense_fp64(segs, head, q_vec, extra_k=None, extra_v=None):
+    """softmax(q K^T / sqrt(d)) V in fp64 for one (sequence, head), from the fp16-rounded inputs the engine
+    was given: `segs` is the sequence's prefill, extra_k / extra_v the rows appended since (already fp16)."""
+    _, k, v = W.cat_segments(segs, head_slice=slice(head, head + 1))
+    k, v = k.half().double()[:, 0], v.half().double()[:, 0]
+    if extra_k is not None and len(extra_k):
+        k = torch.cat([k, torch.stack(extra_k).to(k.device).double()])
+        v = torch.cat([v, torch.stack(extra_v).to(v.device).double()])
+    s = (k @ q_vec.to(k.device).double()) / math.sqrt(k.shape[1])
+    return torch.softmax(s, 0) @ v
+
+
+def test_config5_full_size_properties():
+    # H64, 256 sequences x (4096 shared + 1024 unique): the workload every multi-GPU number is quoted on, on one
+    # GPU at full size.  (a) tensor-core path == the independent sequence-first kernel; (b) sampled (row, head)
+    # pairs, rows from each 64-row block with the first and the last head plus random ones, against dense fp64.
+    w = W.config5(gen_device="cuda")
+    H = 64
+    eng = CabiEngine(H, 128, 64, torch.float16, max_chunks=64 + 256 * 17 + 8)
+    rows = W.populate(eng, w)
+    st_rows = sorted(rows)
+    assert st_rows == list(range(256))
+    q = w.q[rows].to("cuda", torch.float16).contiguous()
+    out = eng.forward(q)
+    st = eng.ctx.stats()
+    assert st["fast_path"] == 1 and st["n_shared_chunks"] == 64 and st["unique_kv_bytes"] == W.unique_kv_bytes(w) == 8_724_152_320
+    out2 = eng.forward(q, 2)
+    assert torch.isfinite(out).all()
+    assert (out.float() - out2.float()).abs().max().item() < TOL_F16
+    g = torch.Generator().manual_seed(15)
+    pairs = [(64 * b + int(torch.randint(0, 64, (1,), generator=g)), h) for b in range(4) for h in (0, H - 1)]
+    pairs += [(int(torch.randint(0, 256, (1,), generator=g)), int(torch.randint(0, H, (1,), generator=g))) for _ in range(8)]
+    worst = 0.0
+    for r, h in pairs:
+        ref = dense_fp64(w.seqs[rows[r]], h, q[r, h])
+        worst = max(worst, (out[r, h].double() - ref).abs().max().item())
+    assert worst < TOL_F16
+    assert eng.ctx.status() == 0
+
+
+def test_config4_full_size_trace():
+    # The two-level tree at full size (H32, 4 groups x 32 sequences, root 1024 + group 1024 + 256 unique), 64 decode
+    # steps appending a token per sequence, 8 sequences replaced every 16 steps, then two more steps: the 65th append
+    # finds every surviving tail full, so a new tail is reserved.  At the checked steps the tensor-core path must agree
+    # with the sequence-first kernel and sampled (row, head) pairs with dense fp64 over prefill + appended rows.
+    cfg = W.Config4(gen_device="cuda")
+    eng = CabiEngine(32, 128, 64, torch.float16, max_chunks=1100)
+    seqs = []      # per row: [segments, appended k rows per head..., appended v rows]
+
+    def add(segs):
+        tokens, k, v = W.cat_segments(segs)
+        seqs.insert(eng.add_seq(tokens, k, v), {"segs": segs, "k": [], "v": []})
+
+    for segs in cfg.initial():
+        add(segs)
+    checked, worst, worst_paths = [], 0.0, 0.0
+    g = torch.Generator().manual_seed(16)
+    n_steps = cfg.steps + 2
+    for step in range(n_steps):
+        if step and step % cfg.churn_every == 0 and step < cfg.steps:
+            for _ in range(cfg.churn):
+                i = cfg.rng.randrange(len(seqs))
+                eng.remove_seq(i)
+                seqs.pop(i)
+            for _ in range(cfg.churn):
+                add(cfg.new_sequence(cfg.rng.randrange(cfg.n_groups)))
+        q, nk, nv = (t.to(torch.float16) for t in cfg.step_inputs(len(seqs)))
+        n_chunks_before = len(eng.tree.get_chunks())
+        eng.append_token([7_000_000 + step] * len(seqs), nk, nv)
+        for i, sq in enumerate(seqs):
+            sq["k"].append(nk[i])
+            sq["v"].append(nv[i])
+        out = eng.forward(q)
+        if step == cfg.steps:   # the originals' tails were full: the append before this forward reserved new ones
+            assert len(eng.tree.get_chunks()) > n_chunks_before
+        if step in (0, 15, 16, 32, 63, cfg.steps, cfg.steps + 1):
+            checked.append(step)
+            out2 = eng.forward(q, 2)
+            assert torch.isfinite(out).all()
+            worst_paths = max(worst_paths, (out.float() - out2.float()).abs().max().item())
+            for _ in range(6):
+                r = int(torch.randint(0, len(seqs), (1,), generator=g))
+                h = int(torch.randint(0, 32, (1,), generator=g))
+                ref = dense_fp64(seqs[r]["segs"], h, q[r, h], [x[h] for x in seqs[r]["k"]], [x[h] for x in seqs[r]["v"]])
+                worst = max(worst, (out[r, h].double() - ref).abs().max().item())
+    assert len(checked) == 7
+    assert worst_paths < TOL_F16 and worst < TOL_F16
+    st = eng.ctx.stats()
+    assert st["n_runs"] >= 5   # the root run and the four group runs
+    assert eng.ctx.status() == 0
 
 
 # ---- the reference's own CUDA kernels as comparator ----------------------------------------------------------
@@ -386,7 +479,7 @@ def test_against_reference_cuda_kernels():
 
 # ---- golden vectors of the unmodified reference ---------------------------------------------------------------
 from golden_replay import fixtures, replay  # noqa: E402
-from workloads import tails_shape, tree_shape  # noqa: E402
+from tree_traces import tails_shape, tree_shape  # noqa: E402
 
 
 @pytest.mark.parametrize("path", fixtures(), ids=lambda p: os.path.basename(p)[:-4])

@@ -106,6 +106,6 @@ def test_c_abi_rejects_bad_arguments():
     assert L.ca_rms_norm(None, None, None, 1e-5, 4, 0, cabi.CA_DTYPE_F16, None) == cabi.CA_ERR_INVALID
     assert L.ca_fused_add_rms_norm(None, None, None, 1e-5, 4, 64, cabi.CA_DTYPE_F16, None) == cabi.CA_ERR_INVALID
     # odd rot_dim, rot_dim > head_size
-    assert L.ca_rotary_embedding(None, None, None, None, 63, 64, 64, 1, 1, 64, 4, 1, 0, None) == cabi.CA_ERR_INVALID
-    assert L.ca_rotary_embedding(None, None, None, None, 128, 64, 64, 1, 1, 64, 4, 1, 0, None) == cabi.CA_ERR_INVALID
+    assert L.ca_rotary_embedding(None, None, None, None, 63, 64, 64, 1, 1, 64, 4, 1, 0, 0, None, None) == cabi.CA_ERR_INVALID
+    assert L.ca_rotary_embedding(None, None, None, None, 128, 64, 64, 1, 1, 64, 4, 1, 0, 0, None, None) == cabi.CA_ERR_INVALID
     assert b"rotary_embedding" in L.ca_last_error()

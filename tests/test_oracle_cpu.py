@@ -8,7 +8,7 @@ import pytest
 from chunk_attn_oracle import Attention as OracleAttention, dense_forward
 from golden_replay import fixtures, replay
 from ref_loader import load_reference
-from workloads import kv_for, tails_shape
+from tree_traces import kv_for, tails_shape
 
 
 @pytest.mark.parametrize("path", fixtures(), ids=lambda p: os.path.basename(p)[:-4])

@@ -6,7 +6,7 @@ import pytest
 from chunk_attn import cabi
 from chunk_attn_oracle import Attention as OracleAttention, dense_forward
 from plan_emulator import emulate
-from workloads import kv_for, random_trace
+from tree_traces import kv_for, random_trace
 
 C = 64  # the fast path's chunk size; the planner is only used for that geometry
 

@@ -6,7 +6,7 @@ import pytest
 from chunk_attn import PrefixTree
 from chunk_attn_oracle import Attention as OracleAttention
 from ref_loader import load_reference
-from workloads import kv_for, random_trace, tails_shape, tree_shape
+from tree_traces import kv_for, random_trace, tails_shape, tree_shape
 
 
 def node(n):
