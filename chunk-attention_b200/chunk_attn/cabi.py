@@ -65,7 +65,7 @@ def _load():
         "ca_last_error": (C.c_char_p, []),
         "ca_version": (i32, []),
         "ca_chunk_bytes": (i64, [i32, i32, i32, i32]),
-        "ca_tile_elem_offset": (i64, [i32, i32, i32, i32]),
+        "ca_tile_elem_offset": (i64, [i32, i32, i32, i32, i32]),
         "ca_context_create": (i32, [C.POINTER(vp), i32, i32, i32, i32, i32, vp, i64, i32]),
         "ca_context_destroy": (None, [vp]),
         "ca_context_set_option": (i32, [vp, i32, i64]),

@@ -140,10 +140,10 @@ int64_t ca_chunk_bytes(int n_heads, int d_head, int chunk_size, int dtype) {
     return (int64_t)n_heads * 2 * chunk_size * d_head * es;
 }
 
-int64_t ca_tile_elem_offset(int d_head, int dtype, int token, int elem) {
+int64_t ca_tile_elem_offset(int d_head, int chunk_size, int dtype, int token, int elem) {
     const int es = esize_of(dtype);
-    if (es == 0 || d_head <= 0 || token < 0 || elem < 0 || elem >= d_head) return -1;
-    const ca::Geometry g = ca::make_geometry(1, d_head, token + 1, es);
+    if (es == 0 || d_head <= 0 || chunk_size <= 0 || token < 0 || token >= chunk_size || elem < 0 || elem >= d_head) return -1;
+    const ca::Geometry g = ca::make_geometry(1, d_head, chunk_size, es);
     return ca::tile_elem_offset(g, token, elem);
 }
 

@@ -34,9 +34,11 @@
 
 #include "ca_kernels.h"
 #include "ca_plan.h"
+#include "ca_ptx.cuh"
 
 namespace ca {
 namespace {
+using namespace ptx;
 
 constexpr int NUM_STAGES = 3;
 constexpr int NUM_CONSUMER_WARPS = FAST_CONSUMER_WARPS;  // one warpgroup
@@ -89,6 +91,13 @@ __device__ __forceinline__ int tile_tokens(const ItemView& it, int j, int delta)
     return t < FAST_C ? t : FAST_C;
 }
 
+// Byte offset, inside a K or V tile, of the 16-byte granule g (0..15) of token row t: the tile is two panels of
+// 64 lines of 128 bytes (ca_layout.h), granule c of a line stored at c ^ (t & 7).
+constexpr int PANEL_BYTES = FAST_C * 128;
+__device__ __forceinline__ uint32_t tile_off(int t, int g) {
+    return (uint32_t)(((g >> 3) * PANEL_BYTES) + (t << 7) + (((g & 7) ^ (t & 7)) << 4));
+}
+
 // Every index an item carries, checked against the bounds the launch was given (a bound of 0 is unchecked).
 // The work list may come from device memory the host never saw (ca_attention_static), so nothing in it is
 // trusted: an item that fails is skipped and the status word says so.
@@ -107,95 +116,6 @@ __device__ __forceinline__ bool item_in_bounds(const PartialParams& p, const Ite
             if (j < it.n_tiles) ok = ok && ch.c[j] >= 0 && ch.c[j] < p.max_chunks;
     }
     return ok;
-}
-
-// ---- PTX wrappers ---------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return done != 0;
-}
-// Wait for the phase with the given parity to complete; false when the bound ran out.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, long long limit) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > limit) return false;
-    }
-    return true;
-}
-// 1-D TMA bulk copy global -> shared, completion counted in bytes on an mbarrier.
-// dst, src 16-byte aligned; bytes a multiple of 16.
-__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-        "l"(src), "r"(bytes), "r"(bar)
-        : "memory");
-}
-__device__ __forceinline__ void ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                 : "r"(addr));
-}
-__device__ __forceinline__ void ldsm_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3,
-                                              uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                 : "r"(addr));
-}
-// D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)
-__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void sts128(uint32_t addr, int x, int y, int z, int w) {
-    asm volatile("st.shared.v4.s32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
-}
-__device__ __forceinline__ void sts128_zero(uint32_t addr) {
-    asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(addr), "r"(0u) : "memory");
-}
-// order this thread's generic-proxy shared-memory writes before later async-proxy (TMA) writes
-__device__ __forceinline__ void fence_proxy_async() {
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
-    const __half2 h = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<const uint32_t*>(&h);
 }
 
 // ---- pipeline bookkeeping shared by producer and consumers ----------------------------------------
@@ -245,10 +165,15 @@ __device__ __forceinline__ bool producer_post(const PartialParams& p, Ring& rg, 
         if (stage_q) q_bytes = (uint32_t)desc->n_rows * (FAST_D * 2);
     }
     mbar_arrive_expect_tx(bar, 2 * bytes + q_bytes);  // release: the description is visible to whoever sees the phase
-    if (bytes) {
+    if (bytes == FAST_TILE_BYTES) {
         const uint32_t dst = rg.ring + rg.stage * FAST_STAGE_BYTES;
         bulk_copy_g2s(dst, src, bytes, bar);
         bulk_copy_g2s(dst + FAST_TILE_BYTES, src + FAST_TILE_BYTES, bytes, bar);
+    } else if (bytes) {
+        // a partly filled tail: the first n token lines of each of the four panels (K, K, V, V)
+        const uint32_t dst = rg.ring + rg.stage * FAST_STAGE_BYTES;
+#pragma unroll
+        for (int pnl = 0; pnl < 4; pnl++) bulk_copy_g2s(dst + pnl * PANEL_BYTES, src + pnl * PANEL_BYTES, bytes / 2, bar);
     }
     if (q_bytes) {
         const uint8_t* q = reinterpret_cast<const uint8_t*>(p.q) +
@@ -471,7 +396,7 @@ __device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView&
             // scores are masked below; their V rows are zeroed here because 0 * NaN is NaN.
             const int first_absent = nt > tok0 ? nt : tok0;
             for (int idx = lane; idx < (tok0 + TW - first_absent) * 16; idx += 32)
-                sts128_zero(vbase + (first_absent + (idx >> 4)) * (FAST_D * 2) + ((idx & 15) << 4));
+                sts128_zero(vbase + tile_off(first_absent + (idx >> 4), idx & 15));
             __syncwarp();
         }
 
@@ -493,7 +418,7 @@ __device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView&
                 const int t = tok0 + np * 16 + k_tok;
                 const int g = 2 * ks + k_gsel;
                 uint32_t b0, b1, b2, b3;
-                ldsm_x4(b0, b1, b2, b3, kbase + t * (FAST_D * 2) + ((g ^ (t & 7)) << 4));
+                ldsm_x4(b0, b1, b2, b3, kbase + tile_off(t, g));
                 mma_16816(sg[ks % KG][2 * np], qa[ks], b0, b1);
                 mma_16816(sg[ks % KG][2 * np + 1], qa[ks], b2, b3);
             }
@@ -573,7 +498,7 @@ __device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView&
                 const int t = tok0 + kk * 16 + v_tok;
                 const int g = 2 * dp + v_gsel;
                 uint32_t b0, b1, b2, b3;
-                ldsm_x4_trans(b0, b1, b2, b3, vbase + t * (FAST_D * 2) + ((g ^ (t & 7)) << 4));
+                ldsm_x4_trans(b0, b1, b2, b3, vbase + tile_off(t, g));
                 mma_16816(o[2 * dp], pa[kk], b0, b1);
                 mma_16816(o[2 * dp + 1], pa[kk], b2, b3);
             }
@@ -667,7 +592,7 @@ __device__ __forceinline__ bool simt_item(const PartialParams& p, const ItemView
                 const int t = warp * TPW + 2 * jj + half;
                 float acc = 0.f;
                 if (t < nt) {
-                    const uint4 raw = lds128(kt + t * (FAST_D * 2) + ((g ^ (t & 7)) << 4));
+                    const uint4 raw = lds128(kt + tile_off(t, g));
                     const __half2* h = reinterpret_cast<const __half2*>(&raw);
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
@@ -703,7 +628,7 @@ __device__ __forceinline__ bool simt_item(const PartialParams& p, const ItemView
                 if (t < nt) {
                     const float pj = fast_exp2(s[jj] - mn);
                     l += pj;
-                    const uint4 raw = lds128(vt + t * (FAST_D * 2) + ((g ^ (t & 7)) << 4));
+                    const uint4 raw = lds128(vt + tile_off(t, g));
                     const __half2* h = reinterpret_cast<const __half2*>(&raw);
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
@@ -902,7 +827,7 @@ __global__ void __launch_bounds__(SHORT_WARPS * 32) attn_short_tails_kernel(cons
                 const int t = 32 * r + 16 * half + i;
                 float acc = 0.f;
                 if (t < nt) {
-                    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(ktile + t * (FAST_D * 2) + ((g16 ^ (t & 7)) << 4)));
+                    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(ktile + tile_off(t, g16)));
                     const __half2* h = reinterpret_cast<const __half2*>(&raw);
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
@@ -930,7 +855,7 @@ __global__ void __launch_bounds__(SHORT_WARPS * 32) attn_short_tails_kernel(cons
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     const int gran = lane >> 1, sub = (lane & 1) << 3;
     auto add_row = [&](int t, float pw) {
-        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(vtile + t * (FAST_D * 2) + ((gran ^ (t & 7)) << 4) + sub));
+        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(vtile + tile_off(t, gran) + sub));
         const __half2* h = reinterpret_cast<const __half2*>(&raw);
         const float2 a = __half22float2(h[0]), b = __half22float2(h[1]);
         acc.x = fmaf(pw, a.x, acc.x);

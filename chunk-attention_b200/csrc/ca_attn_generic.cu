@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_seq_generic_kernel(const 
     const int s = pair / p.geo.n_heads;
     const int h = pair - s * p.geo.n_heads;
     const int d = p.geo.d_head;
-    const int gpr = p.geo.gpr, swz = p.geo.swz;
+    const int gpr = p.geo.gpr;
     const T* pool = reinterpret_cast<const T*>(p.pool);
     {
         const T* q = reinterpret_cast<const T*>(p.q) + (size_t)pair * d;
@@ -104,11 +104,10 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_seq_generic_kernel(const 
             float sc = -INFINITY;
             if (lane < nv) {
                 float acc = 0.f;
-                const T* row = kt + (size_t)t * d;
                 if (VEC) {
                     for (int g = 0; g < gpr; g++) {
                         float kf[EPG];
-                        Gran<T>::load(row + ((g ^ (t & swz)) * EPG), kf);
+                        Gran<T>::load(kt + tile_granule_index(p.geo, t, g) * EPG, kf);
 #pragma unroll
                         for (int k = 0; k < EPG; k++) acc = fmaf(q_s[g * EPG + k], kf[k], acc);
                     }
@@ -129,14 +128,13 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_seq_generic_kernel(const 
             for (int j = 0; j < nv; j++) {
                 const float pw = __shfl_sync(0xffffffffu, pj, j);
                 const int tj = t0 + j;
-                const T* row = vt + (size_t)tj * d;
                 if (VEC) {
 #pragma unroll
                     for (int gi = 0; gi < 2; gi++) {
                         const int g = lane + 32 * gi;
                         if (g < gpr) {
                             float vf[EPG];
-                            Gran<T>::load(row + ((g ^ (tj & swz)) * EPG), vf);
+                            Gran<T>::load(vt + tile_granule_index(p.geo, tj, g) * EPG, vf);
 #pragma unroll
                             for (int k = 0; k < EPG; k++) o[gi * EPG + k] = fmaf(pw, vf[k], o[gi * EPG + k]);
                         }

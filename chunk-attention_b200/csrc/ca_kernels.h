@@ -62,6 +62,25 @@ cudaError_t launch_attn_partials(const PartialParams& p, int n_ctas, cudaStream_
 cudaError_t launch_attn_short_tails(const PartialParams& p, cudaStream_t stream, bool dependent_launch = false);
 cudaError_t configure_fast_kernels();  // once per device before the first launch
 
+// ---- wide shared runs on tcgen05 / TMEM (ca_attn_wide.cu): one CTA per item ---------------------------------
+struct WideParams {
+    const uint8_t* pool;
+    int n_heads;
+    const void* q;               // fp16 [n_seqs, n_heads, 128]
+    const int4* items;           // PlanItem; chunk[0] is the offset of the item's chunk list in wide_chunks
+    int item_lo, item_hi;
+    const int32_t* wide_chunks;
+    int n_wide_chunks;           // entries of wide_chunks
+    float* part_o;
+    float2* part_ml;
+    float scale_log2;
+    int* status;
+    int n_slots = 0, n_seqs = 0, max_chunks = 0;  // bounds the work list is checked against (0: unchecked)
+    long long wait_limit = DEFAULT_WAIT_LIMIT_CYCLES;
+};
+cudaError_t launch_attn_wide(const WideParams& p, cudaStream_t stream, bool dependent_launch = false);
+cudaError_t configure_wide_kernel();  // once per device before the first launch
+
 constexpr int MERGE_MAX_PEERS = 8;
 struct MergeParams {
     const float* part_o;

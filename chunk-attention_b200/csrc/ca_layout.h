@@ -1,12 +1,19 @@
 // Pool and tile layout shared by host and device code.
 //
-// Pool: [max_chunks][n_heads][2 (K, V)][chunk_size][d_head] elements in one allocation.
-// Tile: the chunk_size x d_head block of one (chunk, head, K|V).  A token row is cut into
-// 16-byte granules; when a row holds a multiple of 8 granules, granule g of token row t is
-// stored at position g ^ (t & 7).  The XOR spreads the eight rows an ldmatrix reads (same
-// logical granule, consecutive tokens) over all 32 shared-memory banks after a tile has been
-// bulk-copied verbatim into shared memory, and keeps a row's granules inside the row, so a
-// row is still one contiguous 16-byte-aligned span for row-wise readers.
+// Pool: [max_chunks][n_heads][2 (K, V)] tiles in one allocation; a tile is the chunk_size x d_head block of
+// one (chunk, head, K|V).  A token row is cut into 16-byte granules.  When a row holds a multiple of 8
+// granules (every geometry the tensor-core kernels serve), the tile is stored as PANELS:
+//
+//     tile = [d_head * esize / 128 panels][chunk_size token rows][8 granules of 16 bytes]
+//
+// panel p holds bytes [128 p, 128 p + 128) of every token row, one 128-byte line per token, and inside a line
+// granule c of token row t sits at position c ^ (t & 7).  This is exactly the canonical 128-byte-swizzled
+// shared-memory layout of the Blackwell tensor cores (tcgen05.mma matrix descriptors, SWIZZLE_128B): a K
+// panel is a K-major operand of 64 elements (fp16), a V panel an MN-major one, so a tile bulk-copied VERBATIM
+// into shared memory (1024-byte aligned) can be handed to tcgen05.mma by descriptor, with no tensor map and
+// no TMA swizzle mode.  The same XOR makes the ldmatrix patterns of the mma.sync path (8 consecutive tokens x
+// one granule, plain for K, .trans for V) and row-wise 128-bit readers bank-conflict free.
+// Other geometries (rows that are not a multiple of 128 bytes) are stored row-major, unswizzled.
 #pragma once
 #include <stdint.h>
 
@@ -25,7 +32,7 @@ struct Geometry {
     int esize;  // bytes per element
     int epg;    // elements per 16-byte granule, or 1 when rows are not a whole number of granules
     int gpr;    // granules per token row (d_head / epg)
-    int swz;    // 7 when granules are XOR-swizzled, else 0
+    int swz;    // 7 when the tile is stored as swizzled 128-byte panels, else 0 (row-major)
     int64_t tile_elems;   // chunk_size * d_head
     int64_t chunk_elems;  // n_heads * 2 * tile_elems
 };
@@ -45,11 +52,19 @@ CA_HD Geometry make_geometry(int n_heads, int d_head, int chunk_size, int esize)
     return g;
 }
 
+// index, in 16-byte units from the start of the tile, of granule `gran` of token row t (geometries with
+// whole-granule rows only)
+CA_HD int64_t tile_granule_index(const Geometry& g, int t, int gran) {
+    if (g.swz) return ((int64_t)(gran >> 3) * g.chunk_size + t) * 8 + ((gran & 7) ^ (t & 7));
+    return (int64_t)t * g.gpr + gran;
+}
+
 // element offset of (token row t, element e) inside a tile
 CA_HD int64_t tile_elem_offset(const Geometry& g, int t, int e) {
     int gran = e / g.epg;
     int within = e - gran * g.epg;
-    return (int64_t)t * g.d_head + (int64_t)((gran ^ (t & g.swz)) * g.epg) + within;
+    if (g.epg == 1) return (int64_t)t * g.d_head + e;
+    return tile_granule_index(g, t, gran) * g.epg + within;
 }
 
 // element offset of the K tile (kv = 0) or V tile (kv = 1) of (chunk, head) inside the pool

@@ -18,6 +18,9 @@
 //    sizes follow guided self-scheduling — as large as allowed while much work remains, shrinking
 //    towards single tiles at the end of the list — so that all CTAs finish within about one tile
 //    of each other;
+//  * wide shared runs (many rows under a long prefix, where the contraction and not memory bounds the step) are
+//    cut into items of their own for the tcgen05 / TMEM kernel: up to 128 rows x up to 32 chunks, one CTA each,
+//    about one wave of them;
 //  * merge lists name, per (row, head), the partial slots the merge kernel combines.
 #pragma once
 #include <stdint.h>
@@ -30,10 +33,19 @@
 namespace ca {
 
 constexpr int ITEM_FLAG_TAIL = 1;     // last tile of the item is the sequence's tail chunk
+constexpr int ITEM_FLAG_WIDE = 2;     // an item of the tcgen05 kernel: chunk[0] is an offset into Plan::wide_chunks
 constexpr int ITEM_SPLITS_SHIFT = 8;  // flags >> 8: token splits of a tensor-core item (4, 2, 1);
                                       // 0 = one-row item walked on CUDA cores
 constexpr int MAX_ROWS_PER_ITEM = 64; // 4 consumer warps x 16 rows
 constexpr int MAX_TILES_PER_ITEM = 9;  // 8 by size, plus a sequence's tail chunk riding along
+constexpr int WIDE_MAX_ROWS = 128;    // query rows of a wide item (the M of tcgen05.mma)
+constexpr int WIDE_MAX_TILES = 32;    // chunks of a wide item
+// Wide routing (wide_mode 1 = automatic): shared runs of more than WIDE_MIN_ROWS rows go to the tcgen05 kernel when
+// walking them with mma.sync would take longer than half the time the step's unique K/V needs at HBM rate — only then
+// is the step bound by the tensor path rather than by memory.  Rates measured on B200.
+constexpr int WIDE_MIN_ROWS = 32;
+constexpr double WIDE_MMA_SYNC_FLOPS = 200e12;
+constexpr double WIDE_HBM_BYTES_PER_S = 6.4e12;
 
 struct PlanItem {
     int32_t n_tiles;      // 1 .. MAX_TILES_PER_ITEM
@@ -52,7 +64,9 @@ struct Plan {
     bool split_phases = false;
     std::vector<PlanItem> items;          // chunk-first items first, short tails last
     int n_items_cf = 0;                   // how many of them are chunk-first items
-    int n_items_short = 0;                // how many at the END of the list are short tails for the warp-per-item kernel
+    int n_items_short = 0;                // how many, after the persistent kernel's items, are short tails for the warp-per-item kernel
+    int n_items_wide = 0;                 // how many at the END of the list are wide items for the tcgen05 kernel
+    std::vector<int32_t> wide_chunks;     // chunk lists of the wide items
     std::vector<int32_t> merge_off, merge_slots;
     std::vector<int32_t> path_off, path_chunks, path_tokens;
     std::vector<int32_t> tail_chunk, tail_tokens;
@@ -66,6 +80,7 @@ inline int item_slots(int n_rows, int splits) { return n_rows == 1 ? 1 : n_rows 
 // Returns an empty string on success, else the reason the input was rejected.
 std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int n_seqs, int n_heads,
                        int chunk_size, int tpp_threshold, int n_ctas, int64_t max_chunks,
-                       bool split_phases, int d_head, int esize, bool fast_path, bool seq_first_tensor);
+                       bool split_phases, int d_head, int esize, bool fast_path, bool seq_first_tensor,
+                       int wide_mode = 1);  // 0: never route runs to the tcgen05 kernel, 1: by cost, 2: every shared run
 
 }  // namespace ca

@@ -23,8 +23,7 @@ __device__ __forceinline__ int units_per_row(const Geometry& g) {
 template <typename U>
 __device__ __forceinline__ void move_unit(void* dst_tile, const void* src_row, const Geometry& g, int t, int unit) {
     if (sizeof(U) == 16) {
-        reinterpret_cast<U*>(dst_tile)[(int64_t)t * g.gpr + (unit ^ (t & g.swz))] =
-            reinterpret_cast<const U*>(src_row)[unit];
+        reinterpret_cast<U*>(dst_tile)[tile_granule_index(g, t, unit)] = reinterpret_cast<const U*>(src_row)[unit];
     } else {
         reinterpret_cast<U*>(dst_tile)[tile_elem_offset(g, t, unit)] = reinterpret_cast<const U*>(src_row)[unit];
     }

@@ -68,14 +68,17 @@ CA_API int ca_version(void);
  * The pool is ONE device allocation made by the caller:
  *     [max_chunks][n_heads][2 (K then V)][chunk_size][d_head] elements.
  * A (chunk, head) pair therefore owns one contiguous K tile immediately followed by its V tile,
- * which is what one bulk copy into shared memory fetches.  Inside a tile the 16-byte granules
- * of token row t are XOR-swizzled with (t & 7) when a row holds a multiple of 8 granules, so
- * that tensor-core fragment loads from the staged tile are bank-conflict free.  The layout is
+ * which is what one bulk copy into shared memory fetches.  When a token row is a multiple of 128 bytes, a tile is
+ * stored as panels, [row_bytes / 128][chunk_size][128 bytes]: panel p holds bytes [128 p, 128 p + 128) of every
+ * token row, and inside a token's 128-byte line the 16-byte granule c sits at position c ^ (token & 7) -- the
+ * canonical 128-byte-swizzled operand layout of the tcgen05 tensor cores, so a staged tile is handed to
+ * tcgen05.mma by descriptor, and the same layout keeps the ldmatrix loads of the mma.sync path bank-conflict free.
+ * Other row sizes are stored row-major.  The layout is
  * private to this library (the reference exposes no K/V tensors to Python either,
  * cpp/chunk_attn/python_exports.cpp:16-21); ca_tile_elem_offset() is its definition.
  * Replaces the [n_heads, chunk_size, d_head] views of cpp/chunk_attn/chunk_allocator.cpp:43-55. */
 CA_API int64_t ca_chunk_bytes(int n_heads, int d_head, int chunk_size, int dtype);
-CA_API int64_t ca_tile_elem_offset(int d_head, int dtype, int token, int elem);
+CA_API int64_t ca_tile_elem_offset(int d_head, int chunk_size, int dtype, int token, int elem);
 
 /* ---- context --------------------------------------------------------------------------------
  * Replaces GPT::KernelContext (cpp/chunk_attn/kernel_cuda.h:9-55).  Owns the device work lists

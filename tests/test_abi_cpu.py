@@ -29,17 +29,23 @@ def test_host_only_entry_points():
     assert cabi.lib.ca_version() >= 100
     assert cabi.lib.ca_chunk_bytes(32, 128, 64, cabi.CA_DTYPE_F16) == 1 << 20
     assert cabi.lib.ca_chunk_bytes(32, 128, 64, 7) == -1
-    # the tile layout: a permutation of the row's granules, identity when rows are short
-    for d, dt, es in ((128, cabi.CA_DTYPE_F16, 2), (64, cabi.CA_DTYPE_F32, 4), (4, cabi.CA_DTYPE_F32, 4),
-                      (20, cabi.CA_DTYPE_F16, 2)):
-        for t in (0, 1, 7, 9):
-            offs = [cabi.lib.ca_tile_elem_offset(d, dt, t, e) for e in range(d)]
-            assert sorted(offs) == list(range(t * d, (t + 1) * d))
-            per16 = 16 // es
-            if d % per16 == 0 and (d // per16) % 8 == 0:
-                assert offs[0] == t * d + ((0 ^ (t & 7)) * per16)
-            else:
-                assert offs == list(range(t * d, (t + 1) * d))
+    # the tile layout: a permutation of the tile's elements; rows of a multiple of 128 bytes are stored as
+    # 128-byte panels with the granules of a token's line XOR-swizzled by (token & 7), others row-major
+    for d, C_, dt, es in ((128, 64, cabi.CA_DTYPE_F16, 2), (64, 32, cabi.CA_DTYPE_F32, 4), (4, 2, cabi.CA_DTYPE_F32, 4),
+                          (20, 5, cabi.CA_DTYPE_F16, 2), (256, 16, cabi.CA_DTYPE_F16, 2)):
+        per16 = 16 // es
+        panelled = d % per16 == 0 and (d // per16) % 8 == 0
+        offs = [[cabi.lib.ca_tile_elem_offset(d, C_, dt, t, e) for e in range(d)] for t in range(C_)]
+        assert sorted(o for row in offs for o in row) == list(range(C_ * d))
+        for t in range(C_):
+            for e in range(d):
+                if panelled:
+                    gran, within = divmod(e, per16)
+                    want = ((gran >> 3) * C_ + t) * 8 * per16 + ((gran & 7) ^ (t & 7)) * per16 + within
+                else:
+                    want = t * d + e
+                assert offs[t][e] == want
+    assert cabi.lib.ca_tile_elem_offset(128, 64, cabi.CA_DTYPE_F16, 64, 0) == -1
 
 
 @pytest.mark.skipif(torch.cuda.is_available(), reason="checks the behaviour without a device")
