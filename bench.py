@@ -17,7 +17,8 @@ Workloads (synthetic, seeded; synthetic_workloads.py):
          runs cfg5 on one GPU (cfg2 beside it in `headline_cfg2`); CA_BENCH_N1=cfg2 forces cfg2.  The choice
          is recorded in `config.workload_choice`.
 `--workload` overrides the choice (cfg2, cfg5, cfg3_s<shared>, cfg4, short<n_seqs>: a 1024-token common
-prompt with 20-token private suffixes, llama: the decoder loop).
+prompt with 20-token private suffixes, sys<n_seqs>: a 2048-token system prompt with 8-token suffixes, llama: the
+decoder loop).
 
 Every line carries `parity`: sampled (row, head) outputs of the very tensors that are timed, compared with dense
 fp64 attention computed from the seeded inputs (on N > 1 including heads owned by other ranks, regenerated from
@@ -104,6 +105,9 @@ def describe(name, n_gpus):
     if name.startswith("short"):
         return ("%s: H32 d128 c64 fp16, %s seqs x (1024 shared + 20 unique tokens): a long common prompt with short "
                 "private suffixes" % (name, name[5:] or "256"))
+    if name.startswith("sys"):
+        return ("%s: H32 d128 c64 fp16, %s seqs x (2048 shared + 8 unique tokens): many requests over one system "
+                "prompt" % (name, name[3:] or "1024"))
     return "%s: H32 d128 c64 fp16, 64 seqs, context 4096, shared prefix %s" % (name, name.split("_s")[-1])
 
 
@@ -120,6 +124,9 @@ def make_workload(name, n_heads_local, gen_device, rank=0):
         return W.config3(int(name[6:]), n_heads=n_heads_local, gen_device=gen_device)
     if name.startswith("short"):  # short<n_seqs>: not one of the five configurations; the short-suffix serving shape
         return W.single_level(name, n_heads_local, 128, 64, torch.float16, int(name[5:] or 256), 1024, 20, 5, 0.5,
+                              gen_device)
+    if name.startswith("sys"):    # sys<n_seqs>: many requests over one system prompt (contraction-bound)
+        return W.single_level(name, n_heads_local, 128, 64, torch.float16, int(name[3:] or 1024), 2048, 8, 6, 0.5,
                               gen_device)
     raise SystemExit("unknown workload " + name)
 

@@ -25,7 +25,7 @@ EXT_LIB = os.path.join(LIB, "chunk_attn_c" + sysconfig.get_config_var("EXT_SUFFI
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "-I", INCLUDE]
-CU_SOURCES = ["ca_attn_fast.cu", "ca_attn_generic.cu", "ca_pool_ops.cu", "ca_abi.cu", "ca_noalloc.cu", "ca_ops.cu"]
+CU_SOURCES = ["ca_attn_fast.cu", "ca_attn_wide.cu", "ca_attn_generic.cu", "ca_pool_ops.cu", "ca_abi.cu", "ca_noalloc.cu", "ca_ops.cu"]
 CPP_SOURCES = ["ca_plan.cpp"]
 HOST_SOURCES = ["host/chunk.cpp", "host/prefix_tree.cpp", "host/attention.cpp", "host/ops.cpp", "host/bindings.cpp"]
 

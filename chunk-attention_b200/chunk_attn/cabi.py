@@ -16,11 +16,11 @@ CA_OK = 0
 CA_ERR_INVALID, CA_ERR_CUDA, CA_ERR_STATE, CA_ERR_DEVICE_STATUS = -1, -2, -3, -4
 CA_DTYPE_F16, CA_DTYPE_F32 = 0, 1
 CA_OPT_SPLIT_PHASES, CA_OPT_NUM_CTAS, CA_OPT_SEQ_FIRST_TENSOR, CA_OPT_TRACE, CA_OPT_DEPENDENT_LAUNCH = 1, 2, 3, 4, 5
-CA_OPT_WAIT_LIMIT_CYCLES, CA_OPT_TEST_WITHHOLD_ITEM = 7, 8
+CA_OPT_WIDE_RUNS, CA_OPT_WAIT_LIMIT_CYCLES, CA_OPT_TEST_WITHHOLD_ITEM = 6, 7, 8
 STATUS_FULL_WAIT_TIMEOUT, STATUS_EMPTY_WAIT_TIMEOUT, STATUS_DRAIN_TIMEOUT, STATUS_BAD_WORK_LIST, STATUS_BAD_POSITION = 1, 2, 3, 4, 5
 PLAN_ITEMS = 0
 (PLAN_MERGE_OFF, PLAN_MERGE_SLOTS, PLAN_PATH_OFF, PLAN_PATH_CHUNKS, PLAN_PATH_TOKENS, PLAN_TAIL_CHUNK,
- PLAN_TAIL_TOKENS) = range(3, 10)
+ PLAN_TAIL_TOKENS, PLAN_WIDE_CHUNKS) = range(3, 11)
 
 # every symbol include/chunk_attn_b200.h declares
 EXPORTED = [
@@ -44,7 +44,7 @@ class PlanStats(C.Structure):
     _fields_ = [("unique_kv_bytes", C.c_int64), ("n_chunks", C.c_int32), ("n_shared_chunks", C.c_int32),
                 ("n_runs", C.c_int32), ("n_items", C.c_int32), ("n_slots", C.c_int32),
                 ("n_ctas", C.c_int32), ("fast_path", C.c_int32), ("kernels_per_step", C.c_int32),
-                ("n_items_cf", C.c_int32), ("n_items_short", C.c_int32)]
+                ("n_items_cf", C.c_int32), ("n_items_short", C.c_int32), ("n_items_wide", C.c_int32)]
 
     def as_dict(self):
         return {f: getattr(self, f) for f, _ in self._fields_}
@@ -85,7 +85,7 @@ def _load():
         "ca_status_clear": (i32, [vp, vp]),
         "ca_context_stats": (i32, [vp, C.POINTER(PlanStats)]),
         "ca_context_read_trace": (i32, [vp, C.POINTER(C.c_uint64), i32, C.POINTER(i32), vp]),
-        "ca_plan_build": (i32, [C.POINTER(vp), C.POINTER(ChunkInfo), i32, i32, i32, i32, i32, i32, i64, i32, i32]),
+        "ca_plan_build": (i32, [C.POINTER(vp), C.POINTER(ChunkInfo), i32, i32, i32, i32, i32, i32, i64, i32, i32, i32]),
         "ca_plan_build_for_context": (i32, [vp, C.POINTER(vp), C.POINTER(ChunkInfo), i32, i32]),
         "ca_refresh_from_plan": (i32, [vp, vp, vp]),
         "ca_plan_array": (i32, [vp, i32, C.POINTER(C.POINTER(C.c_int32)), C.POINTER(i64)]),
@@ -125,11 +125,11 @@ class Plan:
     """Host-only work-list builder (no GPU needed)."""
 
     def __init__(self, infos, n_seqs, n_heads, chunk_size=64, tpp_threshold=1, n_ctas=296,
-                 max_chunks=1 << 30, split_phases=False, seq_first_tensor=True):
+                 max_chunks=1 << 30, split_phases=False, seq_first_tensor=True, wide_runs=0):
         arr, n = make_infos(infos)
         self._h = C.c_void_p()
         check(lib.ca_plan_build(C.byref(self._h), arr, n, n_seqs, n_heads, chunk_size, tpp_threshold,
-                                n_ctas, max_chunks, int(split_phases), int(seq_first_tensor)))
+                                n_ctas, max_chunks, int(split_phases), int(seq_first_tensor), int(wide_runs)))
 
     def array(self, which):
         ptr, cnt = C.POINTER(C.c_int32)(), C.c_int64()

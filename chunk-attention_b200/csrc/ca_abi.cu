@@ -63,6 +63,7 @@ struct ca_plan {
     // what the plan was built for (checked when it is uploaded into a context)
     int64_t max_chunks = INT64_MAX;
     bool fast = true;
+    int wide_mode = 1;
     int d_head = ca::FAST_D;
     int esize = 2;
 };
@@ -84,6 +85,7 @@ struct ca_context {
     int opt_ctas = 0;
     bool opt_sf_tensor = true;
     int opt_pdl = 3;
+    int opt_wide = 1;
     long long opt_wait_limit = ca::DEFAULT_WAIT_LIMIT_CYCLES;
     int opt_withhold_item = -1;
     unsigned long long* trace = nullptr;  // [kTraceCtas][4], allocated when tracing is switched on
@@ -92,7 +94,7 @@ struct ca_context {
     ca::Plan plan;  // scratch of ca_refresh_kernel_context (vectors keep their capacity)
     // what the launches need to know about the work list that is on the device
     struct {
-        int n_seqs = 0, n_items = 0, n_items_cf = 0, n_items_short = 0, n_ctas = 1;
+        int n_seqs = 0, n_items = 0, n_items_cf = 0, n_items_short = 0, n_items_wide = 0, n_wide_chunks = 0, n_ctas = 1;
         int64_t n_merge_slots = 0;  // entries of merge_slots
         bool split_phases = false;
         ca_plan_stats stats{};
@@ -113,6 +115,7 @@ struct ca_context {
     const int32_t *d_merge_off = nullptr, *d_merge_slots = nullptr;
     const int32_t *d_path_off = nullptr, *d_path_chunks = nullptr, *d_path_tokens = nullptr;
     const int32_t *d_tail_chunk = nullptr, *d_tail_tokens = nullptr;
+    const int32_t* d_wide_chunks = nullptr;
 
     // partial results of the current step (scratch)
     float* part_o = nullptr;
@@ -182,6 +185,7 @@ int ca_context_create(ca_context** out, int device, int n_heads, int d_head, int
     if (e == cudaSuccess) e = cudaMalloc(&c->counters, 2 * sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(c->counters, 0, 2 * sizeof(int));
     if (e == cudaSuccess && c->fast) e = ca::configure_fast_kernels();
+    if (e == cudaSuccess && c->fast) e = ca::configure_wide_kernel();
     if (e != cudaSuccess) {
         ca_context_destroy(c);
         return fail_cuda(e, "context set-up");
@@ -219,6 +223,9 @@ int ca_context_set_option(ca_context* c, int option, int64_t value) {
         c->opt_ctas = (int)value;
     } else if (option == CA_OPT_SEQ_FIRST_TENSOR) {
         c->opt_sf_tensor = value != 0;
+    } else if (option == CA_OPT_WIDE_RUNS) {
+        if (value < 0 || value > 2) return fail(CA_ERR_INVALID, "wide-runs mode must be 0, 1 or 2");
+        c->opt_wide = (int)value;
     } else if (option == CA_OPT_DEPENDENT_LAUNCH) {
         if (value < 0 || value > 3) return fail(CA_ERR_INVALID, "dependent-launch mask out of range");
         c->opt_pdl = (int)value;
@@ -259,7 +266,7 @@ int ca_refresh_kernel_context(ca_context* c, const ca_chunk_info* infos, int n_i
     const int n_ctas = c->opt_ctas > 0 ? c->opt_ctas : c->num_sms * ca::FAST_CTAS_PER_SM;
     std::string err = ca::build_plan(c->plan, infos, n_infos, n_seqs, c->geo.n_heads, c->geo.chunk_size,
                                      c->tpp_threshold, n_ctas, c->max_chunks, c->opt_split, c->geo.d_head,
-                                     c->geo.esize, c->fast, c->opt_sf_tensor);
+                                     c->geo.esize, c->fast, c->opt_sf_tensor, c->opt_wide);
     if (!err.empty()) return fail(CA_ERR_INVALID, "work list rejected: " + err);
     return upload_plan(c, c->plan, stream);
 }
@@ -272,12 +279,13 @@ int ca_plan_build_for_context(const ca_context* c, ca_plan** out, const ca_chunk
     const int n_ctas = c->opt_ctas > 0 ? c->opt_ctas : c->num_sms * ca::FAST_CTAS_PER_SM;
     std::string err = ca::build_plan(p->plan, infos, n_infos, n_seqs, c->geo.n_heads, c->geo.chunk_size, c->tpp_threshold,
                                      n_ctas, c->max_chunks, c->opt_split, c->geo.d_head, c->geo.esize, c->fast,
-                                     c->opt_sf_tensor);
+                                     c->opt_sf_tensor, c->opt_wide);
     if (!err.empty()) {
         if (!*out) delete p;  // a caller-owned plan is left to the caller (its contents are unspecified now)
         return fail(CA_ERR_INVALID, "work list rejected: " + err);
     }
     p->max_chunks = c->max_chunks;
+    p->wide_mode = c->opt_wide;
     p->fast = c->fast;
     p->d_head = c->geo.d_head;
     p->esize = c->geo.esize;
@@ -291,7 +299,8 @@ int ca_refresh_from_plan(ca_context* c, const ca_plan* plan, ca_stream stream_) 
     const int n_ctas = c->opt_ctas > 0 ? c->opt_ctas : c->num_sms * ca::FAST_CTAS_PER_SM;
     if (pl.n_heads != c->geo.n_heads || pl.chunk_size != c->geo.chunk_size || plan->d_head != c->geo.d_head ||
         plan->esize != c->geo.esize || plan->fast != c->fast || plan->max_chunks > c->max_chunks ||
-        pl.split_phases != c->opt_split || pl.tpp_threshold != c->tpp_threshold || (c->fast && pl.n_ctas > n_ctas))
+        pl.split_phases != c->opt_split || pl.tpp_threshold != c->tpp_threshold || (c->fast && pl.n_ctas > n_ctas) ||
+        plan->wide_mode != c->opt_wide)
         return fail(CA_ERR_INVALID, "the plan was built for a different geometry, pool size or set of options");
     DeviceGuard guard(c->device);
     if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
@@ -303,7 +312,7 @@ static int upload_plan(ca_context* c, const ca::Plan& pl, cudaStream_t stream) {
 
     // pack every table into one staging buffer
     struct Part { const void* src; size_t bytes; size_t off; };
-    Part parts[8] = {
+    Part parts[9] = {
         {pl.items.data(), pl.items.size() * sizeof(ca::PlanItem), 0},
         {pl.merge_off.data(), pl.merge_off.size() * 4, 0},
         {pl.merge_slots.data(), pl.merge_slots.size() * 4, 0},
@@ -312,6 +321,7 @@ static int upload_plan(ca_context* c, const ca::Plan& pl, cudaStream_t stream) {
         {pl.path_tokens.data(), pl.path_tokens.size() * 4, 0},
         {pl.tail_chunk.data(), pl.tail_chunk.size() * 4, 0},
         {pl.tail_tokens.data(), pl.tail_tokens.size() * 4, 0},
+        {pl.wide_chunks.data(), pl.wide_chunks.size() * 4, 0},
     };
     size_t total = 0;
     for (Part& p : parts) {
@@ -352,6 +362,7 @@ static int upload_plan(ca_context* c, const ca::Plan& pl, cudaStream_t stream) {
     c->d_path_tokens = reinterpret_cast<const int32_t*>(c->dev_blob + parts[5].off);
     c->d_tail_chunk = reinterpret_cast<const int32_t*>(c->dev_blob + parts[6].off);
     c->d_tail_tokens = reinterpret_cast<const int32_t*>(c->dev_blob + parts[7].off);
+    c->d_wide_chunks = reinterpret_cast<const int32_t*>(c->dev_blob + parts[8].off);
 
     // partial-result scratch, grow-only
     const size_t slots = (size_t)pl.stats.n_slots;
@@ -373,6 +384,8 @@ static int upload_plan(ca_context* c, const ca::Plan& pl, cudaStream_t stream) {
     c->meta.n_items = (int)pl.items.size();
     c->meta.n_items_cf = pl.n_items_cf;
     c->meta.n_items_short = pl.n_items_short;
+    c->meta.n_items_wide = pl.n_items_wide;
+    c->meta.n_wide_chunks = (int)pl.wide_chunks.size();
     c->meta.n_ctas = pl.n_ctas;
     c->meta.n_merge_slots = (int64_t)pl.merge_slots.size();
     c->meta.split_phases = pl.split_phases;
@@ -443,8 +456,12 @@ int ca_attn_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_st
     p.max_chunks = (int)(c->max_chunks < INT32_MAX ? c->max_chunks : INT32_MAX);
     p.wait_limit = c->opt_wait_limit;
     p.withhold_item = c->opt_withhold_item;
-    // one launch per range of items; every launch draws from the counter the previous launch zeroed
+    // The work list holds every item once for all heads; a launch is given a range of (item, head) pieces.
+    // One launch per range; every launch draws from the counter the previous launch zeroed.
+    const int H = c->geo.n_heads;
     auto launch = [&](int lo, int hi) -> cudaError_t {
+        lo *= H;
+        hi *= H;
         if (hi <= lo) return cudaSuccess;
         p.item_lo = lo;
         p.item_hi = hi;
@@ -457,13 +474,34 @@ int ca_attn_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_st
         if (e == cudaSuccess) c->launch_parity ^= 1;
         return e;
     };
-    // the short private tails (the last n_items_short items) have a kernel of their own, launched first so
-    // that the persistent kernel's tail leads straight into the merge
-    const int n_items = c->meta.n_items - c->meta.n_items_short;
+    // Items are laid out [persistent kernel][short private tails][wide shared runs]; the two other kernels go
+    // first (the short tails before the wide runs, whose set-up then overlaps them) so that the persistent kernel's
+    // tail leads straight into the merge.
+    const int n_items = c->meta.n_items - c->meta.n_items_short - c->meta.n_items_wide;
     if (c->meta.n_items_short > 0 && (phases & 2)) {
-        p.item_lo = n_items;
-        p.item_hi = c->meta.n_items;
+        p.item_lo = n_items * H;
+        p.item_hi = (n_items + c->meta.n_items_short) * H;
         CA_CUDA(ca::launch_attn_short_tails(p, stream, (c->opt_pdl & 2) != 0));
+    }
+    if (c->meta.n_items_wide > 0 && (phases & 1)) {
+        ca::WideParams w;
+        w.pool = p.pool;
+        w.n_heads = p.n_heads;
+        w.q = q;
+        w.items = c->d_items;
+        w.item_lo = (c->meta.n_items - c->meta.n_items_wide) * H;
+        w.item_hi = c->meta.n_items * H;
+        w.wide_chunks = c->d_wide_chunks;
+        w.n_wide_chunks = c->meta.n_wide_chunks;
+        w.part_o = c->part_o;
+        w.part_ml = c->part_ml;
+        w.scale_log2 = p.scale_log2;
+        w.status = c->status;
+        w.n_slots = p.n_slots;
+        w.n_seqs = p.n_seqs;
+        w.max_chunks = p.max_chunks;
+        w.wait_limit = p.wait_limit;
+        CA_CUDA(ca::launch_attn_wide(w, stream, (c->opt_pdl & 2) != 0));
     }
     if (!c->meta.split_phases) {
         CA_CUDA(launch(0, n_items));
@@ -554,9 +592,10 @@ int ca_attn_merge(ca_context* c, void* out, int n_seqs, ca_stream stream_) {
     m.merge_slots = c->d_merge_slots;
     m.out = out;
     m.n_pairs = n_seqs * c->geo.n_heads;
-    m.n_slots_total = (long long)c->meta.n_merge_slots;
+    m.n_merge_entries = (long long)c->meta.n_merge_slots;
     m.n_slots = c->meta.stats.n_slots;
     m.status = c->status;
+    m.n_heads = c->geo.n_heads;
     CA_CUDA(ca::launch_attn_merge(m, static_cast<cudaStream_t>(stream_), (c->opt_pdl & 1) != 0));
     return CA_OK;
 }
@@ -582,7 +621,7 @@ int ca_attention_to_peers(ca_context* c, const void* q, void* const* peer_out, i
     m.merge_slots = c->d_merge_slots;
     m.out = nullptr;
     m.n_pairs = n_seqs * c->geo.n_heads;
-    m.n_slots_total = (long long)c->meta.n_merge_slots;
+    m.n_merge_entries = (long long)c->meta.n_merge_slots;
     m.n_slots = c->meta.stats.n_slots;
     m.status = c->status;
     m.n_heads = c->geo.n_heads;
@@ -780,13 +819,14 @@ int ca_context_stats(const ca_context* c, ca_plan_stats* out) {
 // ---- host-only planner ---------------------------------------------------------------------------------
 int ca_plan_build(ca_plan** out, const ca_chunk_info* infos, int n_infos, int n_seqs, int n_heads,
                   int chunk_size, int tpp_threshold, int n_ctas, int64_t max_chunks, int split_phases,
-                  int seq_first_tensor) {
+                  int seq_first_tensor, int wide_runs) {
     if (!out) return fail(CA_ERR_INVALID, "out is null");
     *out = nullptr;
     ca_plan* p = new (std::nothrow) ca_plan();
     if (!p) return fail(CA_ERR_INVALID, "out of host memory");
     std::string err = ca::build_plan(p->plan, infos, n_infos, n_seqs, n_heads, chunk_size, tpp_threshold, n_ctas,
-                                     max_chunks, split_phases != 0, ca::FAST_D, 2, true, seq_first_tensor != 0);
+                                     max_chunks, split_phases != 0, ca::FAST_D, 2, true, seq_first_tensor != 0, wide_runs);
+    p->wide_mode = wide_runs;
     if (!err.empty()) {
         delete p;
         return fail(CA_ERR_INVALID, "work list rejected: " + err);
@@ -811,6 +851,7 @@ int ca_plan_array(const ca_plan* plan, int which, const int32_t** data, int64_t*
         case CA_PLAN_PATH_TOKENS: v = &pl.path_tokens; break;
         case CA_PLAN_TAIL_CHUNK: v = &pl.tail_chunk; break;
         case CA_PLAN_TAIL_TOKENS: v = &pl.tail_tokens; break;
+        case CA_PLAN_WIDE_CHUNKS: v = &pl.wide_chunks; break;
         default: return fail(CA_ERR_INVALID, "unknown plan array");
     }
     *data = v->data();

@@ -72,15 +72,20 @@ struct ItemChunks {
     int c[9];  // pool slots of the item's tiles
 };
 
+// The work list holds every item ONCE, for all heads: work piece v of a launch is item v / n_heads for head
+// v % n_heads.  Partial rows are numbered per item as well; row ts of head h lives in slot ts * n_heads + h, so an
+// item's description carries slot_base * n_heads + h and consecutive rows of one head are n_heads slots apart.
 // Volatile so that the loads are issued where they are written (an item ahead of their use)
 // instead of being sunk to the first use by the compiler.
-__device__ __forceinline__ void load_item(const int4* items, int i, ItemView& v, ItemChunks& ch) {
+__device__ __forceinline__ void load_item(const int4* items, int v, int n_heads, ItemView& it, ItemChunks& ch) {
+    const int i = v / n_heads;
+    const int h = v - i * n_heads;
     int4 a, b, c, d;
     asm volatile("ld.global.nc.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(items + 4 * i));
     asm volatile("ld.global.nc.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(items + 4 * i + 1));
     asm volatile("ld.global.nc.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(c.x), "=r"(c.y), "=r"(c.z), "=r"(c.w) : "l"(items + 4 * i + 2));
     asm volatile("ld.global.nc.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(d.x), "=r"(d.y), "=r"(d.z), "=r"(d.w) : "l"(items + 4 * i + 3));
-    v = ItemView{a.x, a.y, a.z, a.w, b.x, b.y, b.z, 0};
+    it = ItemView{a.x, h, a.z, a.w, b.x, b.y, b.z, 0};
     ch = ItemChunks{{b.w, c.x, c.y, c.z, c.w, d.x, d.y, d.z, d.w}};
 }
 
@@ -105,10 +110,11 @@ __device__ __forceinline__ bool item_in_bounds(const PartialParams& p, const Ite
     const int splits = it.flags >> ITEM_SPLITS_SHIFT;
     const int slots = it.n_rows == 1 ? 1 : it.n_rows * (splits > 1 ? splits : 1);
     const int max_rows = splits == 4 ? 16 : (splits == 2 ? 32 : (splits == 1 ? MAX_ROWS_PER_ITEM : (splits == 0 ? 1 : 0)));
-    bool ok = it.n_tiles >= 1 && it.n_tiles <= MAX_TILES_PER_ITEM && it.n_rows >= 1 && it.n_rows <= max_rows &&
+    bool ok = (it.flags & ITEM_FLAG_WIDE) == 0 && it.n_tiles >= 1 && it.n_tiles <= MAX_TILES_PER_ITEM && it.n_rows >= 1 &&
+              it.n_rows <= max_rows &&
               it.head >= 0 && it.head < p.n_heads && it.row_begin >= 0 && it.slot_base >= 0 && it.last_tokens >= 0 &&
               it.last_tokens <= FAST_C;
-    if (p.n_slots > 0) ok = ok && it.slot_base + slots <= p.n_slots;
+    if (p.n_slots > 0) ok = ok && (long long)(it.slot_base + slots) * p.n_heads <= p.n_slots;
     if (p.n_seqs > 0) ok = ok && it.row_begin + it.n_rows <= p.n_seqs;
     if (ok && p.max_chunks > 0) {
 #pragma unroll
@@ -201,7 +207,7 @@ __device__ __forceinline__ void producer_loop(const PartialParams& p, Ring& rg) 
     ItemView it{};
     ItemChunks ch{};
     bool withheld = false;
-    if (id0 < p.item_hi) load_item(p.items, id0, it, ch);
+    if (id0 < p.item_hi) load_item(p.items, id0, p.n_heads, it, ch);
     while (id0 < p.item_hi && ok) {
         if (id0 == p.withhold_item) {
             // failure-path test: this CTA's consumers are never told about the item (nor about the end of the
@@ -212,6 +218,7 @@ __device__ __forceinline__ void producer_loop(const PartialParams& p, Ring& rg) 
         if (!item_in_bounds(p, it, ch)) {
             report(p.status, STATUS_BAD_WORK_LIST);  // skipped: its partial rows keep whatever they held
         } else {
+            it.slot_base = it.slot_base * p.n_heads + it.head;  // this head's first partial row
             // items of up to 16 rows get their query rows staged next to their first tile
             const bool stage_q = (it.flags >> ITEM_SPLITS_SHIFT) == NUM_CONSUMER_WARPS;
             bool first = true;
@@ -234,7 +241,7 @@ __device__ __forceinline__ void producer_loop(const PartialParams& p, Ring& rg) 
         }
         id0 = id1 >= 0 ? id1 : p.item_lo + n_fixed + atomicAdd(p.counter, 1);
         id1 = -1;
-        if (id0 < p.item_hi) load_item(p.items, id0, it, ch);
+        if (id0 < p.item_hi) load_item(p.items, id0, p.n_heads, it, ch);
     }
     if (ok && !withheld) {
         ItemView end_marker{};
@@ -532,18 +539,20 @@ __device__ __forceinline__ bool mma_item(const PartialParams& p, const ItemView&
         }
         return combine_row_and_store(p, it, scratch, merge_bar, row_items, warp, lane, rg);
     }
-    const int slot0 = it.slot_base + split * it.n_rows;
+    // rows of one head are n_heads slots apart
+    const int slot_lo = it.slot_base + (split * it.n_rows + r_lo) * p.n_heads;
+    const int slot_hi = it.slot_base + (split * it.n_rows + r_hi) * p.n_heads;
     if (v_lo) {
-        float* dst = p.part_o + (size_t)(slot0 + r_lo) * FAST_D + 2 * quad;
+        float* dst = p.part_o + (size_t)slot_lo * FAST_D + 2 * quad;
 #pragma unroll
         for (int n = 0; n < 16; n++) *reinterpret_cast<float2*>(dst + 8 * n) = make_float2(o[n][0], o[n][1]);
-        if (quad == 0) p.part_ml[slot0 + r_lo] = make_float2(m_lo, l_lo);
+        if (quad == 0) p.part_ml[slot_lo] = make_float2(m_lo, l_lo);
     }
     if (v_hi) {
-        float* dst = p.part_o + (size_t)(slot0 + r_hi) * FAST_D + 2 * quad;
+        float* dst = p.part_o + (size_t)slot_hi * FAST_D + 2 * quad;
 #pragma unroll
         for (int n = 0; n < 16; n++) *reinterpret_cast<float2*>(dst + 8 * n) = make_float2(o[n][2], o[n][3]);
-        if (quad == 0) p.part_ml[slot0 + r_hi] = make_float2(m_hi, l_hi);
+        if (quad == 0) p.part_ml[slot_hi] = make_float2(m_hi, l_hi);
     }
     return true;
 }
@@ -783,11 +792,13 @@ __global__ void __launch_bounds__(SHORT_WARPS * 32) attn_short_tails_kernel(cons
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int idx = p.item_lo + (int)blockIdx.x * SHORT_WARPS + warp;
-    if (idx >= p.item_hi) return;
+    const int vid = p.item_lo + (int)blockIdx.x * SHORT_WARPS + warp;  // work piece = (item, head)
+    if (vid >= p.item_hi) return;
+    const int idx = vid / p.n_heads, head = vid - idx * p.n_heads;
     const int4 d0 = __ldg(p.items + 4 * idx), d1 = __ldg(p.items + 4 * idx + 1);
-    const int head = d0.y, row = d0.z, slot = d1.x, flags = d1.y, chunk = d1.w;
-    if (head < 0 || head >= p.n_heads || row < 0 || slot < 0 || chunk < 0 || d1.z < 0 || (p.n_slots > 0 && slot >= p.n_slots) ||
+    const int row = d0.z, flags = d1.y, chunk = d1.w;
+    const int slot = d1.x * p.n_heads + head;
+    if (row < 0 || d1.x < 0 || chunk < 0 || d1.z < 0 || (p.n_slots > 0 && slot >= p.n_slots) ||
         (p.n_seqs > 0 && row >= p.n_seqs) || (p.max_chunks > 0 && chunk >= p.max_chunks)) {
         if (lane == 0) report(p.status, STATUS_BAD_WORK_LIST);  // skipped
         return;
@@ -876,24 +887,26 @@ __global__ void __launch_bounds__(SHORT_WARPS * 32) attn_short_tails_kernel(cons
 // maximum, acc this lane's four output elements weighted by 2^(m_i - mm), ll the warp-wide sum of the
 // weighted sums.  slot0: this lane's slot among the first 32 (-1: none), read by the caller.
 // A slot number from a merge list, or -1 (and the status word set) when it lies outside the partial rows.
-__device__ __forceinline__ int checked_slot(const MergeParams& p, int slot) {
-    if (p.n_slots > 0 && (slot < 0 || slot >= p.n_slots)) {
+// `entry` numbers a partial row per head-agnostic item; head h's copy of it is slot entry * n_heads + h.
+__device__ __forceinline__ int checked_slot(const MergeParams& p, int entry, int head) {
+    const long long slot = (long long)entry * p.n_heads + head;
+    if (entry < 0 || (p.n_slots > 0 && slot >= p.n_slots)) {
         if (p.status) atomicCAS(p.status, STATUS_OK, STATUS_BAD_WORK_LIST);
         return -1;
     }
-    return slot;
+    return (int)slot;
 }
 // The bounds [b, e) of a pair's list inside merge_slots; an impossible pair of offsets yields an empty list.
 __device__ __forceinline__ void checked_bounds(const MergeParams& p, int& b, int& e) {
-    if (p.n_slots > 0 && (b < 0 || e < b || e > p.n_slots_total)) {
+    if (p.n_merge_entries > 0 && (b < 0 || e < b || e > p.n_merge_entries)) {
         if (p.status) atomicCAS(p.status, STATUS_OK, STATUS_BAD_WORK_LIST);
         b = e = 0;
     }
 }
 
 template <int FIRST>
-__device__ __forceinline__ void merge_list(const MergeParams& p, int lane, int b, int e, int slot0, float& mm, float& ll,
-                                           float4& acc) {
+__device__ __forceinline__ void merge_list(const MergeParams& p, int lane, int head, int b, int e, int slot0, float& mm,
+                                           float& ll, float4& acc) {
     // The first 32 partials stay in registers; longer lists are re-read pass by pass.  The O rows of
     // the first 16 partials are requested together with the (max, sum) pairs, before the weights are
     // known, so the usual row (a dozen partials) costs ONE round trip after the wait instead of two;
@@ -913,7 +926,7 @@ __device__ __forceinline__ void merge_list(const MergeParams& p, int lane, int b
     }
     mm = ml0.y > 0.f ? ml0.x : NEG_BIG;
     for (int i = b + 32 + lane; i < e; i += 32) {
-        const int si = checked_slot(p, __ldg(p.merge_slots + i));
+        const int si = checked_slot(p, __ldg(p.merge_slots + i), head);
         if (si < 0) continue;
         const float2 ml = p.part_ml[si];
         if (ml.y > 0.f) mm = fmaxf(mm, ml.x);
@@ -930,7 +943,7 @@ __device__ __forceinline__ void merge_list(const MergeParams& p, int lane, int b
             slot = -1;
             ml = make_float2(NEG_BIG, 0.f);
             if (base + lane < e) {
-                slot = checked_slot(p, __ldg(p.merge_slots + base + lane));
+                slot = checked_slot(p, __ldg(p.merge_slots + base + lane), head);
                 if (slot >= 0) ml = p.part_ml[slot];
             }
         }
@@ -1007,12 +1020,14 @@ __global__ void __launch_bounds__(128, MIN_CTAS) attn_merge_kernel(const MergePa
     // The merge lists belong to the work list, which was uploaded before the partial kernel started:
     // as a programmatic dependent this kernel reads them while that kernel is still draining, and
     // only the partials themselves are read after the wait.
-    int b = 0, e = 0, slot0 = -1;
+    int b = 0, e = 0, slot0 = -1, head = 0;
     if (pair < p.n_pairs) {
-        b = __ldg(p.merge_off + pair);
-        e = __ldg(p.merge_off + pair + 1);
+        const int row = pair / p.n_heads;   // the lists are per row; every head of the row combines the same pieces
+        head = pair - row * p.n_heads;
+        b = __ldg(p.merge_off + row);
+        e = __ldg(p.merge_off + row + 1);
         checked_bounds(p, b, e);
-        if (b + lane < e) slot0 = checked_slot(p, __ldg(p.merge_slots + b + lane));
+        if (b + lane < e) slot0 = checked_slot(p, __ldg(p.merge_slots + b + lane), head);
     }
     // wait until the partial kernel's results are visible; a no-op for an ordinary launch
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -1023,7 +1038,7 @@ __global__ void __launch_bounds__(128, MIN_CTAS) attn_merge_kernel(const MergePa
     if (pair >= p.n_pairs) return;
     float mm, ll;
     float4 acc;
-    merge_list<FIRST>(p, lane, b, e, slot0, mm, ll, acc);
+    merge_list<FIRST>(p, lane, head, b, e, slot0, mm, ll, acc);
     store_row(p, pair, lane, acc, ll > 0.f ? 1.f / ll : 0.f);  // a row with no token yields zeros
 }
 
@@ -1035,16 +1050,17 @@ __global__ void __launch_bounds__(128, 3) attn_merge_wide_kernel(const MergePara
     __shared__ float2 s_ml[4];
     const int pair = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int b0 = __ldg(p.merge_off + pair), e0 = __ldg(p.merge_off + pair + 1);
+    const int row = pair / p.n_heads, head = pair - row * p.n_heads;
+    int b0 = __ldg(p.merge_off + row), e0 = __ldg(p.merge_off + row + 1);
     checked_bounds(p, b0, e0);
     const int per = (e0 - b0 + 3) >> 2;
     const int b = min(e0, b0 + warp * per), e = min(e0, b + per);
-    const int slot0 = b + lane < e ? checked_slot(p, __ldg(p.merge_slots + b + lane)) : -1;
+    const int slot0 = b + lane < e ? checked_slot(p, __ldg(p.merge_slots + b + lane), head) : -1;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     float mm, ll;
     float4 acc;
-    merge_list<16>(p, lane, b, e, slot0, mm, ll, acc);
+    merge_list<16>(p, lane, head, b, e, slot0, mm, ll, acc);
     s_acc[warp][lane] = acc;
     if (lane == 0) s_ml[warp] = make_float2(mm, ll);
     __syncthreads();
@@ -1144,7 +1160,7 @@ cudaError_t launch_attn_merge(const MergeParams& p, cudaStream_t stream, bool de
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int grid = (int)cfg.gridDim.x;
     // long lists under few rows: a CTA per row instead of a warp per row (a couple of waves at most)
-    const bool wide = p.n_pairs <= 8 * sms && p.n_slots_total > 48LL * p.n_pairs;
+    const bool wide = p.n_pairs <= 8 * sms && p.n_merge_entries * (long long)p.n_heads > 48LL * p.n_pairs;
     if (wide) cfg.gridDim = dim3(p.n_pairs);
     auto launch = [&]() {
         if (wide) return cudaLaunchKernelEx(&cfg, attn_merge_wide_kernel, p);

@@ -43,7 +43,7 @@ constexpr int W_SLOTS = 4;                             // ring slots, one K or V
 constexpr int W_Q_PANEL = W_ROWS * 128;                // one 64-element panel of the staged queries
 constexpr int W_SMEM_RING = 2 * W_Q_PANEL;             // queries first (32 KiB), then the ring
 constexpr int W_SMEM_BAR = W_SMEM_RING + W_SLOTS * FAST_TILE_BYTES;
-constexpr int W_NUM_BARS = 2 * W_SLOTS + 5;            // full, empty, s_full[2], p_full[2], o_done
+constexpr int W_NUM_BARS = 2 * W_SLOTS + 6;            // full, empty, s_full[2], p_full[2], o_done, q_ready
 constexpr int W_SMEM_BYTES = W_SMEM_BAR + W_NUM_BARS * 8 + 24;
 constexpr int W_THREADS = 192;
 constexpr int W_TMEM_COLS = 256;                       // O: 0..127, S buffers: 128..191 and 192..255
@@ -66,8 +66,8 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
     const uint32_t s_full = empty_bar + 8 * W_SLOTS;
     const uint32_t p_full = s_full + 16;
     const uint32_t o_done = p_full + 16;
+    const uint32_t q_ready = o_done + 8;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + W_SMEM_BAR + W_NUM_BARS * 8);
-    int* s_ok = reinterpret_cast<int*>(tmem_slot + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
             mbar_init(p_full + 8 * b, 4 * 32);
         }
         mbar_init(o_done, 1);
-        *s_ok = 1;
+        mbar_init(q_ready, 4 * 32);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -93,38 +93,42 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    const int idx = p.item_lo + (int)blockIdx.x;
+    // the work list holds every item once for all heads: piece v = (item v / n_heads, head v % n_heads)
+    const int vid = p.item_lo + (int)blockIdx.x;
+    const int idx = vid / p.n_heads, head = vid - idx * p.n_heads;
     const int4 d0 = __ldg(p.items + 4 * idx), d1 = __ldg(p.items + 4 * idx + 1);
-    const int n_tiles = d0.x, head = d0.y, row_begin = d0.z, n_rows = d0.w, slot_base = d1.x, chunk_off = d1.w;
+    const int n_tiles = d0.x, row_begin = d0.z, n_rows = d0.w, slot_base = d1.x, chunk_off = d1.w;
     // the work list may come from memory the host never saw: nothing in it is trusted
-    bool ok = n_tiles >= 1 && n_tiles <= WIDE_MAX_TILES && head >= 0 && head < p.n_heads && n_rows >= 1 && n_rows <= W_ROWS &&
+    bool ok = n_tiles >= 1 && n_tiles <= WIDE_MAX_TILES && n_rows >= 1 && n_rows <= W_ROWS &&
               row_begin >= 0 && slot_base >= 0 && chunk_off >= 0 && chunk_off + n_tiles <= p.n_wide_chunks &&
-              (p.n_slots <= 0 || slot_base + n_rows <= p.n_slots) && (p.n_seqs <= 0 || row_begin + n_rows <= p.n_seqs);
+              (p.n_slots <= 0 || (long long)(slot_base + n_rows) * p.n_heads <= p.n_slots) &&
+              (p.n_seqs <= 0 || row_begin + n_rows <= p.n_seqs);
     tc_fence_before_thread_sync();
-    __syncthreads();
+    __syncthreads();   // barriers initialised, TMEM address published
     tc_fence_after_thread_sync();
-    if (ok && p.max_chunks > 0 && (int)threadIdx.x < n_tiles) {
-        const int c = __ldg(p.wide_chunks + chunk_off + threadIdx.x);
-        if (c < 0 || c >= p.max_chunks) *s_ok = 0;
-    }
     const uint32_t tmem_base = *tmem_slot;
-    __syncthreads();
-    ok = ok && *s_ok != 0;
     if (!ok && threadIdx.x == 0) report(p.status, STATUS_BAD_WORK_LIST);  // skipped: its partial rows keep what they held
 
     if (ok) {
-        // ---- queries -> shared memory, K-major 128-byte-swizzled: two panels of 128 lines; rows past the item are zero
-        {
+        if (warp < 4) {
+            // ---- queries -> shared memory, K-major 128-byte-swizzled: two panels of 128 lines; rows past the item
+            // are zero.  The producer is already fetching K/V tiles meanwhile.
             const uint4* q = reinterpret_cast<const uint4*>(p.q);
-            for (int i = threadIdx.x; i < W_ROWS * 16; i += W_THREADS) {
-                const int r = i >> 4, g = i & 15;
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (r < n_rows) v = __ldg(q + ((size_t)(row_begin + r) * p.n_heads + head) * 16 + g);
+            uint4 v[16];   // all sixteen loads of a thread in flight together
+#pragma unroll
+            for (int u = 0; u < 16; u++) {
+                const int i = threadIdx.x + u * (4 * 32), r = i >> 4, g = i & 15;
+                v[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (r < n_rows) v[u] = __ldg(q + ((size_t)(row_begin + r) * p.n_heads + head) * 16 + g);
+            }
+#pragma unroll
+            for (int u = 0; u < 16; u++) {
+                const int i = threadIdx.x + u * (4 * 32), r = i >> 4, g = i & 15;
                 const uint32_t dst = sbase + (g >> 3) * W_Q_PANEL + r * 128 + (((g & 7) ^ (r & 7)) << 4);
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(v[u].x), "r"(v[u].y), "r"(v[u].z), "r"(v[u].w) : "memory");
             }
             fence_proxy_async();  // the tensor core reads shared memory through the async proxy
-            __syncthreads();
+            mbar_arrive(q_ready);
         }
 
         if (warp == 4) {
@@ -137,7 +141,11 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
                         report(p.status, STATUS_EMPTY_WAIT_TIMEOUT);
                         break;
                     }
-                    const int chunk = __ldg(p.wide_chunks + chunk_off + (i >> 1));
+                    int chunk = __ldg(p.wide_chunks + chunk_off + (i >> 1));
+                    if (chunk < 0 || (p.max_chunks > 0 && chunk >= p.max_chunks)) {
+                        report(p.status, STATUS_BAD_WORK_LIST);  // keep the pipeline moving on a chunk that exists
+                        chunk = 0;
+                    }
                     const uint8_t* src = p.pool + ((size_t)chunk * p.n_heads + head) * (size_t)FAST_STAGE_BYTES +
                                          (size_t)(i & 1) * FAST_TILE_BYTES;
                     mbar_arrive_expect_tx(full_bar + 8 * slot, FAST_TILE_BYTES);
@@ -175,7 +183,11 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
                     umma_commit(s_full + 8 * (j & 1));   // S of tile j is complete ...
                     umma_commit(empty_bar + 8 * slot);   // ... and its K tile may be overwritten
                 };
-                issue_qk(0);
+                if (!mbar_wait_bounded(q_ready, 0, p.wait_limit)) {
+                    report(p.status, STATUS_FULL_WAIT_TIMEOUT);
+                    live = false;
+                }
+                if (live) issue_qk(0);
                 for (int j = 0; j < n_tiles && live; j++) {
                     if (j + 1 < n_tiles) issue_qk(j + 1);  // S of the next tile is computed under this tile's softmax
                     if (!live) break;
@@ -281,7 +293,8 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
             }
             if (live) {
                 tc_fence_after_thread_sync();
-                float* dst = p.part_o + (size_t)(slot_base + r) * FAST_D;
+                const size_t slot = (size_t)(slot_base + r) * p.n_heads + head;  // row r of this head
+                float* dst = p.part_o + slot * FAST_D;
 #pragma unroll
                 for (int c = 0; c < 4; c++) {
                     uint32_t o[32];
@@ -293,7 +306,7 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
                             *reinterpret_cast<uint4*>(dst + c * 32 + 4 * i) = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
                     }
                 }
-                if (active) p.part_ml[slot_base + r] = make_float2(m_used, l);
+                if (active) p.part_ml[slot] = make_float2(m_used, l);
             }
         }
     }

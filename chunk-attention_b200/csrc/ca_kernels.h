@@ -33,8 +33,8 @@ struct PartialParams {
     const uint8_t* pool;         // chunk pool base
     int n_heads;
     const void* q;               // fp16 [n_seqs, n_heads, 128]
-    const int4* items;           // PlanItem as four int4
-    int item_lo, item_hi;        // the launch works through items [item_lo, item_hi)
+    const int4* items;           // PlanItem as four int4, each standing for n_heads pieces of work
+    int item_lo, item_hi;        // the launch works through pieces [item_lo, item_hi); piece v = item v / n_heads, head v % n_heads
     int* counter;                // next item to hand out (relative to item_lo); zero when the launch starts
     int* counter_next;           // the counter of the following launch: zeroed by this one
     float* part_o;               // [n_slots][128]
@@ -85,14 +85,14 @@ constexpr int MERGE_MAX_PEERS = 8;
 struct MergeParams {
     const float* part_o;
     const float2* part_ml;
-    const int32_t* merge_off;    // [n_rows * n_heads + 1]
-    const int32_t* merge_slots;
+    const int32_t* merge_off;    // [n_rows + 1]: the lists are per row, shared by the row's heads
+    const int32_t* merge_slots;  // partial rows numbered per head-agnostic item; head h's is entry * n_heads + h
     void* out;                   // fp16 [n_rows, n_heads, 128]; unused when n_peers > 0
     int n_pairs;                 // n_rows * n_heads
-    long long n_slots_total = 0; // length of merge_slots (picks the kernel instance)
+    long long n_merge_entries = 0; // length of merge_slots
     // Head-sharded output written straight into every rank's full-width buffer (peer memory over
     // NVLink): row s, local head h goes to peer_out[i] + ((s * total_heads) + head_offset + h) * 128.
-    int n_heads = 0;             // local heads (needed to split a pair index when n_peers > 0)
+    int n_heads = 0;             // local heads
     int n_peers = 0;             // 0: write `out` only
     int total_heads = 0;
     int head_offset = 0;

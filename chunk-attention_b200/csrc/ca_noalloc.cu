@@ -66,6 +66,8 @@ int ca_attention_static(const void* pool, int n_heads, const void* q, void* out,
         return fail(CA_ERR_INVALID, "work list needs " + std::to_string(n_slots) + " partial rows; the static scratch holds " +
                                         std::to_string(kMaxSlots) + " (CA_STATIC_MAX_SLOTS): use ca_attention, or plan fewer, larger pieces");
     if (n_ctas > 4096) return fail(CA_ERR_INVALID, "more than 4096 CTAs");
+    if (n_slots % n_heads != 0) return fail(CA_ERR_INVALID, "n_slots must be a multiple of n_heads (ca_plan_stats.n_slots is)");
+    if ((long long)n_items * n_heads > INT32_MAX) return fail(CA_ERR_INVALID, "too many items");
     if (n_seqs == 0) return CA_OK;
     if (!pool || !q || !out || !items || !merge_off || !merge_slots) return fail(CA_ERR_INVALID, "null pointer");
     if (n_ctas < 1 || n_items < 1) return fail(CA_ERR_INVALID, "a non-empty batch needs at least one item and one CTA");
@@ -115,7 +117,7 @@ int ca_attention_static(const void* pool, int n_heads, const void* q, void* out,
     p.q = q;
     p.items = reinterpret_cast<const int4*>(items);
     p.item_lo = 0;
-    p.item_hi = n_items;
+    p.item_hi = n_items * n_heads;  // every item stands for one piece of work per head
     p.counter = su.counters;
     p.counter_next = su.counters + 1;
     p.part_o = reinterpret_cast<float*>(su.scratch);
@@ -128,7 +130,7 @@ int ca_attention_static(const void* pool, int n_heads, const void* q, void* out,
     // size is not known here, so chunk numbers are taken as they come (max_chunks = 0).
     p.n_slots = n_slots;
     p.n_seqs = n_seqs;
-    e = ca::launch_attn_partials(p, n_ctas < n_items ? n_ctas : n_items, stream);
+    e = ca::launch_attn_partials(p, n_ctas < p.item_hi ? n_ctas : p.item_hi, stream);
     if (e != cudaSuccess) return fail(CA_ERR_CUDA, std::string("partial kernel launch: ") + cudaGetErrorString(e));
     ca::MergeParams m;
     m.part_o = p.part_o;
@@ -137,9 +139,10 @@ int ca_attention_static(const void* pool, int n_heads, const void* q, void* out,
     m.merge_slots = merge_slots;
     m.out = out;
     m.n_pairs = n_seqs * n_heads;
-    m.n_slots_total = n_slots;
+    m.n_merge_entries = n_slots / n_heads;  // every partial row is named once, per item, for all heads
     m.n_slots = n_slots;
     m.status = status_word;
+    m.n_heads = n_heads;
     e = ca::launch_attn_merge(m, stream, true);
     if (e != cudaSuccess) return fail(CA_ERR_CUDA, std::string("merge kernel launch: ") + cudaGetErrorString(e));
     return CA_OK;

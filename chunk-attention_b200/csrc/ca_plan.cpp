@@ -8,10 +8,12 @@
 namespace ca {
 namespace {
 
+// A unit is the same for every head (heads differ only in which tile of a chunk they read and where their partial
+// rows go), so units, items and merge lists are built ONCE and the kernels expand them over the heads.
 struct Unit {
-    const int32_t* chunks;        // pool slots, root to leaf (storage shared by the unit's heads)
+    const int32_t* chunks;        // pool slots, root to leaf
     int32_t n_chunks;
-    int32_t head, row_begin, n_rows, splits, last_tokens;
+    int32_t row_begin, n_rows, splits, last_tokens;
     bool tail;                    // last tile is a sequence's tail chunk
 };
 
@@ -24,13 +26,14 @@ std::string fmt(const char* f, long a = 0, long b = 0, long c = 0) {
 // Cut the units [ubegin, uend) into items.  Guided self-scheduling: an item takes
 // remaining_tiles / n_ctas tiles, clamped to [1, MAX_TILES_PER_ITEM], so the list starts with
 // full-size items and ends with single tiles.
-void cut_units(Plan& plan, const std::vector<Unit>& units, size_t ubegin, size_t uend, int n_ctas, int32_t& n_slots,
-               int64_t tiles_elsewhere = 0) {
+void cut_units(Plan& plan, const std::vector<Unit>& units, size_t ubegin, size_t uend, int n_ctas, int n_heads,
+               int32_t& n_slots, int64_t tiles_elsewhere = 0) {
     // tiles_elsewhere: work of the same step that other kernels do (the short tails); counting it keeps
     // the pieces of shared runs long - every piece of a run costs a partial row per sharer, so they
     // are not tapered down to single tiles for the sake of the last microsecond
+    // every item exists once per head: the work that remains is counted in (tile, head) pairs
     int64_t remaining = tiles_elsewhere;
-    for (size_t u = ubegin; u < uend; u++) remaining += units[u].n_chunks;
+    for (size_t u = ubegin; u < uend; u++) remaining += (int64_t)units[u].n_chunks * n_heads;
     for (size_t u = ubegin; u < uend; u++) {
         const Unit& un = units[u];
         const int n_tiles = un.n_chunks;
@@ -44,7 +47,7 @@ void cut_units(Plan& plan, const std::vector<Unit>& units, size_t ubegin, size_t
             plan.items.emplace_back();
             PlanItem& it = plan.items.back();
             it.n_tiles = len;
-            it.head = un.head;
+            it.head = 0;
             it.row_begin = un.row_begin;
             it.n_rows = un.n_rows;
             it.slot_base = n_slots;
@@ -54,7 +57,7 @@ void cut_units(Plan& plan, const std::vector<Unit>& units, size_t ubegin, size_t
             for (int k = 0; k < len; k++) it.chunk[k] = un.chunks[j + k];
             n_slots += item_slots(un.n_rows, un.splits);
             j += len;
-            remaining -= len;
+            remaining -= (int64_t)len * n_heads;
         }
     }
 }
@@ -63,9 +66,11 @@ void cut_units(Plan& plan, const std::vector<Unit>& units, size_t ubegin, size_t
 
 std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int n_seqs, int n_heads,
                        int chunk_size, int tpp_threshold, int n_ctas, int64_t max_chunks,
-                       bool split_phases, int d_head, int esize, bool fast_path, bool seq_first_tensor) {
+                       bool split_phases, int d_head, int esize, bool fast_path, bool seq_first_tensor, int wide_mode) {
     // the vectors keep their capacity from one rebuild to the next
     plan.items.clear();
+    plan.wide_chunks.clear();
+    plan.n_items_wide = 0;
     plan.merge_slots.clear();
     plan.path_chunks.clear();
     plan.path_tokens.clear();
@@ -134,7 +139,7 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
     plan.stats.n_chunks = n_infos;
     plan.stats.fast_path = fast_path ? 1 : 0;
     plan.stats.kernels_per_step = 1;
-    plan.merge_off.assign((size_t)n_seqs * n_heads + 1, 0);
+    plan.merge_off.assign((size_t)n_seqs + 1, 0);
     if (!fast_path) {
         plan.n_ctas = 0;
         return "";
@@ -166,13 +171,27 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
     }
     plan.stats.n_runs = (int)runs.size();
 
+    // ---- which runs go to the tcgen05 kernel ---------------------------------------------------------------
+    std::vector<char> run_wide(runs.size(), 0);
+    if (wide_mode == 2) {
+        for (size_t r = 0; r < runs.size(); r++) run_wide[r] = 1;
+    } else if (wide_mode == 1) {
+        double flops = 0;
+        for (const Run& r : runs)
+            if (r.e - r.b > WIDE_MIN_ROWS) flops += 4.0 * chunk_size * d_head * (double)(r.e - r.b) * (double)r.chunks.size() * n_heads;
+        const double t_mma = flops / WIDE_MMA_SYNC_FLOPS, t_hbm = (double)plan.stats.unique_kv_bytes / WIDE_HBM_BYTES_PER_S;
+        if (t_mma > 0.5 * t_hbm)
+            for (size_t r = 0; r < runs.size(); r++) run_wide[r] = runs[r].e - runs[r].b > WIDE_MIN_ROWS ? 1 : 0;
+    }
+
     // ---- units ---------------------------------------------------------------------------------------------
-    // the chunk lists are stored once (per run, per sequence) and referenced by every head's unit
     std::vector<int32_t> priv_arena;
     priv_arena.reserve(path_total);  // never reallocates: the units keep pointers into it
     std::vector<Unit> units;
-    units.reserve((runs.size() * 2 + (size_t)n_seqs) * n_heads);
-    for (Run& r : runs) {
+    units.reserve(runs.size() * 2 + (size_t)n_seqs);
+    for (size_t ri = 0; ri < runs.size(); ri++) {
+        Run& r = runs[ri];
+        if (run_wide[ri]) continue;
         const int n = r.e - r.b;
         const int n_blocks = (n + MAX_ROWS_PER_ITEM - 1) / MAX_ROWS_PER_ITEM;
         const int rows_per_block = (n + n_blocks - 1) / n_blocks;
@@ -181,8 +200,7 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
             const int rows = std::min(rows_per_block, r.e - rb);
             if (rows <= 0) continue;
             const int splits = rows <= 16 ? 4 : (rows <= 32 ? 2 : 1);
-            for (int h = 0; h < n_heads; h++)
-                units.push_back(Unit{r.chunks.data(), (int32_t)r.chunks.size(), h, rb, rows, splits, chunk_size, false});
+            units.push_back(Unit{r.chunks.data(), (int32_t)r.chunks.size(), rb, rows, splits, chunk_size, false});
         }
     }
     const size_t n_units_cf = units.size();
@@ -196,10 +214,10 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
         for (int s = 0; s < n_seqs; s++) {
             int n_priv = 0;
             for (int32_t p = plan.path_off[s]; p < plan.path_off[s + 1]; p++) n_priv += shared[path_info[p]] ? 0 : 1;
-            n_short += n_priv == 1 ? n_heads : 0;
+            n_short += n_priv == 1 ? 1 : 0;
         }
-        route_short = n_short > 4 * (int64_t)n_ctas;  // fewer are cheaper inside the persistent kernel than a launch of their own
-        if (route_short) short_units.reserve((size_t)n_short);
+        route_short = n_short * n_heads > 4 * (int64_t)n_ctas;  // fewer are cheaper inside the persistent kernel than a launch of their own
+        if (route_short) short_units.reserve((size_t)n_seqs);
     }
     for (int s = 0; s < n_seqs; s++) {
         const int32_t* priv = priv_arena.data() + priv_arena.size();
@@ -214,8 +232,7 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
             if (!shared[path_info[p]] && plan.path_tokens[p] != chunk_size)
                 return fmt("row %ld has a partially filled chunk that is not its tail", s);
         std::vector<Unit>& dst = (route_short && n_priv == 1) ? short_units : units;
-        for (int h = 0; h < n_heads; h++)
-            dst.push_back(Unit{priv, n_priv, h, s, 1, seq_first_tensor ? 4 : 0, plan.tail_tokens[s], true});
+        dst.push_back(Unit{priv, n_priv, s, 1, seq_first_tensor ? 4 : 0, plan.tail_tokens[s], true});
     }
 
     // ---- items ---------------------------------------------------------------------------------------------
@@ -223,29 +240,27 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
     {
         int64_t tiles = 0;
         for (const Unit& u : units) tiles += u.n_chunks;
-        plan.items.reserve((size_t)(tiles / 4 + units.size() + 4 * (size_t)n_ctas));
+        plan.items.reserve((size_t)(tiles / 4 + units.size() + 4 * (size_t)n_ctas / n_heads + 16));
     }
-    const int64_t short_tiles = (int64_t)short_units.size();
+    const int64_t short_tiles = (int64_t)short_units.size() * n_heads;
     if (!split_phases) {
-        cut_units(plan, units, 0, units.size(), n_ctas, n_slots, short_tiles);
+        cut_units(plan, units, 0, units.size(), n_ctas, n_heads, n_slots, short_tiles);
         plan.n_items_cf = 0;
         for (const PlanItem& it : plan.items) plan.n_items_cf += it.n_rows > 1 ? 1 : 0;
-        plan.stats.kernels_per_step = 2;
     } else {
         // each phase is a launch of its own, with its own taper towards small items
-        cut_units(plan, units, 0, n_units_cf, n_ctas, n_slots);
+        cut_units(plan, units, 0, n_units_cf, n_ctas, n_heads, n_slots);
         plan.n_items_cf = (int)plan.items.size();
-        cut_units(plan, units, n_units_cf, units.size(), n_ctas, n_slots);
-        plan.stats.kernels_per_step = (plan.n_items_cf > 0 ? 1 : 0) + 2;
+        cut_units(plan, units, n_units_cf, units.size(), n_ctas, n_heads, n_slots);
     }
-    plan.n_ctas = (int)std::min<int64_t>(n_ctas, std::max<int64_t>(1, (int64_t)plan.items.size()));
+    plan.n_ctas = (int)std::min<int64_t>(n_ctas, std::max<int64_t>(1, (int64_t)plan.items.size() * n_heads));
     // the short tails: one single-tile item each, after the persistent kernel's items
     plan.n_items_short = (int)short_units.size();
     for (const Unit& un : short_units) {
         plan.items.emplace_back();
         PlanItem& it = plan.items.back();
         it.n_tiles = 1;
-        it.head = un.head;
+        it.head = 0;
         it.row_begin = un.row_begin;
         it.n_rows = 1;
         it.slot_base = n_slots++;
@@ -253,13 +268,62 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
         it.last_tokens = un.last_tokens;
         it.chunk[0] = un.chunks[0];
     }
-    if (plan.n_items_short > 0) plan.stats.kernels_per_step += 1;
+    // the wide runs: (run, head, block of up to 128 rows) cut into about one wave of pieces of up to 32 chunks
+    {
+        int64_t n_wide_units = 0;
+        for (size_t ri = 0; ri < runs.size(); ri++)
+            if (run_wide[ri]) n_wide_units += (int64_t)((runs[ri].e - runs[ri].b + WIDE_MAX_ROWS - 1) / WIDE_MAX_ROWS) * n_heads;  // one per head
+        const int pieces_wanted = n_wide_units > 0 ? (int)std::max<int64_t>(1, n_ctas / n_wide_units) : 1;
+        for (size_t ri = 0; ri < runs.size(); ri++) {
+            if (!run_wide[ri]) continue;
+            const Run& r = runs[ri];
+            const int n = r.e - r.b, n_chunks = (int)r.chunks.size();
+            const int n_blocks = (n + WIDE_MAX_ROWS - 1) / WIDE_MAX_ROWS;
+            const int rows_per_block = (n + n_blocks - 1) / n_blocks;
+            // pieces of 2 .. 32 chunks, equal up to one
+            int n_pieces = std::min(pieces_wanted, std::max(1, n_chunks / 2));
+            n_pieces = std::max(n_pieces, (n_chunks + WIDE_MAX_TILES - 1) / WIDE_MAX_TILES);
+            const int32_t list_off = (int32_t)plan.wide_chunks.size();
+            plan.wide_chunks.insert(plan.wide_chunks.end(), r.chunks.begin(), r.chunks.end());
+            for (int blk = 0; blk < n_blocks; blk++) {
+                const int rb = r.b + blk * rows_per_block;
+                const int rows = std::min(rows_per_block, r.e - rb);
+                if (rows <= 0) continue;
+                for (int pc = 0; pc < n_pieces; pc++) {
+                    const int c0 = (int)((int64_t)n_chunks * pc / n_pieces), c1 = (int)((int64_t)n_chunks * (pc + 1) / n_pieces);
+                    if (c1 <= c0) continue;
+                    plan.items.emplace_back();
+                    PlanItem& it = plan.items.back();
+                    it.n_tiles = c1 - c0;
+                    it.head = 0;
+                    it.row_begin = rb;
+                    it.n_rows = rows;
+                    it.slot_base = n_slots;
+                    it.flags = ITEM_FLAG_WIDE | (1 << ITEM_SPLITS_SHIFT);
+                    it.last_tokens = chunk_size;
+                    it.chunk[0] = list_off + c0;
+                    n_slots += rows;
+                    plan.n_items_wide++;
+                }
+            }
+        }
+    }
+    {
+        // launches of one step: the persistent kernel (one per phase when the phases are split), the short-tails
+        // kernel, the wide-runs kernel, each only when it has items, and the merge kernel
+        const int n_persistent = (int)plan.items.size() - plan.n_items_short - plan.n_items_wide;
+        int k = 1;
+        if (!split_phases) k += n_persistent > 0 ? 1 : 0;
+        else k += (plan.n_items_cf > 0 ? 1 : 0) + (n_persistent - plan.n_items_cf > 0 ? 1 : 0);
+        k += (plan.n_items_short > 0 ? 1 : 0) + (plan.n_items_wide > 0 ? 1 : 0);
+        plan.stats.kernels_per_step = k;
+    }
 
-    // ---- merge lists -------------------------------------------------------------------------------------
+    // ---- merge lists: per ROW, the partial rows (numbered per head-agnostic item) that hold a piece of it ---------
     for (const PlanItem& it : plan.items) {
         const int splits = it.n_rows == 1 ? 1 : std::max(1, it.flags >> ITEM_SPLITS_SHIFT);
-        int32_t* off = plan.merge_off.data() + (size_t)it.row_begin * n_heads + it.head + 1;
-        for (int r = 0; r < it.n_rows; r++, off += n_heads) *off += splits;
+        int32_t* off = plan.merge_off.data() + (size_t)it.row_begin + 1;
+        for (int r = 0; r < it.n_rows; r++, off++) *off += splits;
     }
     for (size_t i = 1; i < plan.merge_off.size(); i++) plan.merge_off[i] += plan.merge_off[i - 1];
     plan.merge_slots.resize(plan.merge_off.back());
@@ -267,19 +331,21 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
         std::vector<int32_t> cursor(plan.merge_off.begin(), plan.merge_off.end() - 1);
         for (const PlanItem& it : plan.items) {
             const int splits = it.n_rows == 1 ? 1 : std::max(1, it.flags >> ITEM_SPLITS_SHIFT);
-            // per (row, head) the slots are listed split by split, as the loops below visit them
-            int32_t* cur = cursor.data() + (size_t)it.row_begin * n_heads + it.head;
-            for (int r = 0; r < it.n_rows; r++, cur += n_heads) {
+            // per row the slots are listed split by split, as the loops below visit them
+            int32_t* cur = cursor.data() + (size_t)it.row_begin;
+            for (int r = 0; r < it.n_rows; r++, cur++) {
                 int32_t* dst = plan.merge_slots.data() + *cur;
                 for (int sp = 0; sp < splits; sp++) dst[sp] = it.slot_base + sp * it.n_rows + r;
                 *cur += splits;
             }
         }
     }
-    plan.stats.n_items = (int)plan.items.size();
-    plan.stats.n_items_cf = plan.n_items_cf;
-    plan.stats.n_items_short = plan.n_items_short;
-    plan.stats.n_slots = n_slots;
+    // the counters describe the expanded work list (every item once per head)
+    plan.stats.n_items = (int)plan.items.size() * n_heads;
+    plan.stats.n_items_cf = plan.n_items_cf * n_heads;
+    plan.stats.n_items_short = plan.n_items_short * n_heads;
+    plan.stats.n_items_wide = plan.n_items_wide * n_heads;
+    plan.stats.n_slots = n_slots * n_heads;
     plan.stats.n_ctas = plan.n_ctas;
     return "";
 }

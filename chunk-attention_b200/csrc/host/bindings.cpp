@@ -32,6 +32,7 @@ py::dict stats_to_dict(const ca_plan_stats& st) {
     d["kernels_per_step"] = st.kernels_per_step;
     d["n_items_cf"] = st.n_items_cf;
     d["n_items_short"] = st.n_items_short;
+    d["n_items_wide"] = st.n_items_wide;
     return d;
 }
 

@@ -101,6 +101,10 @@ CA_API void ca_context_destroy(ca_context* ctx);
  * drains; bit 1, the attention kernel is set up while the kernel before it in the stream finishes
  * (it waits for that kernel's completion before it touches global memory).  Default 3. */
 #define CA_OPT_DEPENDENT_LAUNCH 5
+/* Shared runs on the tcgen05 / TMEM kernel (tensor memory accumulators, tcgen05.mma fed by descriptor from the
+ * staged tiles): 0 never, 1 (default) when walking the step's wide runs (more than 32 rows) with mma.sync would
+ * take longer than half of what its unique K/V needs at HBM rate, 2 every shared run. */
+#define CA_OPT_WIDE_RUNS 6
 /* SM cycles a kernel may wait on one of its internal barriers before it gives up, records a status code
  * (ca_status_read) and returns; default 4e9, about two seconds.  The waits exist so that a lost copy or a
  * damaged work list ends in an error code instead of a hung GPU. */
@@ -218,8 +222,10 @@ typedef struct ca_plan_stats {
     int32_t fast_path;         /* 1 when the tensor-core/TMA kernels serve this geometry          */
     int32_t kernels_per_step;  /* launches one ca_attention call makes                            */
     int32_t n_items_cf;        /* how many items are chunk-first items (they come first)          */
-    int32_t n_items_short;     /* how many items, at the end of the list, are short private tails
+    int32_t n_items_short;     /* how many items, after the persistent kernel's, are short private tails
                                   walked by the warp-per-item kernel instead of the persistent one */
+    int32_t n_items_wide;      /* how many items, at the end of the list, are pieces of wide shared runs
+                                  for the tcgen05 / TMEM kernel                                       */
 } ca_plan_stats;
 CA_API int ca_context_stats(const ca_context* ctx, ca_plan_stats* out);
 
@@ -263,7 +269,8 @@ CA_API int ca_rotary_embedding(const int64_t* positions, void* query, void* key,
  * calling thread's current device:
  *   pool            the chunk pool (layout above), 256-byte aligned
  *   q, out          [n_seqs, n_heads, 128] fp16, contiguous
- *   items, merge_off, merge_slots   the work list: the arrays ca_plan_build produces
+ *   items, merge_off, merge_slots   the work list: the arrays ca_plan_build produces with wide_runs = 0
+ *                   (this entry point launches the persistent kernel only)
  *                   (CA_PLAN_ITEMS with n_items entries of 16 ints, CA_PLAN_MERGE_OFF,
  *                   CA_PLAN_MERGE_SLOTS), copied to the device by the caller
  *   n_ctas          persistent CTAs to launch (ca_plan_stats.n_ctas)
@@ -313,9 +320,12 @@ CA_API int ca_attention_static_status(int32_t* status, ca_stream stream);
 #define CA_PLAN_PATH_TOKENS 7    /* int32[]: tokens in that chunk at refresh                     */
 #define CA_PLAN_TAIL_CHUNK 8     /* int32[n_seqs]                                                */
 #define CA_PLAN_TAIL_TOKENS 9    /* int32[n_seqs]                                                */
+#define CA_PLAN_WIDE_CHUNKS 10   /* int32[]: chunk lists of the wide items (an item's first chunk entry
+                                    is its offset here); empty when wide_runs is 0               */
+/* wide_runs: the meaning of CA_OPT_WIDE_RUNS (0 never, 1 by cost, 2 every shared run) */
 CA_API int ca_plan_build(ca_plan** out, const ca_chunk_info* infos, int n_infos, int n_seqs,
                          int n_heads, int chunk_size, int tpp_threshold, int n_ctas,
-                         int64_t max_chunks, int split_phases, int seq_first_tensor);
+                         int64_t max_chunks, int split_phases, int seq_first_tensor, int wide_runs);
 CA_API int ca_plan_array(const ca_plan* plan, int which, const int32_t** data, int64_t* count);
 CA_API int ca_plan_stats_get(const ca_plan* plan, ca_plan_stats* out);
 /* One work list for several contexts.  The caches of a model's layers see the same tree at every step, so

@@ -127,6 +127,19 @@ def build_cuda(ref, force=False):
     return target
 
 
+def install_models(ref):
+    """Install (copy, unchanged) the reference's pure-Python model layer -- src/chunk_attn/models: llama_hf and
+    ModelHost -- into oracle/_ref/py/models, the git-ignored output folder, so that the drop-in test can run
+    those very files on top of this repository's `chunk_attn` package on a machine that has no reference tree."""
+    import shutil
+    src = os.path.join(ref, "src", "chunk_attn", "models")
+    dst = os.path.join(OUT, "py", "models")
+    if os.path.isdir(dst):
+        shutil.rmtree(dst)
+    shutil.copytree(src, dst, ignore=shutil.ignore_patterns("__pycache__"))
+    return dst
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("CHUNK_ATTN_REFERENCE_TREE"), required="CHUNK_ATTN_REFERENCE_TREE" not in os.environ,
@@ -138,6 +151,7 @@ def main():
         print("reference tree not found at %s: keeping whatever is already in %s" % (a.ref, OUT))
         return
     print(build_cpu(a.ref, a.force))
+    print(install_models(a.ref))
     if a.cuda:
         print(build_cuda(a.ref, a.force))
 

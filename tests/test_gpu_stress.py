@@ -6,7 +6,7 @@ import random
 import pytest
 import torch
 
-from chunk_attn import Attention
+from chunk_attn import Attention, cabi
 
 pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda", 0)
@@ -16,9 +16,11 @@ TOL = 1e-3
 class Mirror:
     """Row-ordered list of (tokens, k, v) histories kept next to the engine."""
 
-    def __init__(self, H, seed, memory_mb=1024):
+    def __init__(self, H, seed, memory_mb=1024, wide=None):
         self.H, self.d = H, 128
         self.attn = Attention(n_heads=H, d_head=128, chunk_size=64, memory_mb=memory_mb, dtype=torch.float16, device=DEV)
+        if wide is not None:   # 2: every shared run on the tcgen05 kernel, 0: none (default: the planner decides)
+            self.attn.set_option(cabi.CA_OPT_WIDE_RUNS, wide)
         self.g = torch.Generator(device=DEV).manual_seed(seed)
         self.rows = []
         self.next_token = 1
@@ -79,10 +81,11 @@ class Mirror:
         return worst
 
 
+@pytest.mark.parametrize("wide", [None, 2, 0])
 @pytest.mark.parametrize("H,seed", [(1, 0), (3, 1), (8, 2), (40, 3)])
-def test_random_trees(H, seed):
+def test_random_trees(H, seed, wide):
     rnd = random.Random(seed)
-    m = Mirror(H, seed, memory_mb=1536 if H == 40 else 768)
+    m = Mirror(H, seed, memory_mb=1536 if H == 40 else 768, wide=wide)
     # a few unrelated roots, then sequences branching off existing ones at chunk-aligned and ragged cuts
     for _ in range(3):
         m.add(None, 0, rnd.choice([1, 63, 64, 65, 200, 512]))
@@ -107,10 +110,11 @@ def test_random_trees(H, seed):
     assert st["fast_path"] == 1 and st["n_shared_chunks"] > 0
 
 
-def test_wide_batch_over_one_long_prefix():
-    """300 rows over one 1024-token prefix (row blocks of 64 in the chunk-first phase), ragged suffixes, and a
-    decode loop long enough for every tail to cross a chunk boundary."""
-    m = Mirror(4, 9, memory_mb=1024)
+@pytest.mark.parametrize("wide", [0, 2])
+def test_wide_batch_over_one_long_prefix(wide):
+    """300 rows over one 1024-token prefix (row blocks of 64 in the chunk-first phase of the persistent kernel, of
+    100 on the tcgen05 kernel), ragged suffixes, and a decode loop long enough for every tail to cross a chunk boundary."""
+    m = Mirror(4, 9, memory_mb=1024, wide=wide)
     rnd = random.Random(9)
     m.add(None, 0, 1024 + 5)
     for _ in range(299):

@@ -162,7 +162,7 @@ def test_items_of_config2_shape():
             infos.append((cid, C, s, s + 1)); cid += 1
         infos.append((cid, 0, s, s + 1)); cid += 1
     plan = cabi.Plan(infos, 32, 32, n_ctas=296)
-    items = plan.items()
+    items = np.repeat(plan.items(), 32, axis=0)   # every item stands for one piece of work per head
     sizes = items[:, 0]
     full = sizes - (items[:, 5] & 1)          # the tails are empty here
     assert sizes.max() == 9 and full.max() == 8 and full[0] == 8 and full.min() >= 1
@@ -198,12 +198,61 @@ def test_short_tails_go_to_the_end_of_the_list_when_there_are_many():
     st = plan.stats()
     items = plan.items()
     assert st["n_items_short"] == 6 * H and st["kernels_per_step"] == 3
-    tail = items[-st["n_items_short"]:]
+    tail = items[-st["n_items_short"] // H:]      # the list holds every item once for all heads
     assert all(int(r[0]) == 1 and int(r[3]) == 1 and int(r[5]) & 1 for r in tail)      # one tile, one row, a tail
-    assert sorted((int(r[2]), int(r[1])) for r in tail) == [(s, h) for s in range(6) for h in range(H)]
-    main = items[:-st["n_items_short"]]
+    assert sorted(int(r[2]) for r in tail) == list(range(6))
+    main = items[:-st["n_items_short"] // H]
     assert not any(int(r[3]) == 1 and int(r[2]) < 6 for r in main)                     # none of them is walked twice
     plan2, _ = check(ora, H, d, n_ctas=64)        # 12 short items <= 4 x 64 CTAs: they stay in the main list
     assert plan2.stats()["n_items_short"] == 0 and plan2.stats()["kernels_per_step"] == 2
     plan3, _ = check(ora, H, d, n_ctas=2, seq_first_tensor=False)   # the CUDA-core option keeps its own walk
     assert plan3.stats()["n_items_short"] == 0
+
+
+# ---- wide shared runs: the items of the tcgen05 kernel -----------------------------------------------------------
+@pytest.mark.parametrize("n_seqs,n_ctas", [(2, 8), (70, 8), (130, 296), (300, 16)])
+def test_wide_runs_forced(n_seqs, n_ctas):
+    # wide_runs = 2 sends every shared run to the wide kernel: row blocks of up to 128 rows, pieces of up to 32 chunks
+    ora = build_tree(shared_spec(n_seqs, 5 * C, C + 9), H=2, d=8)
+    plan, loads = check(ora, 2, 8, n_ctas=n_ctas, wide_runs=2)
+    st = plan.stats()
+    items = plan.items()
+    wide = items[len(items) - st["n_items_wide"] // 2:]
+    assert st["n_items_wide"] > 0 and st["n_items_cf"] == 0
+    assert all(int(r[3]) > 1 for r in wide) and max(int(r[3]) for r in wide) <= 128
+    blocks = (n_seqs + 127) // 128
+    assert sum(int(r[0]) for r in wide) == 5 * blocks                # every chunk once per row block (and per head)
+    assert st["kernels_per_step"] == 3                                # wide + persistent (the private tails) + merge
+
+
+def test_wide_routing_by_cost():
+    # automatic routing: a long prefix under many rows and next to nothing else is bound by the contraction ...
+    ora = build_tree(shared_spec(100, 20 * C, 3), H=2, d=8)
+    plan, _ = check(ora, 2, 8, n_ctas=32, wide_runs=1)
+    assert plan.stats()["n_items_wide"] > 0
+    # ... the same prefix under long private tails is bound by memory and stays with the persistent kernel,
+    ora = build_tree(shared_spec(40, 2 * C, 20 * C), H=2, d=8)
+    plan, _ = check(ora, 2, 8, n_ctas=32, wide_runs=1)
+    assert plan.stats()["n_items_wide"] == 0
+    # and so do runs of few rows, however long
+    ora = build_tree(shared_spec(32, 30 * C, 3), H=2, d=8)
+    plan, _ = check(ora, 2, 8, n_ctas=32, wide_runs=1)
+    assert plan.stats()["n_items_wide"] == 0
+    # wide_runs = 0 never routes
+    ora = build_tree(shared_spec(100, 20 * C, 3), H=2, d=8)
+    plan, _ = check(ora, 2, 8, n_ctas=32, wide_runs=0)
+    assert plan.stats()["n_items_wide"] == 0
+
+
+def test_wide_two_level_tree_and_long_runs():
+    # a root run of 70 chunks (pieces of at most 32) over 150 rows (two row blocks), groups below it
+    spec = []
+    root = list(range(70 * C))
+    for g, n in enumerate((100, 50)):
+        gp = [10_000_000 * (g + 1) + j for j in range(2 * C)]
+        for s in range(n):
+            spec.append(root + gp + [100_000_000 * (len(spec) + 1) + j for j in range(5)])
+    ora = build_tree(spec, H=1, d=4)
+    plan, loads = check(ora, 1, 4, n_ctas=4, wide_runs=2, atol=1e-8)
+    wide = plan.items()[len(plan.items()) - plan.stats()["n_items_wide"]:]   # one head
+    assert max(int(r[0]) for r in wide) <= 32 and min(int(r[0]) for r in wide) >= 2

@@ -33,8 +33,9 @@ def device_i32(a):
 
 def call_static(eng, H, q, out, n_rows, items, st, merge_off, merge_slots, delta, status, n_slots=None):
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    # the item array holds every item once for all heads; ca_plan_stats counts the (item, head) pieces
     return cabi.lib.ca_attention_static(
-        eng.pool.data_ptr(), H, q.data_ptr(), out.data_ptr(), n_rows, items.data_ptr(), st["n_items"], st["n_ctas"],
+        eng.pool.data_ptr(), H, q.data_ptr(), out.data_ptr(), n_rows, items.data_ptr(), st["n_items"] // H, st["n_ctas"],
         merge_off.data_ptr(), merge_slots.data_ptr(), st["n_slots"] if n_slots is None else n_slots, delta,
         status.data_ptr() if status is not None else None, stream)
 
@@ -107,7 +108,7 @@ def test_static_entry_point_matches_ca_attention_and_the_oracle(n_ctas):
 
     # a work list naming partial rows outside [0, n_slots): the entries are skipped on the device and reported
     bad_items = plan.array(cabi.PLAN_ITEMS).reshape(-1, 16).copy()
-    bad_items[0, 4] = st["n_slots"] + 7                # slot_base of the first item
+    bad_items[0, 4] = st["n_slots"] // H + 7           # slot_base of the first item (numbered per item, not per head)
     bad_merge = plan.array(cabi.PLAN_MERGE_SLOTS).copy()
     bad_merge[-1] = cabi.CA_STATIC_MAX_SLOTS + 123
     for it_dev, ms_dev in ((device_i32(bad_items.reshape(-1)), merge_slots), (items, device_i32(bad_merge))):
