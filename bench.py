@@ -69,6 +69,9 @@ def parse():
     ap.add_argument("--warmup-runs", type=int, default=1, help="llama workload: untimed repetitions")
     ap.add_argument("--gather", default="p2p", choices=["nccl", "p2p"],
                     help="N > 1: all-gather with NCCL, or rows stored into peers' outputs by the merge kernel")
+    ap.add_argument("--barrier", default="own", choices=["own", "torch"],
+                    help="N > 1, p2p: this library's bounded barrier kernel, or torch's symmetric-memory barrier")
+    ap.add_argument("--no-multicast", action="store_true", help="N > 1, p2p: unicast peer stores instead of multimem.st")
     return ap.parse_args()
 
 
@@ -268,7 +271,7 @@ def build_engine(name, n_heads_local, dev, args, sharded=False, rank=0, keep_wor
     need_mb = (n_chunks * chunk_bytes + 2 ** 20 - 1) // 2 ** 20 + 1
     if sharded:
         attn = HeadShardedAttention(total_heads(name), 128, 64, memory_mb=need_mb, dtype=torch.float16, device=dev,
-                                    gather=args.gather)
+                                    gather=args.gather, barrier=args.barrier, multicast=not args.no_multicast)
         engine = attn.local
     else:
         attn = Attention(n_heads=n_heads_local, d_head=128, chunk_size=64, memory_mb=need_mb,
@@ -810,7 +813,8 @@ def run_b200(args):
             dist.all_reduce(flag, op=dist.ReduceOp.MIN)
             if int(flag.item()) != 1:
                 raise SystemExit("p2p gather differs from the NCCL all-gather")
-            gather_note = "p2p (verified equal to the NCCL all-gather on this batch)"
+            gather_note = "p2p, %s, %s barrier (verified equal to the NCCL all-gather on this batch)" % (
+                "multimem.st through the switch" if attn.multicast_in_use() else "unicast peer stores", attn.barrier_kind)
         except SystemExit:
             raise
         except Exception as exc:
@@ -902,15 +906,17 @@ def run_b200(args):
             ql = attn._mine(q).contiguous()
             bufs = attn._symm_buffers(ql.shape[0], ql.dtype, ql.device)
             # rows stored into every rank's buffer, no barrier after the step (nobody reads the rows here)
+            # = the step as the producer sees it when the READER of the gathered rows takes the barrier
             breakdown["rows_stored_into_peers_no_barrier_us"] = timed_loop(
                 lambda: attn.local.forward_to_peers(q=ql, peer_out_ptrs=bufs[0][2], total_heads=attn.n_heads,
-                                                    head_offset=attn.rank * attn.h_local))
-            breakdown["barrier_alone_us"] = timed_loop(lambda: bufs[0][1].barrier(channel=0))
-            if hasattr(attn, "forward_deferred"):
-                # the same step with the barrier handed to the reader of the gathered rows (a side stream), so
-                # that the next step's attention kernel, which does not read them, starts under it
-                breakdown["step_barrier_deferred_to_reader_us"] = timed_loop(lambda: attn.forward_deferred(q))
-                attn.wait_deferred()
+                                                    head_offset=attn.rank * attn.h_local, multicast_ptr=bufs[0][3]))
+            if bufs[0][3]:
+                breakdown["rows_stored_unicast_no_barrier_us"] = timed_loop(
+                    lambda: attn.local.forward_to_peers(q=ql, peer_out_ptrs=bufs[0][2], total_heads=attn.n_heads,
+                                                        head_offset=attn.rank * attn.h_local, multicast_ptr=0))
+            breakdown["barrier_alone_us"] = timed_loop(lambda: attn._barrier(bufs[0][1]))
+            breakdown["torch_symm_mem_barrier_alone_us"] = timed_loop(lambda: bufs[0][1].barrier(channel=0))
+            breakdown["barrier_status"] = attn.barrier_status()
 
     kern = kernel_times(engine, q, K, args.split_phases) if stats["fast_path"] else None
     clocks = sampler.stop() if rank == 0 else None

@@ -26,7 +26,7 @@ PLAN_ITEMS = 0
 EXPORTED = [
     "ca_last_error", "ca_version", "ca_chunk_bytes", "ca_tile_elem_offset", "ca_context_create",
     "ca_context_destroy", "ca_context_set_option", "ca_refresh_kernel_context", "ca_append_kv",
-    "ca_context_delta_tokens", "ca_attention", "ca_attention_host", "ca_attention_to_peers", "ca_attn_partials", "ca_attn_merge",
+    "ca_context_delta_tokens", "ca_attention", "ca_attention_host", "ca_attention_to_peers", "ca_peer_barrier", "ca_attn_partials", "ca_attn_merge",
     "ca_scatter_prefill", "ca_scatter_rows", "ca_copy_chunks", "ca_read_chunk", "ca_status_read", "ca_status_clear", "ca_context_stats",
     "ca_context_read_trace",
     "ca_plan_build", "ca_plan_build_for_context", "ca_refresh_from_plan", "ca_plan_array", "ca_plan_stats_get", "ca_plan_destroy", "ca_attention_static", "ca_attention_static_status",
@@ -74,7 +74,8 @@ def _load():
         "ca_context_delta_tokens": (i32, [vp]),
         "ca_attention": (i32, [vp, vp, vp, i32, i32, vp]),
         "ca_attention_host": (i32, [vp, vp, vp, i32, i32, vp]),
-        "ca_attention_to_peers": (i32, [vp, vp, C.POINTER(vp), i32, i32, i32, i32, vp]),
+        "ca_attention_to_peers": (i32, [vp, vp, C.POINTER(vp), i32, vp, i32, i32, i32, vp]),
+        "ca_peer_barrier": (i32, [C.POINTER(vp), i32, i32, C.c_uint32, i64, vp, vp]),
         "ca_attn_partials": (i32, [vp, vp, i32, i32, vp]),
         "ca_attn_merge": (i32, [vp, vp, i32, vp]),
         "ca_scatter_prefill": (i32, [vp, vp, vp, i64, i64, i32, i32, C.POINTER(C.c_int32), vp]),
@@ -119,6 +120,14 @@ def make_infos(infos):
     for i, (cid, nt, b, e) in enumerate(infos):
         arr[i] = ChunkInfo(cid, nt, b, e)
     return arr, len(infos)
+
+
+def peer_barrier(flag_ptrs, rank, epoch, timeout_ns=2_000_000_000, status_ptr=None, stream=None):
+    """Bounded barrier among the ranks whose flag arrays are flag_ptrs (device addresses), on `stream`."""
+    import torch
+    arr = (C.c_void_p * len(flag_ptrs))(*flag_ptrs)
+    st = C.c_void_p(stream if stream is not None else torch.cuda.current_stream().cuda_stream)
+    check(lib.ca_peer_barrier(arr, len(flag_ptrs), rank, epoch & 0xFFFFFFFF, timeout_ns, status_ptr, st))
 
 
 class Plan:
@@ -188,10 +197,10 @@ class Context:
         check(lib.ca_attention_host(self._h, q_cpu.data_ptr(), out_cpu.data_ptr(), q_cpu.shape[0], partition,
                                     self._stream()))
 
-    def attention_to_peers(self, q, peer_ptrs, total_heads, head_offset):
+    def attention_to_peers(self, q, peer_ptrs, total_heads, head_offset, multicast_ptr=None):
         arr = (C.c_void_p * len(peer_ptrs))(*peer_ptrs)
-        check(lib.ca_attention_to_peers(self._h, q.data_ptr(), arr, len(peer_ptrs), total_heads, head_offset,
-                                        q.shape[0], self._stream()))
+        check(lib.ca_attention_to_peers(self._h, q.data_ptr(), arr, len(peer_ptrs), multicast_ptr, total_heads,
+                                        head_offset, q.shape[0], self._stream()))
 
     def attn_partials(self, q, phases=3):
         check(lib.ca_attn_partials(self._h, q.data_ptr(), q.shape[0], phases, self._stream()))

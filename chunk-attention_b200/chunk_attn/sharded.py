@@ -7,8 +7,12 @@ everywhere without any metadata exchange.  The only exchange is the optional gat
 on every rank, in one of two ways:
   gather="nccl"  all_gather_into_tensor (NCCL over NVLink) followed by a permute;
   gather="p2p"   the merge kernel itself stores every output row into each rank's full-width buffer
-                 (symmetric memory, plain peer stores over NVLink), followed by one barrier on the
-                 stream: compute and gather in a single kernel, no collective call and no permute.
+                 (symmetric memory; one multimem.st per row segment that the NVSwitch replicates when a multicast
+                 mapping exists, else plain peer stores over NVLink), followed by one barrier on the stream:
+                 compute and gather in a single kernel, no collective call and no permute.  The barrier is this
+                 library's own kernel (ca_peer_barrier): a release store of the step number into every peer's flag
+                 array and a wait on one's own, BOUNDED -- a peer that never arrives costs the time limit and a
+                 status code (`barrier_status()`), never a hung GPU.
 The reference itself is single-device (no torch.distributed anywhere in it).
 """
 import time
@@ -24,7 +28,8 @@ class PeerLost(RuntimeError):
 
 class HeadShardedAttention:
     def __init__(self, n_heads, d_head, chunk_size, memory_mb=1024, share_prefix=True, tpp_threshold=1,
-                 dtype=None, device=None, group=None, attention_factory=None, gather="nccl"):
+                 dtype=None, device=None, group=None, attention_factory=None, gather="nccl", barrier="own",
+                 multicast=True, barrier_timeout_s=2.0):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -44,6 +49,14 @@ class HeadShardedAttention:
             raise ValueError("gather must be 'nccl' or 'p2p'")
         self.gather_mode = gather if self.world > 1 else "nccl"
         self._symm = None      # (tensor [rows, H, d], handle, peer pointers)
+        if barrier not in ("own", "torch"):
+            raise ValueError("barrier must be 'own' (bounded, this library's kernel) or 'torch' (symmetric-memory barrier)")
+        self.barrier_kind = barrier
+        self.use_multicast = multicast
+        self.barrier_timeout_ns = int(barrier_timeout_s * 1e9)
+        self._flags = None     # (flag tensor, handle, peer pointers) of the own barrier
+        self._epoch = 0
+        self._status = None
         # host-side liveness check (off unless check_peers / peer_timeout_s is used)
         self.peer_timeout_s = None
         self._hb_store = None
@@ -140,10 +153,40 @@ class HeadShardedAttention:
             for _ in range(2):
                 buf = symm_mem.empty((rows, self.n_heads, self.d_head), dtype=dtype, device=device)
                 hdl = symm_mem.rendezvous(buf, group)
-                bufs.append((buf, hdl, [int(p) for p in hdl.buffer_ptrs]))
+                mc = 0
+                if self.use_multicast:
+                    try:
+                        mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
+                    except Exception:
+                        mc = 0
+                bufs.append((buf, hdl, [int(p) for p in hdl.buffer_ptrs], mc))
             self._symm = bufs
             self._step = 0
+            if self._flags is None:
+                flags = symm_mem.empty((64,), dtype=torch.int32, device=device)
+                flags.zero_()
+                fh = symm_mem.rendezvous(flags, group)
+                self._flags = (flags, fh, [int(p) for p in fh.buffer_ptrs])
+                self._status = torch.zeros(1, dtype=torch.int32, device=device)
+                torch.cuda.synchronize(device)
+                fh.barrier(channel=0)   # once, at set-up: nobody signals before every array is zero
+                torch.cuda.synchronize(device)
         return self._symm
+
+    def multicast_in_use(self):
+        return bool(self._symm and self._symm[0][3])
+
+    def _barrier(self, hdl):
+        if self.barrier_kind == "torch":
+            hdl.barrier(channel=0)
+            return
+        from . import cabi
+        self._epoch += 1
+        cabi.peer_barrier(self._flags[2], self.rank, self._epoch, self.barrier_timeout_ns, self._status.data_ptr())
+
+    def barrier_status(self):
+        """0, or 6 when a barrier of this object gave up waiting for a peer (synchronises)."""
+        return int(self._status.item()) if self._status is not None else 0
 
     def forward(self, q, partition=0, gather=True):
         """Attention of this rank's head slice; with gather=True the full-width [n_seqs, H, d] result on every rank.
@@ -157,11 +200,11 @@ class HeadShardedAttention:
             # Buffer k & 1 for step k.  When a rank passes the barrier of step k + 1, every rank's stream
             # has passed its reads of step k's buffer, so step k + 2 may overwrite it without a barrier
             # of its own: one barrier per step.
-            buf, hdl, ptrs = self._symm_buffers(ql.shape[0], ql.dtype, ql.device)[self._step & 1]
+            buf, hdl, ptrs, mc = self._symm_buffers(ql.shape[0], ql.dtype, ql.device)[self._step & 1]
             self._step += 1
             self.local.forward_to_peers(q=ql, peer_out_ptrs=ptrs, total_heads=self.n_heads,
-                                        head_offset=self.rank * self.h_local)
-            hdl.barrier(channel=0)   # every rank's rows have landed everywhere
+                                        head_offset=self.rank * self.h_local, multicast_ptr=mc)
+            self._barrier(hdl)       # every rank's rows have landed everywhere
             return buf[:ql.shape[0]]
         out = self.forward_local(q, partition)
         return self.gather(out) if gather else out

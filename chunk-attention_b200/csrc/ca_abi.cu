@@ -96,6 +96,7 @@ struct ca_context {
     struct {
         int n_seqs = 0, n_items = 0, n_items_cf = 0, n_items_short = 0, n_items_wide = 0, n_wide_chunks = 0, n_ctas = 1;
         int64_t n_merge_slots = 0;  // entries of merge_slots
+        int max_merge_len = 0;
         bool split_phases = false;
         ca_plan_stats stats{};
     } meta;
@@ -388,6 +389,7 @@ static int upload_plan(ca_context* c, const ca::Plan& pl, cudaStream_t stream) {
     c->meta.n_wide_chunks = (int)pl.wide_chunks.size();
     c->meta.n_ctas = pl.n_ctas;
     c->meta.n_merge_slots = (int64_t)pl.merge_slots.size();
+    c->meta.max_merge_len = pl.max_merge_len;
     c->meta.split_phases = pl.split_phases;
     c->meta.stats = pl.stats;
     c->valid = true;
@@ -501,6 +503,9 @@ int ca_attn_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_st
         w.n_seqs = p.n_seqs;
         w.max_chunks = p.max_chunks;
         w.wait_limit = p.wait_limit;
+        w.trace = c->trace;
+        c->trace_ctas = (w.item_hi - w.item_lo) < kTraceCtas ? (w.item_hi - w.item_lo) : 0;
+        if (c->trace_ctas == 0) w.trace = nullptr;
         CA_CUDA(ca::launch_attn_wide(w, stream, (c->opt_pdl & 2) != 0));
     }
     if (!c->meta.split_phases) {
@@ -593,6 +598,7 @@ int ca_attn_merge(ca_context* c, void* out, int n_seqs, ca_stream stream_) {
     m.out = out;
     m.n_pairs = n_seqs * c->geo.n_heads;
     m.n_merge_entries = (long long)c->meta.n_merge_slots;
+    m.max_list = c->meta.max_merge_len;
     m.n_slots = c->meta.stats.n_slots;
     m.status = c->status;
     m.n_heads = c->geo.n_heads;
@@ -600,15 +606,35 @@ int ca_attn_merge(ca_context* c, void* out, int n_seqs, ca_stream stream_) {
     return CA_OK;
 }
 
-int ca_attention_to_peers(ca_context* c, const void* q, void* const* peer_out, int n_peers, int total_heads,
-                          int head_offset, int n_seqs, ca_stream stream_) {
+int ca_peer_barrier(void* const* flag_arrays, int n_peers, int rank, uint32_t epoch, int64_t timeout_ns, int32_t* status,
+                    ca_stream stream_) {
+    if (n_peers < 1 || n_peers > ca::MERGE_MAX_PEERS || !flag_arrays) return fail(CA_ERR_INVALID, "1 to 8 flag arrays are required");
+    if (rank < 0 || rank >= n_peers) return fail(CA_ERR_INVALID, "rank outside the group");
+    if (timeout_ns <= 0) return fail(CA_ERR_INVALID, "the barrier needs a time limit");
+    ca::PeerBarrierParams p{};
+    for (int i = 0; i < n_peers; i++) {
+        if (!flag_arrays[i] || reinterpret_cast<uintptr_t>(flag_arrays[i]) % 4) return fail(CA_ERR_INVALID, "null or misaligned flag array");
+        p.flags[i] = static_cast<uint32_t*>(flag_arrays[i]);
+    }
+    p.n_peers = n_peers;
+    p.rank = rank;
+    p.epoch = epoch;
+    p.timeout_ns = timeout_ns;
+    p.status = status;
+    CA_CUDA(ca::launch_peer_barrier(p, static_cast<cudaStream_t>(stream_)));
+    return CA_OK;
+}
+
+int ca_attention_to_peers(ca_context* c, const void* q, void* const* peer_out, int n_peers, void* multicast_out,
+                          int total_heads, int head_offset, int n_seqs, ca_stream stream_) {
     int rc = check_attention_args(c, q, n_seqs);
     if (rc != CA_OK) return rc;
     if (!c->fast) return fail(CA_ERR_INVALID, "writing into peers' outputs exists only for fp16 / d_head 128 / chunk_size 64");
     if (n_peers < 1 || n_peers > ca::MERGE_MAX_PEERS || !peer_out) return fail(CA_ERR_INVALID, "1 to 8 peer outputs are required");
     if (head_offset < 0 || total_heads < head_offset + c->geo.n_heads) return fail(CA_ERR_INVALID, "head slice outside the full width");
     for (int i = 0; i < n_peers; i++)
-        if (!peer_out[i] || reinterpret_cast<uintptr_t>(peer_out[i]) % 8) return fail(CA_ERR_INVALID, "null or misaligned peer output");
+        if (!peer_out[i] || reinterpret_cast<uintptr_t>(peer_out[i]) % 16) return fail(CA_ERR_INVALID, "null or misaligned peer output");
+    if (reinterpret_cast<uintptr_t>(multicast_out) % 16) return fail(CA_ERR_INVALID, "misaligned multicast output");
     if (n_seqs == 0) return CA_OK;
     rc = ca_attn_partials(c, q, n_seqs, 3, stream_);
     if (rc != CA_OK) return rc;
@@ -622,6 +648,7 @@ int ca_attention_to_peers(ca_context* c, const void* q, void* const* peer_out, i
     m.out = nullptr;
     m.n_pairs = n_seqs * c->geo.n_heads;
     m.n_merge_entries = (long long)c->meta.n_merge_slots;
+    m.max_list = c->meta.max_merge_len;
     m.n_slots = c->meta.stats.n_slots;
     m.status = c->status;
     m.n_heads = c->geo.n_heads;
@@ -629,6 +656,7 @@ int ca_attention_to_peers(ca_context* c, const void* q, void* const* peer_out, i
     m.total_heads = total_heads;
     m.head_offset = head_offset;
     for (int i = 0; i < n_peers; i++) m.peer_out[i] = peer_out[i];
+    m.mc_out = multicast_out;
     CA_CUDA(ca::launch_attn_merge(m, static_cast<cudaStream_t>(stream_), (c->opt_pdl & 1) != 0));
     return CA_OK;
 }

@@ -782,105 +782,123 @@ __global__ void __launch_bounds__(NUM_THREADS, 2) attn_partial_kernel(const Part
 // A (sequence, head) whose private part is a single, usually partly filled, chunk is too small an item
 // for the persistent kernel (an item costs its warps the same whatever it holds).  When a batch has
 // many of them the planner puts them at the end of the item list and this kernel walks them instead:
-// one WARP per item, straight from global memory.  A half-warp reads one K row per load (coalesced, the
-// query granule of each lane in registers) and sums the products over its 16 lanes, maximum and sum come
-// from shuffles, and in P.V each lane owns four output elements (coalesced 8-byte reads along a V row).  The result is an ordinary partial (max and sum in log2
-// units, un-normalised O), combined with the row's other partials by the merge kernel.
+// one HALF-WARP per item, straight from global memory, eight tokens per round with all of a round's loads
+// (K rows and V rows) issued before any is used, so a tail of up to eight tokens costs one round trip after
+// the item's description.  Lane g of the half-warp owns granule g of every row: 16 bytes of each K row (the
+// products are summed over the 16 lanes with shuffles, which leaves every lane with every score, so the
+// softmax needs no further exchange) and 16 bytes = 8 output elements of each V row.  The result is an
+// ordinary partial (max and sum in log2 units, un-normalised O), combined with the row's other partials by
+// the merge kernel.
 constexpr int SHORT_WARPS = 8;
+constexpr int SHORT_ITEMS_PER_CTA = 2 * SHORT_WARPS;
+constexpr int SHORT_BLOCK = 8;   // tokens per round
 
-__global__ void __launch_bounds__(SHORT_WARPS * 32) attn_short_tails_kernel(const PartialParams p) {
+__global__ void __launch_bounds__(SHORT_WARPS * 32, 2) attn_short_tails_kernel(const PartialParams p) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int vid = p.item_lo + (int)blockIdx.x * SHORT_WARPS + warp;  // work piece = (item, head)
-    if (vid >= p.item_hi) return;
-    const int idx = vid / p.n_heads, head = vid - idx * p.n_heads;
-    const int4 d0 = __ldg(p.items + 4 * idx), d1 = __ldg(p.items + 4 * idx + 1);
-    const int row = d0.z, flags = d1.y, chunk = d1.w;
-    const int slot = d1.x * p.n_heads + head;
-    if (row < 0 || d1.x < 0 || chunk < 0 || d1.z < 0 || (p.n_slots > 0 && slot >= p.n_slots) ||
-        (p.n_seqs > 0 && row >= p.n_seqs) || (p.max_chunks > 0 && chunk >= p.max_chunks)) {
-        if (lane == 0) report(p.status, STATUS_BAD_WORK_LIST);  // skipped
-        return;
-    }
-    const int nt = min(FAST_C, d1.z + ((flags & ITEM_FLAG_TAIL) ? p.delta_tokens : 0));
-    if (nt <= 0) {  // an empty reserved tail
-        if (lane == 0) p.part_ml[slot] = make_float2(NEG_BIG, 0.f);
-        return;
-    }
-    // A half-warp reads one 256-byte K row per load, lane & 15 = granule: each lane keeps its granule of
-    // the query (pre-scaled to log2 units) in registers.
-    const int g16 = lane & 15, half = lane >> 4;
-    float qf[8];
-    {
-        const __half* q = reinterpret_cast<const __half*>(p.q) + ((size_t)row * p.n_heads + head) * FAST_D + 8 * g16;
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(q));
-        const __half2* h = reinterpret_cast<const __half2*>(&raw);
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const float2 f = __half22float2(h[k]);
-            qf[2 * k] = f.x * p.scale_log2;
-            qf[2 * k + 1] = f.y * p.scale_log2;
+    const int g = lane & 15, half = lane >> 4;
+    const int vid = p.item_lo + ((int)blockIdx.x * SHORT_WARPS + warp) * 2 + half;  // work piece = (item, head)
+    // every lane runs every round (the shuffles below need the whole warp); a half-warp without an item, or with a
+    // rejected one, simply has no tokens
+    int nt = 0, row = 0, head = 0, chunk = 0, slot = -1;
+    if (vid < p.item_hi) {
+        const int idx = vid / p.n_heads;
+        head = vid - idx * p.n_heads;
+        const int4 d0 = __ldg(p.items + 4 * idx), d1 = __ldg(p.items + 4 * idx + 1);
+        row = d0.z;
+        chunk = d1.w;
+        slot = d1.x * p.n_heads + head;
+        if (row < 0 || d1.x < 0 || chunk < 0 || d1.z < 0 || (p.n_slots > 0 && slot >= p.n_slots) ||
+            (p.n_seqs > 0 && row >= p.n_seqs) || (p.max_chunks > 0 && chunk >= p.max_chunks)) {
+            if (g == 0) report(p.status, STATUS_BAD_WORK_LIST);  // skipped
+            slot = -1;
+        } else {
+            nt = min(FAST_C, d1.z + ((d1.y & ITEM_FLAG_TAIL) ? p.delta_tokens : 0));
         }
     }
+    const int nt_warp = max(nt, __shfl_xor_sync(0xffffffffu, nt, 16));
     const uint8_t* ktile = p.pool + ((size_t)chunk * p.n_heads + head) * (size_t)FAST_STAGE_BYTES;
     const uint8_t* vtile = ktile + FAST_TILE_BYTES;
-
-    // Scores in log2 units.  Step i of round r: the lower half-warp takes token 32 r + i, the upper one
-    // token 32 r + 16 + i (two coalesced rows per load); after the 16-lane sum the lane whose number is
-    // the token's (mod 32) keeps the score, so lane j ends up owning tokens j and j + 32.
-    float sc[2] = {NEG_BIG, NEG_BIG};
+    uint4 qraw = make_uint4(0u, 0u, 0u, 0u);
+    if (nt > 0)
+        qraw = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.q) + ((size_t)row * p.n_heads + head) * FAST_D + 8 * g));
+    float qf[8];
+    float m = NEG_BIG, l = 0.f;
+    float o[8];
 #pragma unroll
-    for (int r = 0; r < 2; r++) {
-        if (32 * r < nt) {
+    for (int e = 0; e < 8; e++) o[e] = 0.f;
+    for (int t0 = 0; t0 < nt_warp; t0 += SHORT_BLOCK) {
+        uint4 kr[SHORT_BLOCK], vr[SHORT_BLOCK];
 #pragma unroll
-            for (int i = 0; i < 16; i++) {
-                const int t = 32 * r + 16 * half + i;
-                float acc = 0.f;
-                if (t < nt) {
-                    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(ktile + tile_off(t, g16)));
-                    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+        for (int i = 0; i < SHORT_BLOCK; i++) {
+            kr[i] = make_uint4(0u, 0u, 0u, 0u);
+            vr[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (t0 + i < nt) {
+                kr[i] = __ldg(reinterpret_cast<const uint4*>(ktile + tile_off(t0 + i, g)));
+                vr[i] = __ldg(reinterpret_cast<const uint4*>(vtile + tile_off(t0 + i, g)));
+            }
+        }
+        if (t0 == 0) {  // the query granule of this lane, pre-scaled to log2 units
+            const __half2* h = reinterpret_cast<const __half2*>(&qraw);
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const float2 f = __half22float2(h[k]);
+                qf[2 * k] = f.x * p.scale_log2;
+                qf[2 * k + 1] = f.y * p.scale_log2;
+            }
+        }
+        const int n_here = min(SHORT_BLOCK, nt_warp - t0);  // warp-uniform: rounds are cut short together
+        float sc[SHORT_BLOCK];
+        float mx = NEG_BIG;
+#pragma unroll
+        for (int i = 0; i < SHORT_BLOCK; i++) {
+            sc[i] = NEG_BIG;
+            if (i < n_here) {
+                const __half2* h = reinterpret_cast<const __half2*>(&kr[i]);
+                float a = 0.f;
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const float2 f = __half22float2(h[k]);
+                    a = fmaf(qf[2 * k], f.x, a);
+                    a = fmaf(qf[2 * k + 1], f.y, a);
+                }
+#pragma unroll
+                for (int off = 8; off >= 1; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+                if (t0 + i < nt) sc[i] = a;
+                mx = fmaxf(mx, sc[i]);
+            }
+        }
+        if (t0 < nt) {  // this half-warp's item still has tokens in the round
+            const float mn = fmaxf(m, mx);
+            const float alpha = fast_exp2(m - mn);
+            m = mn;
+            l *= alpha;
+#pragma unroll
+            for (int e = 0; e < 8; e++) o[e] *= alpha;
+#pragma unroll
+            for (int i = 0; i < SHORT_BLOCK; i++) {
+                if (i < n_here) {
+                    const float pw = t0 + i < nt ? fast_exp2(sc[i] - mn) : 0.f;
+                    l += pw;
+                    const __half2* h = reinterpret_cast<const __half2*>(&vr[i]);
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
                         const float2 f = __half22float2(h[k]);
-                        acc = fmaf(qf[2 * k], f.x, acc);
-                        acc = fmaf(qf[2 * k + 1], f.y, acc);
+                        o[2 * k] = fmaf(pw, f.x, o[2 * k]);
+                        o[2 * k + 1] = fmaf(pw, f.y, o[2 * k + 1]);
                     }
                 }
-#pragma unroll
-                for (int off = 8; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-                if (g16 == i && t < nt) sc[r] = acc;
             }
         }
     }
-    float m = fmaxf(sc[0], sc[1]);
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
-    const float p0 = lane < nt ? fast_exp2(sc[0] - m) : 0.f;
-    const float p1 = lane + 32 < nt ? fast_exp2(sc[1] - m) : 0.f;
-    float l = p0 + p1;
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
-
-    // O = P V: this lane's four output elements are 8 bytes of granule lane / 2 of every V row
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    const int gran = lane >> 1, sub = (lane & 1) << 3;
-    auto add_row = [&](int t, float pw) {
-        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(vtile + tile_off(t, gran) + sub));
-        const __half2* h = reinterpret_cast<const __half2*>(&raw);
-        const float2 a = __half22float2(h[0]), b = __half22float2(h[1]);
-        acc.x = fmaf(pw, a.x, acc.x);
-        acc.y = fmaf(pw, a.y, acc.y);
-        acc.z = fmaf(pw, b.x, acc.z);
-        acc.w = fmaf(pw, b.y, acc.w);
-    };
-    const int n_lo = min(nt, 32);
-#pragma unroll 4
-    for (int t = 0; t < n_lo; t++) add_row(t, __shfl_sync(0xffffffffu, p0, t));
-#pragma unroll 4
-    for (int t = 32; t < nt; t++) add_row(t, __shfl_sync(0xffffffffu, p1, t - 32));
-    *reinterpret_cast<float4*>(p.part_o + (size_t)slot * FAST_D + 4 * lane) = acc;
-    if (lane == 0) p.part_ml[slot] = make_float2(m, l);
+    if (slot < 0) return;
+    if (nt > 0) {
+        float4* dst = reinterpret_cast<float4*>(p.part_o + (size_t)slot * FAST_D + 8 * g);
+        dst[0] = make_float4(o[0], o[1], o[2], o[3]);
+        dst[1] = make_float4(o[4], o[5], o[6], o[7]);
+    }
+    if (g == 0) p.part_ml[slot] = make_float2(nt > 0 ? m : NEG_BIG, l);  // an empty reserved tail: (none, 0)
 }
 
 // The un-normalised combination of the partials merge_slots[b .. e) by one warp: on return mm is their
@@ -1003,13 +1021,118 @@ __device__ __forceinline__ void store_row(const MergeParams& p, int pair, int la
     if (p.n_peers == 0) {
         *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.out) + (size_t)pair * FAST_D + 4 * lane) = packed;
     } else {
-        // head-sharded: the row goes into every rank's full-width output (plain stores to peer memory)
+        // head-sharded: the row goes into every rank's full-width output
         const int row = pair / p.n_heads;
         const int head = pair - row * p.n_heads;
         const size_t off = ((size_t)row * p.total_heads + p.head_offset + head) * FAST_D + 4 * lane;
+        if (p.mc_out) {
+            // one store to the multicast address: the switch replicates it into every rank's buffer
+            asm volatile("multimem.st.weak.global.v2.f16x2 [%0], {%1, %2};" ::"l"(reinterpret_cast<__half*>(p.mc_out) + off),
+                         "r"(packed.x), "r"(packed.y)
+                         : "memory");
+        } else {
+            // plain stores to peer memory over NVLink
+#pragma unroll
+            for (int i = 0; i < MERGE_MAX_PEERS; i++)
+                if (i < p.n_peers) *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.peer_out[i]) + off) = packed;
+        }
+    }
+}
+
+// Large batches whose rows have at most four pieces each (one long shared prefix plus a short private tail, the
+// usual serving shape): eight lanes per (row, head), each owning 16 output elements, every piece's (max, sum)
+// and O segment requested at once, so the whole combination is one round trip after the list lookups and a warp
+// finishes four pairs instead of one.
+constexpr int SMALL_MAX_LIST = 4;
+__global__ void __launch_bounds__(128) attn_merge_small_kernel(const MergeParams p) {
+    const int pair = blockIdx.x * 16 + (threadIdx.x >> 3);
+    const int sub = threadIdx.x & 7;
+    int slot[SMALL_MAX_LIST];
+#pragma unroll
+    for (int u = 0; u < SMALL_MAX_LIST; u++) slot[u] = -1;
+    if (pair < p.n_pairs) {
+        const int row = pair / p.n_heads, head = pair - row * p.n_heads;
+        int b = __ldg(p.merge_off + row), e = __ldg(p.merge_off + row + 1);
+        checked_bounds(p, b, e);
+#pragma unroll
+        for (int u = 0; u < SMALL_MAX_LIST; u++)
+            if (b + u < e) slot[u] = checked_slot(p, __ldg(p.merge_slots + b + u), head);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (pair >= p.n_pairs) return;
+    float2 ml[SMALL_MAX_LIST];
+    float4 v[SMALL_MAX_LIST][4];
+#pragma unroll
+    for (int u = 0; u < SMALL_MAX_LIST; u++) {
+        ml[u] = make_float2(NEG_BIG, 0.f);
+#pragma unroll
+        for (int k = 0; k < 4; k++) v[u][k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (slot[u] >= 0) {
+            ml[u] = p.part_ml[slot[u]];
+            const float4* src = reinterpret_cast<const float4*>(p.part_o + (size_t)slot[u] * FAST_D + 16 * sub);
+#pragma unroll
+            for (int k = 0; k < 4; k++) v[u][k] = src[k];
+        }
+    }
+    float mm = NEG_BIG;
+#pragma unroll
+    for (int u = 0; u < SMALL_MAX_LIST; u++)
+        if (ml[u].y > 0.f) mm = fmaxf(mm, ml[u].x);
+    float ll = 0.f;
+    float4 o[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) o[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int u = 0; u < SMALL_MAX_LIST; u++) {
+        if (ml[u].y > 0.f) {  // a piece without tokens has no O row: its slot holds stale data
+            const float w = fast_exp2(ml[u].x - mm);
+            ll = fmaf(w, ml[u].y, ll);
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                o[k].x = fmaf(w, v[u][k].x, o[k].x);
+                o[k].y = fmaf(w, v[u][k].y, o[k].y);
+                o[k].z = fmaf(w, v[u][k].z, o[k].z);
+                o[k].w = fmaf(w, v[u][k].w, o[k].w);
+            }
+        }
+    }
+    const float inv = ll > 0.f ? 1.f / ll : 0.f;  // a row with no token yields zeros
+    uint4 packed[2];
+    {
+        uint32_t h[8];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            h[2 * k] = pack_half2(o[k].x * inv, o[k].y * inv);
+            h[2 * k + 1] = pack_half2(o[k].z * inv, o[k].w * inv);
+        }
+        packed[0] = make_uint4(h[0], h[1], h[2], h[3]);
+        packed[1] = make_uint4(h[4], h[5], h[6], h[7]);
+    }
+    if (p.n_peers == 0) {
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.out) + (size_t)pair * FAST_D + 16 * sub);
+        dst[0] = packed[0];
+        dst[1] = packed[1];
+    } else {
+        const int row = pair / p.n_heads, head = pair - row * p.n_heads;
+        const size_t off = ((size_t)row * p.total_heads + p.head_offset + head) * FAST_D + 16 * sub;
+        if (p.mc_out) {
+            __half* dst = reinterpret_cast<__half*>(p.mc_out) + off;
+            asm volatile("multimem.st.weak.global.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(packed[0].x),
+                         "r"(packed[0].y), "r"(packed[0].z), "r"(packed[0].w)
+                         : "memory");
+            asm volatile("multimem.st.weak.global.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst + 8), "r"(packed[1].x),
+                         "r"(packed[1].y), "r"(packed[1].z), "r"(packed[1].w)
+                         : "memory");
+            return;
+        }
 #pragma unroll
         for (int i = 0; i < MERGE_MAX_PEERS; i++)
-            if (i < p.n_peers) *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.peer_out[i]) + off) = packed;
+            if (i < p.n_peers) {
+                uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.peer_out[i]) + off);
+                dst[0] = packed[0];
+                dst[1] = packed[1];
+            }
     }
 }
 
@@ -1086,7 +1209,35 @@ __global__ void __launch_bounds__(128, 3) attn_merge_wide_kernel(const MergePara
     store_row(p, pair, lane, out, sum > 0.f ? 1.f / sum : 0.f);
 }
 
+// ---- barrier among the ranks of a node ------------------------------------------------------------------------
+// Lane i tells rank i that this rank has arrived (a release store of the epoch into word `rank` of rank i's flag
+// array, over NVLink), then waits -- for a bounded time -- until rank i's arrival shows in this rank's own array.
+// The kernel before it in the stream has completed, so the rows it stored into the peers are ordered before the
+// release.  A peer that never arrives costs the time limit and a status code, not a hung GPU.
+__global__ void peer_barrier_kernel(const PeerBarrierParams p) {
+    const int i = threadIdx.x;
+    if (i >= p.n_peers) return;
+    uint32_t* theirs = p.flags[i] + p.rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(p.epoch) : "memory");
+    const uint32_t* mine = p.flags[p.rank] + i;
+    const unsigned long long t0 = global_timer_ns();
+    while (true) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+        if ((int32_t)(v - p.epoch) >= 0) break;
+        if ((long long)(global_timer_ns() - t0) > p.timeout_ns) {
+            if (p.status) atomicCAS(p.status, STATUS_OK, STATUS_PEER_WAIT_TIMEOUT);
+            break;
+        }
+    }
+}
+
 }  // namespace
+
+cudaError_t launch_peer_barrier(const PeerBarrierParams& p, cudaStream_t stream) {
+    peer_barrier_kernel<<<1, 32, 0, stream>>>(p);
+    return cudaGetLastError();
+}
 
 cudaError_t configure_fast_kernels() {
     // opt in to the large dynamic shared-memory carve-out, once per device (per context creation)
@@ -1123,7 +1274,7 @@ cudaError_t launch_attn_short_tails(const PartialParams& p, cudaStream_t stream,
     if (n <= 0) return cudaSuccess;
     static const bool pdl_disabled = std::getenv("CA_DISABLE_PDL") != nullptr;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((n + SHORT_WARPS - 1) / SHORT_WARPS);
+    cfg.gridDim = dim3((n + SHORT_ITEMS_PER_CTA - 1) / SHORT_ITEMS_PER_CTA);
     cfg.blockDim = dim3(SHORT_WARPS * 32);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = stream;
@@ -1162,8 +1313,12 @@ cudaError_t launch_attn_merge(const MergeParams& p, cudaStream_t stream, bool de
     // long lists under few rows: a CTA per row instead of a warp per row (a couple of waves at most)
     const bool wide = p.n_pairs <= 8 * sms && p.n_merge_entries * (long long)p.n_heads > 48LL * p.n_pairs;
     if (wide) cfg.gridDim = dim3(p.n_pairs);
+    // many rows of at most four pieces each: eight lanes per row instead of a warp
+    const bool small = !wide && p.max_list > 0 && p.max_list <= SMALL_MAX_LIST && grid > 3 * sms;
+    if (small) cfg.gridDim = dim3((p.n_pairs + 15) / 16);
     auto launch = [&]() {
         if (wide) return cudaLaunchKernelEx(&cfg, attn_merge_wide_kernel, p);
+        if (small) return cudaLaunchKernelEx(&cfg, attn_merge_small_kernel, p);
         if (grid <= 3 * sms) return cudaLaunchKernelEx(&cfg, attn_merge_kernel<16, 3>, p);
         if (grid <= 5 * sms) return cudaLaunchKernelEx(&cfg, attn_merge_kernel<8, 5>, p);
         return cudaLaunchKernelEx(&cfg, attn_merge_kernel<0, 7>, p);

@@ -48,6 +48,8 @@ constexpr int W_SMEM_BYTES = W_SMEM_BAR + W_NUM_BARS * 8 + 24;
 constexpr int W_THREADS = 192;
 constexpr int W_TMEM_COLS = 256;                       // O: 0..127, S buffers: 128..191 and 192..255
 constexpr int W_COL_S = 128;
+constexpr int W_STAGE_PITCH = FAST_D + 4;               // floats per staged output row (528 bytes: conflict-free 128-bit stores)
+static_assert(W_ROWS * W_STAGE_PITCH * 4 <= W_SMEM_BAR, "the output staging must fit under the barriers");
 constexpr float W_NEG_BIG = -1.0e30f;
 constexpr float W_RESCALE_STEP = 8.f;                  // log2 units a row's maximum may drift above the scale in use
 static_assert(2 * (W_SMEM_BYTES + 1024) <= 233472, "two CTAs do not fit in one SM's shared memory");
@@ -69,6 +71,8 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
     const uint32_t q_ready = o_done + 8;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + W_SMEM_BAR + W_NUM_BARS * 8);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    unsigned long long* tr = p.trace ? p.trace + 8 * blockIdx.x : nullptr;
+    if (tr && threadIdx.x == 0) tr[0] = global_timer_ns();
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < W_SLOTS; i++) {
@@ -107,6 +111,7 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
     __syncthreads();   // barriers initialised, TMEM address published
     tc_fence_after_thread_sync();
     const uint32_t tmem_base = *tmem_slot;
+    if (tr && threadIdx.x == 0) tr[1] = global_timer_ns();
     if (!ok && threadIdx.x == 0) report(p.status, STATUS_BAD_WORK_LIST);  // skipped: its partial rows keep what they held
 
     if (ok) {
@@ -226,6 +231,7 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
                     break;
                 }
                 tc_fence_after_thread_sync();
+                if (tr && j == 0 && threadIdx.x == 0) tr[2] = global_timer_ns();
                 uint32_t s0[32], s1[32];
                 tmem_ld32(lane_addr + W_COL_S + b * FAST_C, s0);
                 tmem_ld32(lane_addr + W_COL_S + b * FAST_C + 32, s1);
@@ -286,28 +292,40 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
                 tc_fence_before_thread_sync();
                 mbar_arrive(p_full + 8 * b);
             }
+            if (tr && threadIdx.x == 0) tr[3] = global_timer_ns();
             if (live) {
                 live = mbar_wait_bounded(o_done, (n_tiles - 1) & 1, p.wait_limit);
                 live = __all_sync(0xffffffffu, live);
                 if (!live && lane == 0) report(p.status, STATUS_FULL_WAIT_TIMEOUT);
             }
+            if (tr && threadIdx.x == 0) tr[4] = global_timer_ns();
             if (live) {
                 tc_fence_after_thread_sync();
-                const size_t slot = (size_t)(slot_base + r) * p.n_heads + head;  // row r of this head
-                float* dst = p.part_o + slot * FAST_D;
+                // O leaves through shared memory (the staged queries and the ring are free now: every MMA has
+                // completed): a thread holds one ROW, but a row must reach global memory as whole 512-byte lines.
+                // Each warp stages and writes its own 32 rows, so a warp-level barrier is all the ordering it needs.
+                float* stage = reinterpret_cast<float*>(smem);
 #pragma unroll
                 for (int c = 0; c < 4; c++) {
                     uint32_t o[32];
                     tmem_ld32(lane_addr + c * 32, o);
                     tmem_wait_ld();
-                    if (active) {
 #pragma unroll
-                        for (int i = 0; i < 8; i++)
-                            *reinterpret_cast<uint4*>(dst + c * 32 + 4 * i) = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
-                    }
+                    for (int i = 0; i < 8; i++)
+                        *reinterpret_cast<uint4*>(stage + r * W_STAGE_PITCH + c * 32 + 4 * i) =
+                            make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
                 }
-                if (active) p.part_ml[slot] = make_float2(m_used, l);
+                __syncwarp();
+                const int rows_here = min(32, n_rows - warp * 32);   // <= 0 for a warp past the item's rows
+                for (int rr = 0; rr < rows_here; rr++) {
+                    const int row = warp * 32 + rr;
+                    const size_t slot = (size_t)(slot_base + row) * p.n_heads + head;  // row `row` of this head
+                    const uint4 v = *reinterpret_cast<const uint4*>(stage + row * W_STAGE_PITCH + 4 * lane);
+                    *reinterpret_cast<uint4*>(p.part_o + slot * FAST_D + 4 * lane) = v;
+                }
+                if (active) p.part_ml[(size_t)(slot_base + r) * p.n_heads + head] = make_float2(m_used, l);
             }
+            if (tr && threadIdx.x == 0) tr[5] = global_timer_ns();
         }
     }
     // ---- common exit of every path: nobody touches TMEM after this barrier, then the allocating warp frees it
@@ -316,6 +334,7 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
     if (warp == 5) {
         tc_fence_after_thread_sync();
         tmem_dealloc(tmem_base, W_TMEM_COLS);
+        if (tr && lane == 0) tr[6] = global_timer_ns();
     }
 }
 

@@ -77,6 +77,8 @@ struct WideParams {
     int* status;
     int n_slots = 0, n_seqs = 0, max_chunks = 0;  // bounds the work list is checked against (0: unchecked)
     long long wait_limit = DEFAULT_WAIT_LIMIT_CYCLES;
+    unsigned long long* trace = nullptr;  // optional [n_ctas][8] ns timestamps: entry, set-up done, first S ready,
+                                          // last P written, O complete, partial rows stored, exit
 };
 cudaError_t launch_attn_wide(const WideParams& p, cudaStream_t stream, bool dependent_launch = false);
 cudaError_t configure_wide_kernel();  // once per device before the first launch
@@ -90,6 +92,7 @@ struct MergeParams {
     void* out;                   // fp16 [n_rows, n_heads, 128]; unused when n_peers > 0
     int n_pairs;                 // n_rows * n_heads
     long long n_merge_entries = 0; // length of merge_slots
+    int max_list = 0;            // longest list of a row (0: unknown); picks the kernel instance
     // Head-sharded output written straight into every rank's full-width buffer (peer memory over
     // NVLink): row s, local head h goes to peer_out[i] + ((s * total_heads) + head_offset + h) * 128.
     int n_heads = 0;             // local heads
@@ -97,10 +100,25 @@ struct MergeParams {
     int total_heads = 0;
     int head_offset = 0;
     void* peer_out[MERGE_MAX_PEERS] = {};
+    void* mc_out = nullptr;      // optional multicast address of the same buffer on all ranks (NVLink SHARP): one
+                                 // multimem.st per row segment then replaces the n_peers unicast stores
     int n_slots = 0;             // partial rows behind part_o / part_ml; a list entry outside [0, n_slots) is skipped
     int* status = nullptr;       // and STATUS_BAD_WORK_LIST recorded here (0 / null: unchecked)
 };
 cudaError_t launch_attn_merge(const MergeParams& p, cudaStream_t stream, bool dependent_launch);
+
+constexpr int STATUS_PEER_WAIT_TIMEOUT = 6;   // a peer did not reach the barrier within the time allowed
+// One-phase barrier among the ranks of a node over flag words in each other's memory: rank r stores `epoch` into
+// word r of every peer's flag array, then waits until every word of its own array has reached `epoch`.
+struct PeerBarrierParams {
+    uint32_t* flags[MERGE_MAX_PEERS];  // flags[i]: rank i's array of n_peers words (this rank's own included)
+    int n_peers;
+    int rank;
+    uint32_t epoch;                    // grows by one per barrier; the words only ever grow
+    long long timeout_ns;              // of the GPU's global timer
+    int* status;                       // may be null
+};
+cudaError_t launch_peer_barrier(const PeerBarrierParams& p, cudaStream_t stream);
 
 // ---- generic path: any d_head <= 256, any chunk size, fp16 or fp32 ----------------------------------
 struct GenericParams {

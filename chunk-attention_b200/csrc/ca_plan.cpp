@@ -325,7 +325,11 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
         int32_t* off = plan.merge_off.data() + (size_t)it.row_begin + 1;
         for (int r = 0; r < it.n_rows; r++, off++) *off += splits;
     }
-    for (size_t i = 1; i < plan.merge_off.size(); i++) plan.merge_off[i] += plan.merge_off[i - 1];
+    plan.max_merge_len = 0;
+    for (size_t i = 1; i < plan.merge_off.size(); i++) {
+        plan.max_merge_len = std::max(plan.max_merge_len, (int)plan.merge_off[i]);
+        plan.merge_off[i] += plan.merge_off[i - 1];
+    }
     plan.merge_slots.resize(plan.merge_off.back());
     {
         std::vector<int32_t> cursor(plan.merge_off.begin(), plan.merge_off.end() - 1);

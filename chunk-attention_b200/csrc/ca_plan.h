@@ -68,6 +68,7 @@ struct Plan {
     int n_items_wide = 0;                 // how many at the END of the list are wide items for the tcgen05 kernel
     std::vector<int32_t> wide_chunks;     // chunk lists of the wide items
     std::vector<int32_t> merge_off, merge_slots;
+    int max_merge_len = 0;                // pieces of the row that has most
     std::vector<int32_t> path_off, path_chunks, path_tokens;
     std::vector<int32_t> tail_chunk, tail_tokens;
     ca_plan_stats stats{};

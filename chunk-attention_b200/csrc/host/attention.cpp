@@ -1,5 +1,7 @@
 #include "attention.h"
 
+#include <chrono>
+
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 
@@ -206,9 +208,17 @@ std::vector<Chunk*> Attention::reserve() {
     return fresh;
 }
 
+namespace {
+inline int64_t now_ns() {
+    return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+}  // namespace
+
 void Attention::refresh_kernel_context(bool force) {
     if (!force && valid_) return;
+    const int64_t t0 = now_ns();
     std::vector<ca_chunk_info> infos = tree_->get_chunks();
+    const int64_t t1 = now_ns();
     c10::cuda::CUDAGuard guard(options_.device());
     SharedPlan& sp = *shared_plan_;
     const bool same = sp.plan != nullptr && sp.n_seqs == tree_->n_seqs() && sp.infos.size() == infos.size() &&
@@ -223,8 +233,14 @@ void Attention::refresh_kernel_context(bool force) {
     } else {
         sp.reuses++;
     }
+    const int64_t t2 = now_ns();
     check_rc(ca_refresh_from_plan(ctx_, sp.plan, stream()), "refresh_kernel_context");
     valid_ = true;
+    const int64_t t3 = now_ns();
+    host_times_.refreshes++;
+    host_times_.walk_ns += t1 - t0;
+    host_times_.plan_ns += t2 - t1;
+    host_times_.upload_ns += t3 - t2;
 }
 
 std::vector<Chunk*> Attention::append_token(const std::vector<int>& tokens, torch::Tensor k, torch::Tensor v, bool) {
@@ -300,7 +316,7 @@ torch::Tensor Attention::forward_host(torch::Tensor q, c10::optional<torch::Tens
 }
 
 void Attention::forward_to_peers(torch::Tensor q, const std::vector<int64_t>& peer_out_ptrs, int total_heads,
-                                 int head_offset) {
+                                 int head_offset, int64_t multicast_ptr) {
     if (!q.is_contiguous()) throw std::runtime_error("q is not contiguous");
     if (q.dim() != 3 || q.size(0) != (int64_t)tree_->n_seqs() || q.size(1) != n_heads_ || q.size(2) != d_head_ ||
         q.device() != options_.device() || q.scalar_type() != c10::typeMetaToScalarType(options_.dtype()))
@@ -309,8 +325,8 @@ void Attention::forward_to_peers(torch::Tensor q, const std::vector<int64_t>& pe
     for (int64_t p : peer_out_ptrs) ptrs.push_back(reinterpret_cast<void*>(p));
     c10::cuda::CUDAGuard guard(options_.device());
     refresh_kernel_context(false);
-    check_rc(ca_attention_to_peers(ctx_, q.data_ptr(), ptrs.data(), (int)ptrs.size(), total_heads, head_offset,
-                                   (int)q.size(0), stream()),
+    check_rc(ca_attention_to_peers(ctx_, q.data_ptr(), ptrs.data(), (int)ptrs.size(), reinterpret_cast<void*>(multicast_ptr),
+                                   total_heads, head_offset, (int)q.size(0), stream()),
              "forward_to_peers");
 }
 

@@ -57,7 +57,10 @@ class Attention {
     torch::Tensor forward_host(torch::Tensor q, c10::optional<torch::Tensor> out, int partition = 0);
     // head-sharded forward: rows are written into every rank's full-width output buffer (device
     // addresses this GPU can reach), this cache's heads landing at head_offset of total_heads
-    void forward_to_peers(torch::Tensor q, const std::vector<int64_t>& peer_out_ptrs, int total_heads, int head_offset);
+    // multicast_ptr != 0: a multicast address mapping the same buffer on every rank; rows are then written with one
+    // multimem.st each instead of one store per rank
+    void forward_to_peers(torch::Tensor q, const std::vector<int64_t>& peer_out_ptrs, int total_heads, int head_offset,
+                          int64_t multicast_ptr = 0);
 
     Chunk* get_trie() { return tree_->root(); }
     std::vector<Chunk*> tails() { return tree_->tails(); }
@@ -70,6 +73,10 @@ class Attention {
     int device_status();
     // (plans built, plans reused) by this cache and the caches it shares its work lists with
     std::pair<int64_t, int64_t> plan_sharing() const { return {shared_plan_->builds, shared_plan_->reuses}; }
+    // host time spent bringing the work lists up to date since the object was made: the tree walk (get_chunks),
+    // planning (or finding the shared plan current) and the upload, in nanoseconds, and how many refreshes
+    struct HostTimes { int64_t refreshes = 0, walk_ns = 0, plan_ns = 0, upload_ns = 0; };
+    HostTimes host_times() const { return host_times_; }
     // the two launches of forward(), separately (per-kernel timing)
     void attn_partials(torch::Tensor q, int phases);
     void attn_merge(torch::Tensor out);
@@ -89,6 +96,7 @@ class Attention {
     std::unique_ptr<PrefixTree> tree_;
     ca_context* ctx_ = nullptr;
     bool valid_ = false;
+    HostTimes host_times_;
 
     // The work list of the current tree, shared by the caches made from one another with
     // Attention(other) (a model's layers): whoever refreshes first after a tree change plans, the

@@ -62,6 +62,9 @@ PYBIND11_MODULE(chunk_attn_c, m) {
                // the default device is wherever a fresh tensor lands; asking Python (not libtorch)
                // honours `with torch.device(...)` and torch.set_default_device, which live there
                if (device.is_none()) device = py::module_::import("torch").attr("empty")(0).attr("device");
+               // a device given by name ("cuda:0"), as the reference's llama_hf passes its config.torch_device
+               if (py::isinstance<py::str>(device)) device = py::module_::import("torch").attr("device")(device);
+               if (py::isinstance<py::str>(dtype)) dtype = py::module_::import("torch").attr(dtype);
                torch::Device device_c = torch::python::detail::py_object_to_device(device);
                return new Attention(n_heads, d_head, chunk_size, memory_mb, share_prefix, tpp_threshold, dtype_c,
                                     device_c);
@@ -91,11 +94,20 @@ PYBIND11_MODULE(chunk_attn_c, m) {
       .def("set_option", &Attention::set_option, py::arg("option"), py::arg("value"))
       .def("device_status", &Attention::device_status)
       .def("plan_sharing", &Attention::plan_sharing)
+      .def("host_times", [](Attention& a) {
+          const auto t = a.host_times();
+          py::dict d;
+          d["refreshes"] = t.refreshes;
+          d["walk_us"] = t.walk_ns * 1e-3;
+          d["plan_us"] = t.plan_ns * 1e-3;
+          d["upload_us"] = t.upload_ns * 1e-3;
+          return d;
+      })
       // blocks until the result is in host memory: other Python threads run meanwhile
       .def("forward_host", &Attention::forward_host, py::arg("q"), py::arg("out") = py::none(), py::arg("partition") = 0,
            py::call_guard<py::gil_scoped_release>())
       .def("forward_to_peers", &Attention::forward_to_peers, py::arg("q"), py::arg("peer_out_ptrs"),
-           py::arg("total_heads"), py::arg("head_offset"))
+           py::arg("total_heads"), py::arg("head_offset"), py::arg("multicast_ptr") = 0)
       .def("attn_partials", &Attention::attn_partials, py::arg("q"), py::arg("phases") = 3)
       .def("attn_merge", &Attention::attn_merge, py::arg("out"));
 

@@ -149,10 +149,23 @@ CA_API int ca_attention_host(ca_context* ctx, const void* q_host, void* out_host
  * each rank's full-width buffer peer_out[i], fp16 [n_seqs, total_heads, d_head], with plain stores
  * to peer memory over NVLink — compute and gather in one kernel, no collective library call.
  * peer_out is a HOST array of n_peers (<= 8) device pointers that this GPU can address (the rank's
- * own buffer included); the caller orders the ranks before anyone reads (a barrier on the stream).
+ * own buffer included), 16-byte aligned; the caller orders the ranks before anyone reads (ca_peer_barrier on the
+ * stream).  multicast_out, when not NULL, is a multicast address that maps the same buffer on every rank
+ * (NVLink SHARP / NVLS, e.g. the multicast pointer of a torch symmetric-memory allocation): every row segment is
+ * then written with ONE multimem.st that the switch replicates, instead of n_peers unicast stores.
  * No counterpart in the reference, which is single-device. */
 CA_API int ca_attention_to_peers(ca_context* ctx, const void* q, void* const* peer_out, int n_peers,
-                                 int total_heads, int head_offset, int n_seqs, ca_stream stream);
+                                 void* multicast_out, int total_heads, int head_offset, int n_seqs, ca_stream stream);
+
+/* Barrier among the n_peers ranks of a node, on the stream: flag_arrays is a HOST array of device pointers,
+ * flag_arrays[i] = rank i's array of n_peers 32-bit words in memory every rank can address (zero at the start).
+ * Rank `rank` stores `epoch` (1, 2, 3, ... one more per barrier) into word `rank` of every array and waits until
+ * all words of its own array have reached it.  The wait is bounded: after timeout_ns a rank gives up, stores 6
+ * into *status (optional device word) and the kernel returns -- a peer that never arrives costs the time limit,
+ * never a hung GPU.  Replaces the device-side barrier of the collective library for the fused gather; no
+ * counterpart in the reference. */
+CA_API int ca_peer_barrier(void* const* flag_arrays, int n_peers, int rank, uint32_t epoch, int64_t timeout_ns,
+                           int32_t* status, ca_stream stream);
 
 /* The two halves of ca_attention, separately launchable (profiling, tests):
  * ca_attn_partials = chunk-first over shared runs + sequence-first over private tails, emitting

@@ -161,3 +161,19 @@ def test_many_short_tails_take_the_warp_per_item_kernel():
         m2.add(None, 0, rnd.randint(1, 64))
     m2.check()
     assert m2.attn.plan_stats()["n_items_short"] >= 300 * 4  # (a row of exactly 64 tokens has a full chunk + an empty tail)
+
+
+@pytest.mark.parametrize("wide", [0, 2])
+def test_large_batch_of_short_lists_takes_the_eight_lane_merge(wide):
+    """600 rows over one 256-token prefix, a few private tokens each: 2400 (row, head) pairs of two to four pieces,
+    the shape the eight-lanes-per-pair merge kernel serves; appended tokens and a removed row on the way."""
+    m = Mirror(4, 21, memory_mb=1024, wide=wide)
+    rnd = random.Random(21)
+    m.add(None, 0, 256 + 2)
+    for _ in range(599):
+        m.add(0, 256, rnd.randint(1, 30))
+    m.check()
+    for step in range(3):
+        m.append_all()
+    m.remove(17)
+    m.check()
