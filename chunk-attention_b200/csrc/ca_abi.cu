@@ -95,6 +95,7 @@ struct ca_context {
     // what the launches need to know about the work list that is on the device
     struct {
         int n_seqs = 0, n_items = 0, n_items_cf = 0, n_items_short = 0, n_items_wide = 0, n_wide_chunks = 0, n_ctas = 1;
+        bool short_all_empty = false;  // the short tails were all empty at the refresh and their (max, sum) rows are zeroed
         int64_t n_merge_slots = 0;  // entries of merge_slots
         int max_merge_len = 0;
         bool split_phases = false;
@@ -117,6 +118,15 @@ struct ca_context {
     const int32_t *d_path_off = nullptr, *d_path_chunks = nullptr, *d_path_tokens = nullptr;
     const int32_t *d_tail_chunk = nullptr, *d_tail_tokens = nullptr;
     const int32_t* d_wide_chunks = nullptr;
+    // The per-row path lists are read by the any-geometry kernel only: a context of the tensor-core geometry
+    // builds and uploads them on the first partition = 2 request after a refresh, from this copy of the input.
+    bool paths_on_device = false;
+    ca::Plan path_plan;           // infos + path_* of the current tree
+    char* paths_host = nullptr;
+    char* paths_dev = nullptr;
+    size_t paths_cap = 0;
+    cudaEvent_t paths_done = nullptr;
+    bool paths_pending = false;
 
     // partial results of the current step (scratch)
     float* part_o = nullptr;
@@ -181,6 +191,7 @@ int ca_context_create(ca_context** out, int device, int n_heads, int d_head, int
     c->fast = (dtype == CA_DTYPE_F16 && d_head == ca::FAST_D && chunk_size == ca::FAST_C);
     c->num_sms = prop.multiProcessorCount;
     cudaError_t e = cudaEventCreateWithFlags(&c->upload_done, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->paths_done, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaMalloc(&c->status, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(c->status, 0, sizeof(int));
     if (e == cudaSuccess) e = cudaMalloc(&c->counters, 2 * sizeof(int));
@@ -202,6 +213,12 @@ void ca_context_destroy(ca_context* c) {
         if (c->upload_pending) cudaEventSynchronize(c->upload_done);
         cudaEventDestroy(c->upload_done);
     }
+    if (c->paths_done) {
+        if (c->paths_pending) cudaEventSynchronize(c->paths_done);
+        cudaEventDestroy(c->paths_done);
+    }
+    if (c->paths_host) cudaFreeHost(c->paths_host);
+    if (c->paths_dev) cudaFree(c->paths_dev);
     if (c->host_blob) cudaFreeHost(c->host_blob);
     if (c->dev_blob) cudaFree(c->dev_blob);
     if (c->part_o) cudaFree(c->part_o);
@@ -267,7 +284,7 @@ int ca_refresh_kernel_context(ca_context* c, const ca_chunk_info* infos, int n_i
     const int n_ctas = c->opt_ctas > 0 ? c->opt_ctas : c->num_sms * ca::FAST_CTAS_PER_SM;
     std::string err = ca::build_plan(c->plan, infos, n_infos, n_seqs, c->geo.n_heads, c->geo.chunk_size,
                                      c->tpp_threshold, n_ctas, c->max_chunks, c->opt_split, c->geo.d_head,
-                                     c->geo.esize, c->fast, c->opt_sf_tensor, c->opt_wide);
+                                     c->geo.esize, c->fast, c->opt_sf_tensor, c->opt_wide, /*want_paths=*/!c->fast);
     if (!err.empty()) return fail(CA_ERR_INVALID, "work list rejected: " + err);
     return upload_plan(c, c->plan, stream);
 }
@@ -280,7 +297,7 @@ int ca_plan_build_for_context(const ca_context* c, ca_plan** out, const ca_chunk
     const int n_ctas = c->opt_ctas > 0 ? c->opt_ctas : c->num_sms * ca::FAST_CTAS_PER_SM;
     std::string err = ca::build_plan(p->plan, infos, n_infos, n_seqs, c->geo.n_heads, c->geo.chunk_size, c->tpp_threshold,
                                      n_ctas, c->max_chunks, c->opt_split, c->geo.d_head, c->geo.esize, c->fast,
-                                     c->opt_sf_tensor, c->opt_wide);
+                                     c->opt_sf_tensor, c->opt_wide, /*want_paths=*/!c->fast);
     if (!err.empty()) {
         if (!*out) delete p;  // a caller-owned plan is left to the caller (its contents are unspecified now)
         return fail(CA_ERR_INVALID, "work list rejected: " + err);
@@ -317,9 +334,9 @@ static int upload_plan(ca_context* c, const ca::Plan& pl, cudaStream_t stream) {
         {pl.items.data(), pl.items.size() * sizeof(ca::PlanItem), 0},
         {pl.merge_off.data(), pl.merge_off.size() * 4, 0},
         {pl.merge_slots.data(), pl.merge_slots.size() * 4, 0},
-        {pl.path_off.data(), pl.path_off.size() * 4, 0},
-        {pl.path_chunks.data(), pl.path_chunks.size() * 4, 0},
-        {pl.path_tokens.data(), pl.path_tokens.size() * 4, 0},
+        {pl.path_off.data(), pl.has_paths ? pl.path_off.size() * 4 : 0, 0},
+        {pl.path_chunks.data(), pl.has_paths ? pl.path_chunks.size() * 4 : 0, 0},
+        {pl.path_tokens.data(), pl.has_paths ? pl.path_tokens.size() * 4 : 0, 0},
         {pl.tail_chunk.data(), pl.tail_chunk.size() * 4, 0},
         {pl.tail_tokens.data(), pl.tail_tokens.size() * 4, 0},
         {pl.wide_chunks.data(), pl.wide_chunks.size() * 4, 0},
@@ -364,6 +381,12 @@ static int upload_plan(ca_context* c, const ca::Plan& pl, cudaStream_t stream) {
     c->d_tail_chunk = reinterpret_cast<const int32_t*>(c->dev_blob + parts[6].off);
     c->d_tail_tokens = reinterpret_cast<const int32_t*>(c->dev_blob + parts[7].off);
     c->d_wide_chunks = reinterpret_cast<const int32_t*>(c->dev_blob + parts[8].off);
+    c->paths_on_device = pl.has_paths;
+    if (!pl.has_paths) {  // keep what a later partition = 2 request needs to build them
+        c->path_plan.infos = pl.infos;
+        c->path_plan.n_seqs = pl.n_seqs;
+        c->path_plan.has_paths = false;
+    }
 
     // partial-result scratch, grow-only
     const size_t slots = (size_t)pl.stats.n_slots;
@@ -377,6 +400,15 @@ static int upload_plan(ca_context* c, const ca::Plan& pl, cudaStream_t stream) {
         CA_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->part_o), cap * ca::FAST_D * sizeof(float)));
         CA_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->part_ml), cap * sizeof(float2)));
         c->part_cap = cap;
+    }
+    // Short tails that are all empty (freshly reserved ones under a fully shared prefix) have nothing to compute until a
+    // token is appended: their (max, sum) rows are zeroed here -- a sum of zero marks a piece without tokens -- and the
+    // launch of their kernel is left out while delta_tokens is 0.
+    c->meta.short_all_empty = false;
+    if (pl.n_items_short > 0 && pl.short_all_empty) {
+        CA_CUDA(cudaMemsetAsync(c->part_ml + (size_t)pl.short_slot_base * pl.n_heads, 0,
+                                (size_t)pl.n_items_short * pl.n_heads * sizeof(float2), stream));
+        c->meta.short_all_empty = true;
     }
     c->max_tail_tokens = 0;
     for (int32_t t : pl.tail_tokens) c->max_tail_tokens = t > c->max_tail_tokens ? t : c->max_tail_tokens;
@@ -480,7 +512,7 @@ int ca_attn_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_st
     // first (the short tails before the wide runs, whose set-up then overlaps them) so that the persistent kernel's
     // tail leads straight into the merge.
     const int n_items = c->meta.n_items - c->meta.n_items_short - c->meta.n_items_wide;
-    if (c->meta.n_items_short > 0 && (phases & 2)) {
+    if (c->meta.n_items_short > 0 && (phases & 2) && !(c->meta.short_all_empty && c->delta_tokens == 0)) {
         p.item_lo = n_items * H;
         p.item_hi = (n_items + c->meta.n_items_short) * H;
         CA_CUDA(ca::launch_attn_short_tails(p, stream, (c->opt_pdl & 2) != 0));
@@ -661,6 +693,42 @@ int ca_attention_to_peers(ca_context* c, const void* q, void* const* peer_out, i
     return CA_OK;
 }
 
+// The any-geometry kernel's path lists for a context that planned without them (one build and one upload per
+// tree change, on the first request that needs them).
+static int ensure_paths(ca_context* c, cudaStream_t stream) {
+    if (c->paths_on_device) return CA_OK;
+    ca::Plan& pp = c->path_plan;
+    ca::build_paths(pp);
+    const size_t b0 = align_up(pp.path_off.size() * 4, 256), b1 = align_up(pp.path_chunks.size() * 4, 256),
+                 b2 = align_up(pp.path_tokens.size() * 4, 256);
+    const size_t total = b0 + b1 + b2 + 256;
+    if (c->paths_pending) {
+        CA_CUDA(cudaEventSynchronize(c->paths_done));
+        c->paths_pending = false;
+    }
+    if (total > c->paths_cap) {
+        if (c->paths_host) CA_CUDA(cudaFreeHost(c->paths_host));
+        if (c->paths_dev) CA_CUDA(cudaFree(c->paths_dev));
+        c->paths_host = c->paths_dev = nullptr;
+        c->paths_cap = 0;
+        const size_t cap = align_up(total * 3 / 2, 4096);
+        CA_CUDA(cudaMallocHost(reinterpret_cast<void**>(&c->paths_host), cap));
+        CA_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->paths_dev), cap));
+        c->paths_cap = cap;
+    }
+    std::memcpy(c->paths_host, pp.path_off.data(), pp.path_off.size() * 4);
+    if (!pp.path_chunks.empty()) std::memcpy(c->paths_host + b0, pp.path_chunks.data(), pp.path_chunks.size() * 4);
+    if (!pp.path_tokens.empty()) std::memcpy(c->paths_host + b0 + b1, pp.path_tokens.data(), pp.path_tokens.size() * 4);
+    CA_CUDA(cudaMemcpyAsync(c->paths_dev, c->paths_host, total - 256, cudaMemcpyHostToDevice, stream));
+    CA_CUDA(cudaEventRecord(c->paths_done, stream));
+    c->paths_pending = true;
+    c->d_path_off = reinterpret_cast<const int32_t*>(c->paths_dev);
+    c->d_path_chunks = reinterpret_cast<const int32_t*>(c->paths_dev + b0);
+    c->d_path_tokens = reinterpret_cast<const int32_t*>(c->paths_dev + b0 + b1);
+    c->paths_on_device = true;
+    return CA_OK;
+}
+
 int ca_attention(ca_context* c, const void* q, void* out, int n_seqs, int partition, ca_stream stream_) {
     int rc = check_attention_args(c, q, n_seqs);
     if (rc != CA_OK) return rc;
@@ -674,6 +742,8 @@ int ca_attention(ca_context* c, const void* q, void* out, int n_seqs, int partit
     }
     DeviceGuard guard(c->device);
     if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    rc = ensure_paths(c, static_cast<cudaStream_t>(stream_));
+    if (rc != CA_OK) return rc;
     ca::GenericParams g;
     g.pool = c->pool;
     g.geo = c->geo;
@@ -841,6 +911,7 @@ int ca_context_stats(const ca_context* c, ca_plan_stats* out) {
     if (!c || !out) return fail(CA_ERR_INVALID, "null argument");
     if (!c->valid) return fail(CA_ERR_STATE, "work list is stale");
     *out = c->meta.stats;
+    if (c->meta.short_all_empty && c->delta_tokens == 0) out->kernels_per_step -= 1;  // nothing to do for empty tails
     return CA_OK;
 }
 
@@ -866,6 +937,8 @@ int ca_plan_build(ca_plan** out, const ca_chunk_info* infos, int n_infos, int n_
 int ca_plan_array(const ca_plan* plan, int which, const int32_t** data, int64_t* count) {
     if (!plan || !data || !count) return fail(CA_ERR_INVALID, "null argument");
     const ca::Plan& pl = plan->plan;
+    if (!pl.has_paths && (which == CA_PLAN_PATH_OFF || which == CA_PLAN_PATH_CHUNKS || which == CA_PLAN_PATH_TOKENS))
+        ca::build_paths(const_cast<ca::Plan&>(pl));   // built on first use
     const std::vector<int32_t>* v = nullptr;
     switch (which) {
         case CA_PLAN_ITEMS:

@@ -269,14 +269,19 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
                     for (int i = 0; i < 32; i++) pk[i] = 0u;
                 }
                 tmem_st32(lane_addr + W_COL_S + b * FAST_C, pk);
-                if (__any_sync(0xffffffffu, rescale)) {
-                    // O holds the tiles before this one, scaled by the old maximum: wait for the last of them
+                if (j > 0) {
+                    // Every thread follows o_done phase by phase (an mbarrier wait only tells a phase from its
+                    // neighbour, so nobody may fall two behind): O += P V of tile j - 1 is complete.  It was issued
+                    // before this tile's softmax began, so this rarely waits; and O may now be rescaled.
                     live = mbar_wait_bounded(o_done, (j - 1) & 1, p.wait_limit);
                     live = __all_sync(0xffffffffu, live);
                     if (!live) {
                         if (lane == 0) report(p.status, STATUS_FULL_WAIT_TIMEOUT);
                         break;
                     }
+                }
+                if (__any_sync(0xffffffffu, rescale)) {
+                    // O holds the tiles before this one, scaled by the old maximum
                     tc_fence_after_thread_sync();
 #pragma unroll
                     for (int c = 0; c < 4; c++) {

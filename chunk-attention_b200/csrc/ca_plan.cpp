@@ -64,9 +64,30 @@ void cut_units(Plan& plan, const std::vector<Unit>& units, size_t ubegin, size_t
 
 }  // namespace
 
+// The root-to-leaf chunk list of every row (CSR), read by the any-geometry kernel only.
+void build_paths(Plan& plan) {
+    const int n_seqs = plan.n_seqs;
+    plan.path_off.assign((size_t)n_seqs + 1, 0);
+    for (const ca_chunk_info& ci : plan.infos)
+        for (int s = ci.seq_begin; s < ci.seq_end; s++) plan.path_off[s + 1]++;
+    for (int s = 0; s < n_seqs; s++) plan.path_off[s + 1] += plan.path_off[s];
+    const int64_t total = plan.path_off[n_seqs];
+    plan.path_chunks.resize(total);
+    plan.path_tokens.resize(total);
+    std::vector<int32_t> cursor(plan.path_off.begin(), plan.path_off.end() - 1);
+    for (const ca_chunk_info& ci : plan.infos)
+        for (int s = ci.seq_begin; s < ci.seq_end; s++) {
+            const int32_t p = cursor[s]++;
+            plan.path_chunks[p] = ci.chunk_id;
+            plan.path_tokens[p] = ci.n_tokens;
+        }
+    plan.has_paths = true;
+}
+
 std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int n_seqs, int n_heads,
                        int chunk_size, int tpp_threshold, int n_ctas, int64_t max_chunks,
-                       bool split_phases, int d_head, int esize, bool fast_path, bool seq_first_tensor, int wide_mode) {
+                       bool split_phases, int d_head, int esize, bool fast_path, bool seq_first_tensor, int wide_mode,
+                       bool want_paths) {
     // the vectors keep their capacity from one rebuild to the next
     plan.items.clear();
     plan.wide_chunks.clear();
@@ -90,8 +111,13 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
     plan.tpp_threshold = tpp_threshold;
     plan.split_phases = split_phases;
 
-    // ---- validate, count path lengths ---------------------------------------------------------
-    plan.path_off.assign(n_seqs + 1, 0);
+    // ---- validate; every row must be covered and end in a chunk of its own ---------------------------------
+    // (nothing here expands a shared chunk over its rows: the per-row path lists, which only the any-geometry
+    // kernel reads, are built on demand by build_paths)
+    plan.infos.assign(infos, infos + n_infos);
+    plan.has_paths = false;
+    std::vector<int32_t> cover((size_t)n_seqs + 1, 0);   // difference array of the rows the entries serve
+    std::vector<int32_t> leaf((size_t)n_seqs, -1);       // the last single-row entry of each row
     int64_t unique_tokens = 0;
     for (int i = 0; i < n_infos; i++) {
         const ca_chunk_info& ci = infos[i];
@@ -101,38 +127,30 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
             return fmt("n_tokens %ld of entry %ld outside [0, %ld]", ci.n_tokens, i, chunk_size);
         if (ci.seq_begin < 0 || ci.seq_begin >= ci.seq_end || ci.seq_end > n_seqs)
             return fmt("row range [%ld, %ld) of entry %ld is empty or outside the batch", ci.seq_begin, ci.seq_end, i);
-        for (int s = ci.seq_begin; s < ci.seq_end; s++) plan.path_off[s + 1]++;
+        cover[ci.seq_begin]++;
+        cover[ci.seq_end]--;
+        if (ci.seq_end - ci.seq_begin == 1) leaf[ci.seq_begin] = i;
         unique_tokens += ci.n_tokens;
     }
-    for (int s = 0; s < n_seqs; s++) {
-        if (plan.path_off[s + 1] == 0) return fmt("row %ld is served by no chunk", s);
-        plan.path_off[s + 1] += plan.path_off[s];
+    for (int s = 0, run = 0; s < n_seqs; s++) {
+        run += cover[s];
+        if (run == 0) return fmt("row %ld is served by no chunk", s);
+        if (leaf[s] < 0) return fmt("last chunk of row %ld is shared with other rows; every row needs its own tail", s);
     }
-    const int64_t path_total = plan.path_off[n_seqs];
-    plan.path_chunks.resize(path_total);
-    plan.path_tokens.resize(path_total);
-    std::vector<int32_t> path_info(path_total);  // index into infos
-    {
-        std::vector<int32_t> cursor(plan.path_off.begin(), plan.path_off.end() - 1);
-        for (int i = 0; i < n_infos; i++) {
-            for (int s = infos[i].seq_begin; s < infos[i].seq_end; s++) {
-                int32_t p = cursor[s]++;
-                plan.path_chunks[p] = infos[i].chunk_id;
-                plan.path_tokens[p] = infos[i].n_tokens;
-                path_info[p] = i;
-            }
-        }
+    // the list is depth-first: an entry that serves several rows lies before the leaf of each of them
+    for (int i = 0; i < n_infos; i++) {
+        const ca_chunk_info& ci = infos[i];
+        if (ci.seq_end - ci.seq_begin == 1) continue;
+        for (int s = ci.seq_begin; s < ci.seq_end; s++)
+            if (leaf[s] < i)
+                return fmt("last chunk of row %ld is shared by %ld rows; every row needs its own tail", s, ci.seq_end - ci.seq_begin);
     }
-    // the leaf of every row must be private to it: new tokens are appended there
+    // the leaf of every row is private to it: new tokens are appended there
     plan.tail_chunk.resize(n_seqs);
     plan.tail_tokens.resize(n_seqs);
     for (int s = 0; s < n_seqs; s++) {
-        const ca_chunk_info& leaf = infos[path_info[plan.path_off[s + 1] - 1]];
-        if (leaf.seq_end - leaf.seq_begin != 1)
-            return fmt("last chunk of row %ld is shared by %ld rows; every row needs its own tail", s,
-                       leaf.seq_end - leaf.seq_begin);
-        plan.tail_chunk[s] = leaf.chunk_id;
-        plan.tail_tokens[s] = leaf.n_tokens;
+        plan.tail_chunk[s] = infos[leaf[s]].chunk_id;
+        plan.tail_tokens[s] = infos[leaf[s]].n_tokens;
     }
 
     plan.stats.unique_kv_bytes = unique_tokens * (int64_t)n_heads * d_head * 2 * esize;
@@ -140,6 +158,7 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
     plan.stats.fast_path = fast_path ? 1 : 0;
     plan.stats.kernels_per_step = 1;
     plan.merge_off.assign((size_t)n_seqs + 1, 0);
+    if (want_paths || !fast_path) build_paths(plan);
     if (!fast_path) {
         plan.n_ctas = 0;
         return "";
@@ -185,8 +204,6 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
     }
 
     // ---- units ---------------------------------------------------------------------------------------------
-    std::vector<int32_t> priv_arena;
-    priv_arena.reserve(path_total);  // never reallocates: the units keep pointers into it
     std::vector<Unit> units;
     units.reserve(runs.size() * 2 + (size_t)n_seqs);
     for (size_t ri = 0; ri < runs.size(); ri++) {
@@ -204,35 +221,40 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
         }
     }
     const size_t n_units_cf = units.size();
+    // The private chunks of every row, in path order (CSR): only the chunks that are NOT shared are expanded over
+    // their rows, and those serve a single row unless tpp_threshold was raised.
+    std::vector<int32_t> priv_off((size_t)n_seqs + 1, 0);
+    for (int i = 0; i < n_infos; i++)
+        if (!shared[i])
+            for (int s = infos[i].seq_begin; s < infos[i].seq_end; s++) {
+                // a non-final private tile must be full: only the tail may be partially filled
+                if (i != leaf[s] && infos[i].n_tokens != chunk_size)
+                    return fmt("row %ld has a partially filled chunk that is not its tail", s);
+                priv_off[s + 1]++;
+            }
+    for (int s = 0; s < n_seqs; s++) priv_off[s + 1] += priv_off[s];
+    std::vector<int32_t> priv_arena((size_t)priv_off[n_seqs]);
+    {
+        std::vector<int32_t> cursor(priv_off.begin(), priv_off.end() - 1);
+        for (int i = 0; i < n_infos; i++)
+            if (!shared[i])
+                for (int s = infos[i].seq_begin; s < infos[i].seq_end; s++) priv_arena[cursor[s]++] = infos[i].chunk_id;
+    }
     // Sequences whose private part is a single chunk (a short tail).  When there are many of them they
     // are not walked by the persistent kernel, where an item costs the same whatever its size, but by
-    // a kernel of their own with one warp per (sequence, head); their items go to the end of the list.
+    // a kernel of their own with one half-warp per (sequence, head); their items follow the persistent kernel's.
     std::vector<Unit> short_units;
     bool route_short = false;
     if (seq_first_tensor) {
         int64_t n_short = 0;
-        for (int s = 0; s < n_seqs; s++) {
-            int n_priv = 0;
-            for (int32_t p = plan.path_off[s]; p < plan.path_off[s + 1]; p++) n_priv += shared[path_info[p]] ? 0 : 1;
-            n_short += n_priv == 1 ? 1 : 0;
-        }
+        for (int s = 0; s < n_seqs; s++) n_short += priv_off[s + 1] - priv_off[s] == 1 ? 1 : 0;
         route_short = n_short * n_heads > 4 * (int64_t)n_ctas;  // fewer are cheaper inside the persistent kernel than a launch of their own
         if (route_short) short_units.reserve((size_t)n_seqs);
     }
     for (int s = 0; s < n_seqs; s++) {
-        const int32_t* priv = priv_arena.data() + priv_arena.size();
-        int32_t n_priv = 0;
-        for (int32_t p = plan.path_off[s]; p < plan.path_off[s + 1]; p++)
-            if (!shared[path_info[p]]) {
-                priv_arena.push_back(plan.path_chunks[p]);
-                n_priv++;
-            }
-        // a non-final private tile must be full: only the tail may be partially filled
-        for (int32_t p = plan.path_off[s]; p + 1 < plan.path_off[s + 1]; p++)
-            if (!shared[path_info[p]] && plan.path_tokens[p] != chunk_size)
-                return fmt("row %ld has a partially filled chunk that is not its tail", s);
+        const int32_t n_priv = priv_off[s + 1] - priv_off[s];
         std::vector<Unit>& dst = (route_short && n_priv == 1) ? short_units : units;
-        dst.push_back(Unit{priv, n_priv, s, 1, seq_first_tensor ? 4 : 0, plan.tail_tokens[s], true});
+        dst.push_back(Unit{priv_arena.data() + priv_off[s], n_priv, s, 1, seq_first_tensor ? 4 : 0, plan.tail_tokens[s], true});
     }
 
     // ---- items ---------------------------------------------------------------------------------------------
@@ -256,7 +278,10 @@ std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int 
     plan.n_ctas = (int)std::min<int64_t>(n_ctas, std::max<int64_t>(1, (int64_t)plan.items.size() * n_heads));
     // the short tails: one single-tile item each, after the persistent kernel's items
     plan.n_items_short = (int)short_units.size();
+    plan.short_slot_base = n_slots;
+    plan.short_all_empty = !short_units.empty();
     for (const Unit& un : short_units) {
+        if (un.last_tokens != 0) plan.short_all_empty = false;
         plan.items.emplace_back();
         PlanItem& it = plan.items.back();
         it.n_tiles = 1;

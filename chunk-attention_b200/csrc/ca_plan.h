@@ -65,10 +65,14 @@ struct Plan {
     std::vector<PlanItem> items;          // chunk-first items first, short tails last
     int n_items_cf = 0;                   // how many of them are chunk-first items
     int n_items_short = 0;                // how many, after the persistent kernel's items, are short tails for the warp-per-item kernel
+    bool short_all_empty = false;         // every short tail was empty when the plan was built (freshly reserved tails)
+    int32_t short_slot_base = 0;          // first partial row (per-item numbering) of the short tails
     int n_items_wide = 0;                 // how many at the END of the list are wide items for the tcgen05 kernel
     std::vector<int32_t> wide_chunks;     // chunk lists of the wide items
     std::vector<int32_t> merge_off, merge_slots;
     int max_merge_len = 0;                // pieces of the row that has most
+    std::vector<ca_chunk_info> infos;     // the input, kept so that the path lists can be built later
+    bool has_paths = false;               // path_* are filled (build_paths)
     std::vector<int32_t> path_off, path_chunks, path_tokens;
     std::vector<int32_t> tail_chunk, tail_tokens;
     ca_plan_stats stats{};
@@ -82,6 +86,9 @@ inline int item_slots(int n_rows, int splits) { return n_rows == 1 ? 1 : n_rows 
 std::string build_plan(Plan& plan, const ca_chunk_info* infos, int n_infos, int n_seqs, int n_heads,
                        int chunk_size, int tpp_threshold, int n_ctas, int64_t max_chunks,
                        bool split_phases, int d_head, int esize, bool fast_path, bool seq_first_tensor,
-                       int wide_mode = 1);  // 0: never route runs to the tcgen05 kernel, 1: by cost, 2: every shared run
+                       int wide_mode = 1,   // 0: never route runs to the tcgen05 kernel, 1: by cost, 2: every shared run
+                       bool want_paths = true);  // also build the per-row path lists of the any-geometry kernel
+// The per-row path lists (path_off / path_chunks / path_tokens) from plan.infos, for a plan built without them.
+void build_paths(Plan& plan);
 
 }  // namespace ca
