@@ -86,6 +86,9 @@ struct ca_context {
     bool opt_sf_tensor = true;
     int opt_pdl = 3;
     int opt_wide = 1;
+    bool opt_overlap = false;
+    cudaStream_t side_stream = nullptr;   // the short-tails kernel runs here beside the wide-runs kernel
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     long long opt_wait_limit = ca::DEFAULT_WAIT_LIMIT_CYCLES;
     int opt_withhold_item = -1;
     unsigned long long* trace = nullptr;  // [kTraceCtas][4], allocated when tracing is switched on
@@ -192,6 +195,9 @@ int ca_context_create(ca_context** out, int device, int n_heads, int d_head, int
     c->num_sms = prop.multiProcessorCount;
     cudaError_t e = cudaEventCreateWithFlags(&c->upload_done, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->paths_done, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->side_stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaMalloc(&c->status, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(c->status, 0, sizeof(int));
     if (e == cudaSuccess) e = cudaMalloc(&c->counters, 2 * sizeof(int));
@@ -213,6 +219,12 @@ void ca_context_destroy(ca_context* c) {
         if (c->upload_pending) cudaEventSynchronize(c->upload_done);
         cudaEventDestroy(c->upload_done);
     }
+    if (c->side_stream) {
+        cudaStreamSynchronize(c->side_stream);
+        cudaStreamDestroy(c->side_stream);
+    }
+    if (c->ev_fork) cudaEventDestroy(c->ev_fork);
+    if (c->ev_join) cudaEventDestroy(c->ev_join);
     if (c->paths_done) {
         if (c->paths_pending) cudaEventSynchronize(c->paths_done);
         cudaEventDestroy(c->paths_done);
@@ -244,6 +256,9 @@ int ca_context_set_option(ca_context* c, int option, int64_t value) {
     } else if (option == CA_OPT_WIDE_RUNS) {
         if (value < 0 || value > 2) return fail(CA_ERR_INVALID, "wide-runs mode must be 0, 1 or 2");
         c->opt_wide = (int)value;
+    } else if (option == CA_OPT_OVERLAP_KERNELS) {
+        c->opt_overlap = value != 0;
+        return CA_OK;
     } else if (option == CA_OPT_DEPENDENT_LAUNCH) {
         if (value < 0 || value > 3) return fail(CA_ERR_INVALID, "dependent-launch mask out of range");
         c->opt_pdl = (int)value;
@@ -512,12 +527,26 @@ int ca_attn_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_st
     // first (the short tails before the wide runs, whose set-up then overlaps them) so that the persistent kernel's
     // tail leads straight into the merge.
     const int n_items = c->meta.n_items - c->meta.n_items_short - c->meta.n_items_wide;
-    if (c->meta.n_items_short > 0 && (phases & 2) && !(c->meta.short_all_empty && c->delta_tokens == 0)) {
+    const bool run_short = c->meta.n_items_short > 0 && (phases & 2) && !(c->meta.short_all_empty && c->delta_tokens == 0);
+    const bool run_wide = c->meta.n_items_wide > 0 && (phases & 1);
+    // The short tails are bound by memory, the wide runs by the tensor and special-function pipes, and they touch
+    // disjoint partial rows: optionally (CA_OPT_OVERLAP_KERNELS) the short-tails kernel runs on a second stream
+    // BESIDE the wide kernel (forked and joined with events) instead of before it.  Off by default: measured, the
+    // wide kernel's CTAs leave too little of an SM for the other kernel to make headway beside them.
+    const bool beside = run_short && run_wide && c->opt_overlap;
+    if (run_short) {
         p.item_lo = n_items * H;
         p.item_hi = (n_items + c->meta.n_items_short) * H;
-        CA_CUDA(ca::launch_attn_short_tails(p, stream, (c->opt_pdl & 2) != 0));
+        if (beside) {
+            CA_CUDA(cudaEventRecord(c->ev_fork, stream));
+            CA_CUDA(cudaStreamWaitEvent(c->side_stream, c->ev_fork, 0));
+            CA_CUDA(ca::launch_attn_short_tails(p, c->side_stream, false));
+            CA_CUDA(cudaEventRecord(c->ev_join, c->side_stream));
+        } else {
+            CA_CUDA(ca::launch_attn_short_tails(p, stream, (c->opt_pdl & 2) != 0));
+        }
     }
-    if (c->meta.n_items_wide > 0 && (phases & 1)) {
+    if (run_wide) {
         ca::WideParams w;
         w.pool = p.pool;
         w.n_heads = p.n_heads;
@@ -540,6 +569,7 @@ int ca_attn_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_st
         if (c->trace_ctas == 0) w.trace = nullptr;
         CA_CUDA(ca::launch_attn_wide(w, stream, (c->opt_pdl & 2) != 0));
     }
+    if (beside) CA_CUDA(cudaStreamWaitEvent(stream, c->ev_join, 0));
     if (!c->meta.split_phases) {
         CA_CUDA(launch(0, n_items));
     } else {

@@ -789,11 +789,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 2) attn_partial_kernel(const Part
 // softmax needs no further exchange) and 16 bytes = 8 output elements of each V row.  The result is an
 // ordinary partial (max and sum in log2 units, un-normalised O), combined with the row's other partials by
 // the merge kernel.
-constexpr int SHORT_WARPS = 8;
+constexpr int SHORT_WARPS = 4;   // small CTAs: they fit beside the wide-runs kernel's CTAs when the two overlap
 constexpr int SHORT_ITEMS_PER_CTA = 2 * SHORT_WARPS;
 constexpr int SHORT_BLOCK = 8;   // tokens per round
 
-__global__ void __launch_bounds__(SHORT_WARPS * 32, 2) attn_short_tails_kernel(const PartialParams p) {
+__global__ void __launch_bounds__(SHORT_WARPS * 32, 4) attn_short_tails_kernel(const PartialParams p) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

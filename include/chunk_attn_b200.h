@@ -109,6 +109,10 @@ CA_API void ca_context_destroy(ca_context* ctx);
  * (ca_status_read) and returns; default 4e9, about two seconds.  The waits exist so that a lost copy or a
  * damaged work list ends in an error code instead of a hung GPU. */
 #define CA_OPT_WAIT_LIMIT_CYCLES 7
+/* 1: when a step has both wide shared runs and short private tails, their two kernels (independent work, one bound
+ * by the tensor pipes, one by memory) run side by side on two streams; 0 (default): one after the other -- measured
+ * on B200 the two orders take the same time within 3 %, the wide kernel's CTAs leave little room beside them. */
+#define CA_OPT_OVERLAP_KERNELS 9
 /* Failure-path tests only: the CTA that draws item `value` of the next launches stops feeding its consumer
  * warps, whose bounded wait then runs out (status 1).  -1 (default) switches it off. */
 #define CA_OPT_TEST_WITHHOLD_ITEM 8
