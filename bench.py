@@ -153,7 +153,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "50"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -394,9 +394,9 @@ def measure_static(name, dev, K, W_, args, n_parity=8, ref_cuda=True):
     err = dense_parity(w, rows, out, q, pairs)
     del w
     torch.cuda.empty_cache()
+    sampler = ClockSampler(dev.index or 0).start()
     for _ in range(W_):
         attn.forward(q=q)
-    sampler = ClockSampler(dev.index or 0).start()
     blocks = time_blocks(lambda: attn.forward(q=q), K, 1 + SPREAD_BLOCKS, torch.cuda.synchronize)
     kern = kernel_times(engine, q, K, args.split_phases) if engine.plan_stats()["fast_path"] else None
     clocks = sampler.stop()
@@ -874,12 +874,11 @@ def run_b200(args):
             torch.cuda._sleep(400_000)
 
     W_, K = max(3, args.warmup), max(1, args.steps)
-    for _ in range(W_):
-        step()
-    sync_all()
     sampler = ClockSampler(local_rank)
     if rank == 0:
-        sampler.start()
+        sampler.start()      # before the warm-up: starting it takes milliseconds in which the GPU would idle
+    for _ in range(W_):
+        step()
     blocks = time_blocks(step, K, 1 + SPREAD_BLOCKS, sync_all, align)
     per_rank = None
     if world > 1:

@@ -1215,6 +1215,10 @@ __global__ void __launch_bounds__(128, 3) attn_merge_wide_kernel(const MergePara
 // The kernel before it in the stream has completed, so the rows it stored into the peers are ordered before the
 // release.  A peer that never arrives costs the time limit and a status code, not a hung GPU.
 __global__ void peer_barrier_kernel(const PeerBarrierParams p) {
+    // launched as a programmatic dependent of the kernel whose rows it publishes: resident early, it waits here
+    // for that kernel's completion (a no-op for an ordinary launch) and lets the next kernel set itself up
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int i = threadIdx.x;
     if (i >= p.n_peers) return;
     uint32_t* theirs = p.flags[i] + p.rank;
@@ -1235,8 +1239,23 @@ __global__ void peer_barrier_kernel(const PeerBarrierParams p) {
 }  // namespace
 
 cudaError_t launch_peer_barrier(const PeerBarrierParams& p, cudaStream_t stream) {
-    peer_barrier_kernel<<<1, 32, 0, stream>>>(p);
-    return cudaGetLastError();
+    static const bool pdl_disabled = std::getenv("CA_DISABLE_PDL") != nullptr;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(32);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_disabled ? 0 : 1;
+    cudaError_t err = cudaLaunchKernelEx(&cfg, peer_barrier_kernel, p);
+    if (err != cudaSuccess && cfg.numAttrs == 1) {
+        (void)cudaGetLastError();
+        cfg.numAttrs = 0;
+        err = cudaLaunchKernelEx(&cfg, peer_barrier_kernel, p);
+    }
+    return err;
 }
 
 cudaError_t configure_fast_kernels() {
