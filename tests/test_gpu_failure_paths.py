@@ -52,3 +52,31 @@ def test_option_ranges():
     eng = CabiEngine(2, 128, 64, torch.float16, max_chunks=8)
     with pytest.raises(cabi.CAError):
         eng.ctx.set_option(cabi.CA_OPT_WAIT_LIMIT_CYCLES, 10)   # a limit this short would fail ordinary waits
+
+
+def test_peer_barrier_gives_up_after_its_limit_and_passes_when_the_peer_arrives():
+    # the barrier of the fused multi-GPU gather, on one GPU: two flag arrays stand in for two ranks.  Rank 0 signals
+    # both arrays and waits for word 1 of its own, which nobody sets: after the 2 ms limit the kernel records status 6
+    # and returns.  Once "rank 1" has arrived (its word written by hand) the same barrier passes.
+    flags = [torch.zeros(8, dtype=torch.int32, device="cuda") for _ in range(2)]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ptrs = [f.data_ptr() for f in flags]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    cabi.peer_barrier(ptrs, rank=0, epoch=1, timeout_ns=2_000_000, status_ptr=status.data_ptr())
+    t1.record()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 6
+    assert 1.5 < t0.elapsed_time(t1) < 200.0          # ms: the limit, not an endless spin
+    assert flags[0][0].item() == 1 and flags[1][0].item() == 1   # rank 0's own arrival was published to both
+    status.zero_()
+    flags[0][1] = 1                                   # rank 1 arrives
+    cabi.peer_barrier(ptrs, rank=0, epoch=1, timeout_ns=2_000_000, status_ptr=status.data_ptr())
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    flags[0][1] = 7                                   # a peer that is already further on does not hold anyone up
+    cabi.peer_barrier(ptrs, rank=0, epoch=2, timeout_ns=2_000_000, status_ptr=status.data_ptr())
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    with pytest.raises(cabi.CAError):
+        cabi.peer_barrier(ptrs, rank=2, epoch=1)      # rank outside the group
