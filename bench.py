@@ -434,15 +434,17 @@ def measure_cfg4(dev, args, passes=1, with_e2e=True):
     import synthetic_workloads as W
     attn = Attention(n_heads=32, d_head=128, chunk_size=64, memory_mb=1400, dtype=torch.float16, device=dev)
     ev = lambda: torch.cuda.Event(enable_timing=True)
-    step_ms, fwd_ms, kern_ms, host_ms, ukv, e2e_ms = [], [], [], [], [], []
+    step_ms, fwd_ms, kern_ms, host_ms, ukv, e2e_ms, pipe_ms = [], [], [], [], [], [], []
     parity = {"max_abs": 0.0, "samples": 0, "tol": PARITY_TOL, "against": "dense fp64 over prefill + appended rows",
               "steps_checked": []}
     q_host = out_host = k_host = v_host = None
     sampler = None
-    n_passes = 1 + passes + (1 if with_e2e else 0)
+    n_passes = 1 + passes + 1 + (1 if with_e2e else 0)
     for rep in range(n_passes):
         timed = 1 <= rep <= passes
         e2e_pass = with_e2e and rep == n_passes - 1
+        pipe_pass = rep == passes + 1   # the steps between two replacements enqueued back to back, no host wait between them
+        pre, pe0 = [], None
         cfg = W.Config4(gen_device=dev)
         seqs = []
 
@@ -463,6 +465,22 @@ def measure_cfg4(dev, args, passes=1, with_e2e=True):
                     seqs.pop(i)
                 for _ in range(cfg.churn):
                     add(cfg.new_sequence(cfg.rng.randrange(cfg.n_groups)))
+            if pipe_pass:
+                if not pre:
+                    n_seg = min(cfg.churn_every - step % cfg.churn_every, cfg.steps - step)
+                    pre = [tuple(t.to(torch.float16) for t in cfg.step_inputs(len(seqs))) for _ in range(n_seg)]
+                    torch.cuda.synchronize()
+                    pe0 = ev()
+                    pe0.record()
+                q, nk, nv = pre.pop(0)
+                attn.append_token(tokens=[7_000_000 + step] * len(seqs), k=nk, v=nv)
+                out = attn.forward(q=q)
+                if not pre:
+                    pe1 = ev()
+                    pe1.record()
+                    torch.cuda.synchronize()
+                    pipe_ms.append(pe0.elapsed_time(pe1) / n_seg)
+                continue
             q, nk, nv = (t.to(torch.float16) for t in cfg.step_inputs(len(seqs)))
             toks = [7_000_000 + step] * len(seqs)
             for i, sq in enumerate(seqs):
@@ -537,6 +555,10 @@ def measure_cfg4(dev, args, passes=1, with_e2e=True):
                                          "mean_at_replace_steps": statistics.mean(host_ms[i] for i in churn_steps) * 1e3
                                          if churn_steps else None},
            "step_minus_forward_us": (statistics.mean(step_ms) - statistics.mean(fwd_ms)) * 1e3,
+           "us_per_step_enqueued_back_to_back": statistics.mean(pipe_ms) * 1e3 if pipe_ms else None,
+           "timing": "us_per_step: every step alone on an idle GPU, so the host's append + work-list update is inside it; "
+                     "us_per_step_enqueued_back_to_back: the 16 steps between two replacements enqueued without a host "
+                     "wait, as a decoder loop does (one more pass over the trace)",
            "parity": parity, "clocks": clocks, "device_status": attn.device_status(),
            "gpu_launches_per_step": 1 + attn.plan_stats()["kernels_per_step"]}
     res.update(spread_of([statistics.mean(step_ms[i:i + 16]) * 1e3 for i in range(0, len(step_ms), 16)]))
@@ -1086,8 +1108,8 @@ def run_cfg4(args):
             "config": {"workload": res["workload"], "workload_choice": "--workload", "l2": res["l2"]},
             "gpu_launches": res["steps"] * res["gpu_launches_per_step"]}
     for k in ("parity", "roofline", "e2e", "clocks", "device_status", "forward_us", "forward_us_median",
-              "unique_kv_bytes_mean", "hbm_frac", "host_us_append_and_update", "step_minus_forward_us", "value_median",
-              "value_min", "value_max", "blocks"):
+              "unique_kv_bytes_mean", "hbm_frac", "host_us_append_and_update", "step_minus_forward_us",
+              "us_per_step_enqueued_back_to_back", "timing", "value_median", "value_min", "value_max", "blocks"):
         line[k] = res.get(k)
     if not args.no_cpu_baseline:
         try:

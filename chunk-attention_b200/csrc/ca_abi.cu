@@ -93,6 +93,7 @@ struct ca_context {
     int opt_withhold_item = -1;
     unsigned long long* trace = nullptr;  // [kTraceCtas][4], allocated when tracing is switched on
     int trace_ctas = 0;                   // CTAs of the last traced launch
+    int trace_cycles = 0;                 // CA_OPT_TRACE = 2: the tcgen05 kernel accounts for cycles per role instead
 
     ca::Plan plan;  // scratch of ca_refresh_kernel_context (vectors keep their capacity)
     // what the launches need to know about the work list that is on the device
@@ -273,6 +274,8 @@ int ca_context_set_option(ca_context* c, int option, int64_t value) {
     } else if (option == CA_OPT_TRACE) {
         DeviceGuard guard(c->device);
         if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+        if (value < 0 || value > 2) return fail(CA_ERR_INVALID, "CA_OPT_TRACE takes 0, 1 or 2");
+        c->trace_cycles = value == 2 ? 1 : 0;
         if (value && !c->trace) {
             CA_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->trace), (size_t)kTraceCtas * 8 * sizeof(unsigned long long)));
             CA_CUDA(cudaMemset(c->trace, 0, (size_t)kTraceCtas * 8 * sizeof(unsigned long long)));
@@ -565,6 +568,7 @@ int ca_attn_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_st
         w.max_chunks = p.max_chunks;
         w.wait_limit = p.wait_limit;
         w.trace = c->trace;
+        w.trace_cycles = c->trace_cycles;
         c->trace_ctas = (w.item_hi - w.item_lo) < kTraceCtas ? (w.item_hi - w.item_lo) : 0;
         if (c->trace_ctas == 0) w.trace = nullptr;
         CA_CUDA(ca::launch_attn_wide(w, stream, (c->opt_pdl & 2) != 0));

@@ -59,6 +59,9 @@ constexpr uint32_t IDESC_PV = umma_idesc_f16(W_ROWS, FAST_D, false, true);
 
 __device__ __forceinline__ void report(int* status, int code) { atomicCAS(status, STATUS_OK, code); }
 
+// ACCT: instead of the timestamps 1-5 of the trace, the CTA records where the cycles of its two serial roles go
+// (see WideParams::trace_cycles); a separate instantiation, so the kernel that serves carries none of it.
+template <bool ACCT>
 __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
@@ -111,7 +114,7 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
     __syncthreads();   // barriers initialised, TMEM address published
     tc_fence_after_thread_sync();
     const uint32_t tmem_base = *tmem_slot;
-    if (tr && threadIdx.x == 0) tr[1] = global_timer_ns();
+    if (!ACCT && tr && threadIdx.x == 0) tr[1] = global_timer_ns();
     if (!ok && threadIdx.x == 0) report(p.status, STATUS_BAD_WORK_LIST);  // skipped: its partial rows keep what they held
 
     if (ok) {
@@ -169,12 +172,18 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
             // ---- MMA issuer: one thread
             if (lane == 0) {
                 bool live = true;
+                long long c_issue = 0, c_wait_p = 0, c_wait_k = 0, w0 = 0, w1 = 0;
                 auto issue_qk = [&](int j) {
                     const int i = 2 * j, slot = i & (W_SLOTS - 1);
+                    if (ACCT) w0 = clock64();
                     if (!mbar_wait_bounded(full_bar + 8 * slot, (i / W_SLOTS) & 1, p.wait_limit)) {
                         report(p.status, STATUS_FULL_WAIT_TIMEOUT);
                         live = false;
                         return;
+                    }
+                    if (ACCT) {
+                        w1 = clock64();
+                        c_wait_k += w1 - w0;
                     }
                     tc_fence_after_thread_sync();
                     const uint32_t kaddr = ring + slot * FAST_TILE_BYTES;
@@ -187,6 +196,7 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
                     }
                     umma_commit(s_full + 8 * (j & 1));   // S of tile j is complete ...
                     umma_commit(empty_bar + 8 * slot);   // ... and its K tile may be overwritten
+                    if (ACCT) c_issue += clock64() - w1;
                 };
                 if (!mbar_wait_bounded(q_ready, 0, p.wait_limit)) {
                     report(p.status, STATUS_FULL_WAIT_TIMEOUT);
@@ -197,10 +207,15 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
                     if (j + 1 < n_tiles) issue_qk(j + 1);  // S of the next tile is computed under this tile's softmax
                     if (!live) break;
                     const int i = 2 * j + 1, slot = i & (W_SLOTS - 1);
+                    if (ACCT) w0 = clock64();
                     if (!mbar_wait_bounded(p_full + 8 * (j & 1), (j >> 1) & 1, p.wait_limit) ||
                         !mbar_wait_bounded(full_bar + 8 * slot, (i / W_SLOTS) & 1, p.wait_limit)) {
                         report(p.status, STATUS_FULL_WAIT_TIMEOUT);
                         break;
+                    }
+                    if (ACCT) {
+                        w1 = clock64();
+                        c_wait_p += w1 - w0;
                     }
                     tc_fence_after_thread_sync();
                     const uint32_t vaddr = ring + slot * FAST_TILE_BYTES;
@@ -213,6 +228,12 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
                     }
                     umma_commit(empty_bar + 8 * slot);
                     umma_commit(o_done);
+                    if (ACCT) c_issue += clock64() - w1;
+                }
+                if (ACCT && tr) {
+                    tr[2] = (unsigned long long)c_issue;
+                    tr[3] = (unsigned long long)c_wait_p;
+                    tr[7] = (unsigned long long)c_wait_k;
                 }
             }
         } else {
@@ -222,8 +243,10 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
             const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
             float m_used = W_NEG_BIG, l = 0.f;
             bool live = true;
+            long long c_wait_s = 0, c_chain = 0, c_ld = 0, w0 = 0, w1 = 0;
             for (int j = 0; j < n_tiles && live; j++) {
                 const int b = j & 1;
+                if (ACCT) w0 = clock64();
                 live = mbar_wait_bounded(s_full + 8 * b, (j >> 1) & 1, p.wait_limit);
                 live = __all_sync(0xffffffffu, live);
                 if (!live) {
@@ -231,11 +254,16 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
                     break;
                 }
                 tc_fence_after_thread_sync();
-                if (tr && j == 0 && threadIdx.x == 0) tr[2] = global_timer_ns();
+                if (!ACCT && tr && j == 0 && threadIdx.x == 0) tr[2] = global_timer_ns();
+                if (ACCT) {
+                    w1 = clock64();
+                    c_wait_s += w1 - w0;
+                }
                 uint32_t s0[32], s1[32];
                 tmem_ld32(lane_addr + W_COL_S + b * FAST_C, s0);
                 tmem_ld32(lane_addr + W_COL_S + b * FAST_C + 32, s1);
                 tmem_wait_ld();
+                if (ACCT) c_ld += clock64() - w1;
                 float alpha = 1.f;
                 bool rescale = false;
                 uint32_t pk[32];
@@ -296,14 +324,20 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
                 tmem_wait_st();
                 tc_fence_before_thread_sync();
                 mbar_arrive(p_full + 8 * b);
+                if (ACCT) c_chain += clock64() - w1;
             }
-            if (tr && threadIdx.x == 0) tr[3] = global_timer_ns();
+            if (ACCT && tr && threadIdx.x == 0) {
+                tr[1] = (unsigned long long)c_ld;
+                tr[4] = (unsigned long long)c_wait_s;
+                tr[5] = (unsigned long long)c_chain;
+            }
+            if (!ACCT && tr && threadIdx.x == 0) tr[3] = global_timer_ns();
             if (live) {
                 live = mbar_wait_bounded(o_done, (n_tiles - 1) & 1, p.wait_limit);
                 live = __all_sync(0xffffffffu, live);
                 if (!live && lane == 0) report(p.status, STATUS_FULL_WAIT_TIMEOUT);
             }
-            if (tr && threadIdx.x == 0) tr[4] = global_timer_ns();
+            if (!ACCT && tr && threadIdx.x == 0) tr[4] = global_timer_ns();
             if (live) {
                 tc_fence_after_thread_sync();
                 // O leaves through shared memory (the staged queries and the ring are free now: every MMA has
@@ -330,7 +364,7 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
                 }
                 if (active) p.part_ml[(size_t)(slot_base + r) * p.n_heads + head] = make_float2(m_used, l);
             }
-            if (tr && threadIdx.x == 0) tr[5] = global_timer_ns();
+            if (!ACCT && tr && threadIdx.x == 0) tr[5] = global_timer_ns();
         }
     }
     // ---- common exit of every path: nobody touches TMEM after this barrier, then the allocating warp frees it
@@ -346,9 +380,11 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
 }  // namespace
 
 cudaError_t configure_wide_kernel() {
-    cudaError_t e = cudaFuncSetAttribute(attn_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, W_SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(attn_wide_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, W_SMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_wide_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, W_SMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_wide_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(attn_wide_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    return cudaFuncSetAttribute(attn_wide_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
 }
 
 cudaError_t launch_attn_wide(const WideParams& p, cudaStream_t stream, bool dependent_launch) {
@@ -365,11 +401,12 @@ cudaError_t launch_attn_wide(const WideParams& p, cudaStream_t stream, bool depe
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (dependent_launch && !pdl_disabled) ? 1 : 0;
-    cudaError_t err = cudaLaunchKernelEx(&cfg, attn_wide_kernel, p);
+    auto* kernel = (p.trace && p.trace_cycles) ? attn_wide_kernel<true> : attn_wide_kernel<false>;
+    cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, p);
     if (err != cudaSuccess && cfg.numAttrs == 1) {
         (void)cudaGetLastError();
         cfg.numAttrs = 0;
-        err = cudaLaunchKernelEx(&cfg, attn_wide_kernel, p);
+        err = cudaLaunchKernelEx(&cfg, kernel, p);
     }
     return err;
 }

@@ -95,7 +95,9 @@ CA_API void ca_context_destroy(ca_context* ctx);
 /* how a sequence's private tail (one query row) is walked: 1 (default) on tensor cores, 16 tokens
  * per warp; 0 on CUDA cores with 128-bit shared-memory loads and warp-shuffle reductions */
 #define CA_OPT_SEQ_FIRST_TENSOR 3
-/* 1: the attention kernel records per-CTA nanosecond timestamps, read with ca_context_read_trace */
+/* 1: the attention kernel records per-CTA nanosecond timestamps, read with ca_context_read_trace;
+ * 2: as 1, but the tcgen05 kernel for wide runs accounts for the cycles of its two serial roles instead
+ * (see ca_context_read_trace) */
 #define CA_OPT_TRACE 4
 /* programmatic dependent launches: bit 0, the merge kernel is set up while the attention kernel
  * drains; bit 1, the attention kernel is set up while the kernel before it in the stream finishes
@@ -224,7 +226,14 @@ CA_API int ca_status_clear(ca_context* ctx, ca_stream stream);
  * of the GPU's global timer; out[8i+4..8i+7] = SM cycles: first consumer warp waiting for tiles, the
  * same warp combining warps / storing partials, producer waiting for free stages, first consumer
  * warp in total.  `out` is a HOST array of 8 * max_ctas; returns the CTA count through n_ctas.
- * Synchronises the stream. */
+ * Synchronises the stream.
+ * When the step's wide runs went to the tcgen05 kernel and nothing was left for the persistent kernel, the
+ * trace is that kernel's: out[8i..8i+6] = entry, set-up done, first score tile ready, last P written, O
+ * complete, partial rows stored, exit (ns).  With CA_OPT_TRACE = 2 entries 1-5 and 7 are SM cycles summed over
+ * the CTA's tiles instead: [1] the first softmax thread loading scores from tensor memory, [2] the MMA thread
+ * issuing tcgen05.mma / commit, [3] that thread waiting for P and the V tile, [4] the first softmax thread
+ * waiting for a score tile, [5] that thread from scores ready to P handed over, [7] the MMA thread waiting
+ * for the K tile. */
 CA_API int ca_context_read_trace(ca_context* ctx, uint64_t* out, int max_ctas, int* n_ctas, ca_stream stream);
 
 /* Per-step counters of the current work list (the roofline metric is computed from them). */

@@ -147,3 +147,29 @@ def test_many_requests_over_one_system_prompt():
     pairs = [(int(torch.randint(0, 1024, (1,), generator=g)), int(torch.randint(0, 8, (1,), generator=g))) for _ in range(8)]
     assert dense_rows(w, rows, out, q, pairs) < TOL_F16
     assert attn.device_status() == 0
+
+
+def test_cycle_accounting_trace_mode_computes_the_same_rows():
+    # CA_OPT_TRACE = 2 runs the instantiation of the wide kernel that accounts for the cycles of its serial roles;
+    # the rows it computes are the same, and every CTA reports time spent issuing MMAs and in the softmax chain
+    # (100 identical contexts and few CTAs: the whole step is one shared run and the empty private tails are short
+    # items that cost no launch, so the trace read back is the wide kernel's)
+    w = W.single_level("acct", 4, 128, 64, torch.float16, 100, 16 * 64, 0, 21, 0.5, gen_device="cuda")
+    eng = CabiEngine(4, 128, 64, torch.float16, max_chunks=16 + 2 * 100 + 8)
+    rows = W.populate(eng, w)
+    q = w.q[rows].to("cuda", torch.float16).contiguous()
+    eng.ctx.set_option(cabi.CA_OPT_WIDE_RUNS, 2)
+    eng.ctx.set_option(cabi.CA_OPT_NUM_CTAS, 8)
+    plain = eng.forward(q).clone()
+    eng.ctx.set_option(cabi.CA_OPT_TRACE, 2)
+    traced = eng.forward(q)
+    assert torch.equal(plain, traced)
+    tr = eng.ctx.read_trace().astype("int64")
+    st = eng.ctx.stats()
+    assert st["n_items_wide"] > 0 and st["n_items_wide"] + st["n_items_short"] == st["n_items"]
+    assert len(tr) == st["n_items_wide"]
+    assert len(tr) > 0 and (tr[:, 2] > 0).all() and (tr[:, 5] > 0).all() and (tr[:, 6] > tr[:, 0]).all()
+    with pytest.raises(RuntimeError):
+        eng.ctx.set_option(cabi.CA_OPT_TRACE, 3)
+    eng.ctx.set_option(cabi.CA_OPT_TRACE, 0)
+    assert eng.ctx.status() == 0

@@ -1,0 +1,35 @@
+"""Where the cycles of the tcgen05 kernel for wide shared runs go (diagnostics, run on a B200):
+    python tests/wide_cycle_accounting.py
+sets CA_OPT_TRACE = 2, runs a few decode steps of three shapes whose shared runs the planner routes to that kernel,
+and prints, per K/V tile, the SM cycles of the CTA's two serial roles: the thread that issues the MMAs (issuing,
+waiting for P, waiting for the K tile) and a softmax thread (waiting for a score tile, from scores to P)."""
+import sys, os
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for p in (ROOT, os.path.join(ROOT, "chunk-attention_b200"), os.path.join(ROOT, "oracle"), os.path.join(ROOT, "tests")):
+    sys.path.insert(0, p)
+import numpy as np, torch
+from chunk_attn import cabi
+import synthetic_workloads as W
+from gpu_helpers import CabiEngine
+
+def run(name, n_seqs, shared, unique):
+    w = W.single_level(name, 32, 128, 64, torch.float16, n_seqs, shared, unique, 2, 0.5, "cuda")
+    eng = CabiEngine(32, 128, 64, torch.float16, max_chunks=shared // 64 + 2 * n_seqs + 8)
+    rows = W.populate(eng, w)
+    q = w.q[rows].to("cuda", torch.float16).contiguous()
+    eng.ctx.set_option(cabi.CA_OPT_TRACE, 2)
+    for _ in range(5):
+        out = eng.forward(q)
+    torch.cuda.synchronize()
+    tr = eng.ctx.read_trace().astype(np.int64)
+    st = eng.ctx.stats()
+    tiles = st["n_items_wide"] and (shared // 64) * ((n_seqs + 127) // 128) * 32 / len(tr)
+    total = (tr[:, 6] - tr[:, 0])
+    print(name, "ctas", len(tr), "tiles/cta %.1f" % tiles, "cta lifetime us median %.2f" % (np.median(total) / 1e3))
+    for nm, col in (("mma issue", 2), ("mma wait P(+V)", 3), ("mma wait K", 7), ("softmax wait S", 4), ("softmax chain", 5), ("  of which ld S", 1)):
+        c = tr[:, col] / tiles
+        print("  %-16s cycles per tile: min %7.0f median %7.0f max %7.0f" % (nm, c.min(), np.median(c), c.max()))
+
+run("cfg3_s4096", 64, 4096, 0)
+run("sys1024", 1024, 2048, 8)
+run("sys128", 128, 2048, 8)
