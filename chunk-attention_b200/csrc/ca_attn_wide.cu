@@ -170,9 +170,11 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
             }
         } else if (warp == 5) {
             // ---- MMA issuer: one thread
-            if (lane == 0) {
+            if (elect_one()) {
                 bool live = true;
-                long long c_issue = 0, c_wait_p = 0, c_wait_k = 0, w0 = 0, w1 = 0;
+                constexpr uint32_t DESC_HI = umma_desc_sw128_hi(1024);   // 8-line groups are 1024 bytes apart in every operand
+                const uint32_t q_lo = umma_desc_sw128_lo(sbase, 16);
+                long long c_issue_qk = 0, c_issue_pv = 0, c_wait_p = 0, c_wait_k = 0, w0 = 0, w1 = 0;
                 auto issue_qk = [&](int j) {
                     const int i = 2 * j, slot = i & (W_SLOTS - 1);
                     if (ACCT) w0 = clock64();
@@ -188,15 +190,17 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
                     tc_fence_after_thread_sync();
                     const uint32_t kaddr = ring + slot * FAST_TILE_BYTES;
                     const uint32_t d = tmem_base + W_COL_S + (j & 1) * FAST_C;
+                    // K step ks: 32 bytes further along the 128-byte line, the second panel of 64 elements after four
+                    const uint32_t b_lo = umma_desc_sw128_lo(kaddr, 16);
 #pragma unroll
                     for (int ks = 0; ks < 8; ks++) {
-                        const uint64_t a = umma_desc_sw128(sbase + (ks >> 2) * W_Q_PANEL + (ks & 3) * 32, 16, 1024);
-                        const uint64_t b = umma_desc_sw128(kaddr + (ks >> 2) * (FAST_C * 128) + (ks & 3) * 32, 16, 1024);
+                        const uint64_t a = umma_desc_pack(q_lo + (((ks >> 2) * W_Q_PANEL + (ks & 3) * 32) >> 4), DESC_HI);
+                        const uint64_t b = umma_desc_pack(b_lo + (((ks >> 2) * (FAST_C * 128) + (ks & 3) * 32) >> 4), DESC_HI);
                         umma_ss_f16(d, a, b, IDESC_QK, ks > 0 ? 1u : 0u);
                     }
                     umma_commit(s_full + 8 * (j & 1));   // S of tile j is complete ...
                     umma_commit(empty_bar + 8 * slot);   // ... and its K tile may be overwritten
-                    if (ACCT) c_issue += clock64() - w1;
+                    if (ACCT) c_issue_qk += clock64() - w1;
                 };
                 if (!mbar_wait_bounded(q_ready, 0, p.wait_limit)) {
                     report(p.status, STATUS_FULL_WAIT_TIMEOUT);
@@ -220,20 +224,24 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
                     tc_fence_after_thread_sync();
                     const uint32_t vaddr = ring + slot * FAST_TILE_BYTES;
                     const uint32_t a_tmem = tmem_base + W_COL_S + (j & 1) * FAST_C;  // P over S, two fp16 per column
+                    // 16 tokens = two groups of 8 lines; the two 64-element panels of d_head are 8 KiB apart
+                    const uint32_t v_lo = umma_desc_sw128_lo(vaddr, FAST_C * 128);
 #pragma unroll
                     for (int kk = 0; kk < 4; kk++) {
-                        // 16 tokens = two groups of 8 lines; the two 64-element panels of d_head are 8 KiB apart
-                        const uint64_t b = umma_desc_sw128(vaddr + kk * 2048, FAST_C * 128, 1024);
+                        const uint64_t b = umma_desc_pack(v_lo + ((kk * 2048) >> 4), DESC_HI);
                         umma_ts_f16(tmem_base, a_tmem + kk * 8, b, IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
                     }
                     umma_commit(empty_bar + 8 * slot);
                     umma_commit(o_done);
-                    if (ACCT) c_issue += clock64() - w1;
+                    if (ACCT) c_issue_pv += clock64() - w1;
                 }
                 if (ACCT && tr) {
-                    tr[2] = (unsigned long long)c_issue;
+                    uint32_t smid;
+                    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+                    tr[1] = (unsigned long long)c_issue_pv;
+                    tr[2] = (unsigned long long)c_issue_qk;
                     tr[3] = (unsigned long long)c_wait_p;
-                    tr[7] = (unsigned long long)c_wait_k;
+                    tr[7] = (unsigned long long)c_wait_k | ((unsigned long long)smid << 48);
                 }
             }
         } else {
@@ -243,7 +251,7 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
             const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
             float m_used = W_NEG_BIG, l = 0.f;
             bool live = true;
-            long long c_wait_s = 0, c_chain = 0, c_ld = 0, w0 = 0, w1 = 0;
+            long long c_wait_s = 0, c_chain = 0, w0 = 0, w1 = 0;
             for (int j = 0; j < n_tiles && live; j++) {
                 const int b = j & 1;
                 if (ACCT) w0 = clock64();
@@ -263,7 +271,6 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
                 tmem_ld32(lane_addr + W_COL_S + b * FAST_C, s0);
                 tmem_ld32(lane_addr + W_COL_S + b * FAST_C + 32, s1);
                 tmem_wait_ld();
-                if (ACCT) c_ld += clock64() - w1;
                 float alpha = 1.f;
                 bool rescale = false;
                 uint32_t pk[32];
@@ -327,7 +334,6 @@ __global__ void __launch_bounds__(W_THREADS, 2) attn_wide_kernel(const WideParam
                 if (ACCT) c_chain += clock64() - w1;
             }
             if (ACCT && tr && threadIdx.x == 0) {
-                tr[1] = (unsigned long long)c_ld;
                 tr[4] = (unsigned long long)c_wait_s;
                 tr[5] = (unsigned long long)c_chain;
             }

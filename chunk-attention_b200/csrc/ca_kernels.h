@@ -79,11 +79,11 @@ struct WideParams {
     long long wait_limit = DEFAULT_WAIT_LIMIT_CYCLES;
     unsigned long long* trace = nullptr;  // optional [n_ctas][8] ns timestamps: entry, set-up done, first S ready,
                                           // last P written, O complete, partial rows stored, exit
-    int trace_cycles = 0;                 // 1: entries 1-5 and 7 hold SM cycles summed over the item's tiles instead: [1] the
-                                          // first softmax thread loading S, [2] the MMA thread issuing MMAs and commits,
-                                          // [3] that thread waiting for P and the V tile, [4] the first softmax thread
-                                          // waiting for S, [5] that thread from S ready to P handed over, [7] the MMA
-                                          // thread waiting for the K tile
+    int trace_cycles = 0;                 // 1: entries 1-5 and 7 hold SM cycles summed over the item's tiles instead: the MMA
+                                          // thread issuing [1] the P V and [2] the Q K^T MMAs with their commits, [3] that
+                                          // thread waiting for P and the V tile, [4] the first softmax thread waiting for
+                                          // S, [5] that thread from S ready to P handed over, [7] bits 0-47 the MMA thread
+                                          // waiting for the K tile, bits 48-63 the SM the CTA ran on
 };
 cudaError_t launch_attn_wide(const WideParams& p, cudaStream_t stream, bool dependent_launch = false);
 cudaError_t configure_wide_kernel();  // once per device before the first launch

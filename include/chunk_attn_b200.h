@@ -230,10 +230,10 @@ CA_API int ca_status_clear(ca_context* ctx, ca_stream stream);
  * When the step's wide runs went to the tcgen05 kernel and nothing was left for the persistent kernel, the
  * trace is that kernel's: out[8i..8i+6] = entry, set-up done, first score tile ready, last P written, O
  * complete, partial rows stored, exit (ns).  With CA_OPT_TRACE = 2 entries 1-5 and 7 are SM cycles summed over
- * the CTA's tiles instead: [1] the first softmax thread loading scores from tensor memory, [2] the MMA thread
- * issuing tcgen05.mma / commit, [3] that thread waiting for P and the V tile, [4] the first softmax thread
- * waiting for a score tile, [5] that thread from scores ready to P handed over, [7] the MMA thread waiting
- * for the K tile. */
+ * the CTA's tiles instead: the MMA thread issuing [1] the P V and [2] the Q K^T tcgen05.mma with their
+ * commits, [3] that thread waiting for P and the V tile, [4] the first softmax thread waiting for a score
+ * tile, [5] that thread from scores ready to P handed over, [7] bits 0-47 the MMA thread waiting for the K
+ * tile, bits 48-63 the SM the CTA ran on. */
 CA_API int ca_context_read_trace(ca_context* ctx, uint64_t* out, int max_ctas, int* n_ctas, ca_stream stream);
 
 /* Per-step counters of the current work list (the roofline metric is computed from them). */

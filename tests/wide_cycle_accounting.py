@@ -24,11 +24,20 @@ def run(name, n_seqs, shared, unique):
     tr = eng.ctx.read_trace().astype(np.int64)
     st = eng.ctx.stats()
     tiles = st["n_items_wide"] and (shared // 64) * ((n_seqs + 127) // 128) * 32 / len(tr)
+    sm = tr[:, 7] >> 48
+    tr[:, 7] &= (1 << 48) - 1
+    # a CTA had the SM to itself if no other CTA of the launch ran there (one wave: lifetimes overlap)
+    alone = np.array([np.sum(sm == x) == 1 for x in sm])
     total = (tr[:, 6] - tr[:, 0])
-    print(name, "ctas", len(tr), "tiles/cta %.1f" % tiles, "cta lifetime us median %.2f" % (np.median(total) / 1e3))
-    for nm, col in (("mma issue", 2), ("mma wait P(+V)", 3), ("mma wait K", 7), ("softmax wait S", 4), ("softmax chain", 5), ("  of which ld S", 1)):
+    print(name, "ctas", len(tr), "tiles/cta %.1f" % tiles, "cta lifetime us median %.2f" % (np.median(total) / 1e3),
+          "ctas alone on their SM:", int(alone.sum()))
+    for nm, col in (("mma issue QK (8+2)", 2), ("mma issue PV (4+2)", 1), ("mma wait P(+V)", 3), ("mma wait K", 7),
+                    ("softmax wait S", 4), ("softmax chain", 5)):
         c = tr[:, col] / tiles
-        print("  %-16s cycles per tile: min %7.0f median %7.0f max %7.0f" % (nm, c.min(), np.median(c), c.max()))
+        line = "  %-19s cycles per tile: min %6.0f median %6.0f max %6.0f" % (nm, c.min(), np.median(c), c.max())
+        if alone.any() and not alone.all():
+            line += "   | alone on the SM: median %6.0f, sharing it: median %6.0f" % (np.median(c[alone]), np.median(c[~alone]))
+        print(line)
 
 run("cfg3_s4096", 64, 4096, 0)
 run("sys1024", 1024, 2048, 8)
