@@ -434,7 +434,7 @@ def measure_cfg4(dev, args, passes=1, with_e2e=True):
     import synthetic_workloads as W
     attn = Attention(n_heads=32, d_head=128, chunk_size=64, memory_mb=1400, dtype=torch.float16, device=dev)
     ev = lambda: torch.cuda.Event(enable_timing=True)
-    step_ms, fwd_ms, kern_ms, host_ms, ukv, e2e_ms, pipe_ms = [], [], [], [], [], [], []
+    step_ms, fwd_ms, kern_ms, host_ms, ukv, e2e_ms, pipe_ms, host_parts = [], [], [], [], [], [], [], []
     parity = {"max_abs": 0.0, "samples": 0, "tol": PARITY_TOL, "against": "dense fp64 over prefill + appended rows",
               "steps_checked": []}
     q_host = out_host = k_host = v_host = None
@@ -506,11 +506,13 @@ def measure_cfg4(dev, args, passes=1, with_e2e=True):
                 continue
             torch.cuda.synchronize()
             e0, e1, e2 = ev(), ev(), ev()
+            ht0 = attn.host_times()
             t0 = time.perf_counter()
             e0.record()
             attn.append_token(tokens=toks, k=nk, v=nv)
             attn.refresh_kernel_context(False)
             t1 = time.perf_counter()
+            ht1 = attn.host_times()
             e1.record()
             out = attn.forward(q=q)
             e2.record()
@@ -519,6 +521,7 @@ def measure_cfg4(dev, args, passes=1, with_e2e=True):
                 step_ms.append(e0.elapsed_time(e2))
                 fwd_ms.append(e1.elapsed_time(e2))
                 host_ms.append((t1 - t0) * 1e3)
+                host_parts.append({k: ht1[k] - ht0[k] for k in ("walk_us", "plan_us", "upload_us")})
                 ukv.append(attn.plan_stats()["unique_kv_bytes"])   # as of the last work-list update (appended rows not counted)
                 k0, k1 = ev(), ev()
                 k0.record()
@@ -553,7 +556,10 @@ def measure_cfg4(dev, args, passes=1, with_e2e=True):
            "host_us_append_and_update": {"mean": statistics.mean(host_ms) * 1e3, "median": statistics.median(host_ms) * 1e3,
                                          "max": max(host_ms) * 1e3,
                                          "mean_at_replace_steps": statistics.mean(host_ms[i] for i in churn_steps) * 1e3
-                                         if churn_steps else None},
+                                         if churn_steps else None,
+                                         "work_list_update_at_replace_steps": {
+                                             k: statistics.mean(host_parts[i][k] for i in churn_steps)
+                                             for k in ("walk_us", "plan_us", "upload_us")} if churn_steps else None},
            "step_minus_forward_us": (statistics.mean(step_ms) - statistics.mean(fwd_ms)) * 1e3,
            "us_per_step_enqueued_back_to_back": statistics.mean(pipe_ms) * 1e3 if pipe_ms else None,
            "timing": "us_per_step: every step alone on an idle GPU, so the host's append + work-list update is inside it; "

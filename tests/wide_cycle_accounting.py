@@ -12,25 +12,40 @@ from chunk_attn import cabi
 import synthetic_workloads as W
 from gpu_helpers import CabiEngine
 
-def run(name, n_seqs, shared, unique):
+def build(name, n_seqs, shared, unique):
     w = W.single_level(name, 32, 128, 64, torch.float16, n_seqs, shared, unique, 2, 0.5, "cuda")
     eng = CabiEngine(32, 128, 64, torch.float16, max_chunks=shared // 64 + 2 * n_seqs + 8)
     rows = W.populate(eng, w)
     q = w.q[rows].to("cuda", torch.float16).contiguous()
-    eng.ctx.set_option(cabi.CA_OPT_TRACE, 2)
+    return eng, q
+
+
+def traced(eng, q, mode):
+    eng.ctx.set_option(cabi.CA_OPT_TRACE, mode)
     for _ in range(5):
-        out = eng.forward(q)
+        eng.forward(q)
     torch.cuda.synchronize()
-    tr = eng.ctx.read_trace().astype(np.int64)
+    return eng.ctx.read_trace().astype(np.int64)
+
+
+def run(name, n_seqs, shared, unique):
+    eng, q = build(name, n_seqs, shared, unique)
+    # timeline of a CTA (CA_OPT_TRACE = 1): ns since the first CTA of the launch entered
+    tr = traced(eng, q, 1)
+    rel = (tr[:, :7] - tr[:, 0].min()) / 1e3
     st = eng.ctx.stats()
     tiles = st["n_items_wide"] and (shared // 64) * ((n_seqs + 127) // 128) * 32 / len(tr)
+    print(name, "ctas", len(tr), "tiles/cta %.1f" % tiles, "kernels per step", st["kernels_per_step"])
+    print("  timeline, median us (slowest CTA): " + ", ".join(
+        "%s %.2f (%.2f)" % (n, np.median(rel[:, i]), rel[:, i].max())
+        for i, n in enumerate(["entry", "set-up done", "first S", "last P", "O complete", "rows stored", "exit"])))
+    # cycles of the two serial roles (CA_OPT_TRACE = 2)
+    tr = traced(eng, q, 2)
     sm = tr[:, 7] >> 48
     tr[:, 7] &= (1 << 48) - 1
     # a CTA had the SM to itself if no other CTA of the launch ran there (one wave: lifetimes overlap)
     alone = np.array([np.sum(sm == x) == 1 for x in sm])
-    total = (tr[:, 6] - tr[:, 0])
-    print(name, "ctas", len(tr), "tiles/cta %.1f" % tiles, "cta lifetime us median %.2f" % (np.median(total) / 1e3),
-          "ctas alone on their SM:", int(alone.sum()))
+    print("  ctas alone on their SM:", int(alone.sum()))
     for nm, col in (("mma issue QK (8+2)", 2), ("mma issue PV (4+2)", 1), ("mma wait P(+V)", 3), ("mma wait K", 7),
                     ("softmax wait S", 4), ("softmax chain", 5)):
         c = tr[:, col] / tiles
@@ -38,6 +53,7 @@ def run(name, n_seqs, shared, unique):
         if alone.any() and not alone.all():
             line += "   | alone on the SM: median %6.0f, sharing it: median %6.0f" % (np.median(c[alone]), np.median(c[~alone]))
         print(line)
+
 
 run("cfg3_s4096", 64, 4096, 0)
 run("sys1024", 1024, 2048, 8)
