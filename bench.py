@@ -58,6 +58,9 @@ def parse():
                     help="wide shared runs on the tcgen05 / TMEM path: by the planner's threshold, always, never")
     ap.add_argument("--overlap", action="store_true",
                     help="run the short-tails kernel beside the wide-runs kernel (second stream) instead of before it")
+    ap.add_argument("--no-finish", action="store_true",
+                    help="short private tails always as partial rows + merge kernel (default: the short-tails kernel stores "
+                         "the output rows itself when every row has a short tail)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ref-cuda", action="store_true", help="skip timing the reference's own CUDA kernels")
     ap.add_argument("--no-scale-point", action="store_true", help="N = 1: skip the one-GPU point of the cfg5 series")
@@ -289,6 +292,8 @@ def build_engine(name, n_heads_local, dev, args, sharded=False, rank=0, keep_wor
         engine.set_option(cabi.CA_OPT_WIDE_RUNS, 2 if args.wide == "on" else 0)
     if args.overlap:
         engine.set_option(cabi.CA_OPT_OVERLAP_KERNELS, 1)
+    if args.no_finish:
+        engine.set_option(cabi.CA_OPT_FINISH_IN_TAILS, 0)
     rows = W.populate(engine, w, device=dev, dtype=torch.float16)
     q = w.q[rows].to(dev, torch.float16).contiguous()
     ukv = W.unique_kv_bytes(w)

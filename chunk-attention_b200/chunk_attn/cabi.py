@@ -16,7 +16,7 @@ CA_OK = 0
 CA_ERR_INVALID, CA_ERR_CUDA, CA_ERR_STATE, CA_ERR_DEVICE_STATUS = -1, -2, -3, -4
 CA_DTYPE_F16, CA_DTYPE_F32 = 0, 1
 CA_OPT_SPLIT_PHASES, CA_OPT_NUM_CTAS, CA_OPT_SEQ_FIRST_TENSOR, CA_OPT_TRACE, CA_OPT_DEPENDENT_LAUNCH = 1, 2, 3, 4, 5
-CA_OPT_WIDE_RUNS, CA_OPT_WAIT_LIMIT_CYCLES, CA_OPT_TEST_WITHHOLD_ITEM, CA_OPT_OVERLAP_KERNELS = 6, 7, 8, 9
+CA_OPT_WIDE_RUNS, CA_OPT_WAIT_LIMIT_CYCLES, CA_OPT_TEST_WITHHOLD_ITEM, CA_OPT_OVERLAP_KERNELS, CA_OPT_FINISH_IN_TAILS = 6, 7, 8, 9, 10
 STATUS_FULL_WAIT_TIMEOUT, STATUS_EMPTY_WAIT_TIMEOUT, STATUS_DRAIN_TIMEOUT, STATUS_BAD_WORK_LIST, STATUS_BAD_POSITION = 1, 2, 3, 4, 5
 PLAN_ITEMS = 0
 (PLAN_MERGE_OFF, PLAN_MERGE_SLOTS, PLAN_PATH_OFF, PLAN_PATH_CHUNKS, PLAN_PATH_TOKENS, PLAN_TAIL_CHUNK,

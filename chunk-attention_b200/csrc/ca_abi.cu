@@ -94,6 +94,8 @@ struct ca_context {
     unsigned long long* trace = nullptr;  // [kTraceCtas][4], allocated when tracing is switched on
     int trace_ctas = 0;                   // CTAs of the last traced launch
     int trace_cycles = 0;                 // CA_OPT_TRACE = 2: the tcgen05 kernel accounts for cycles per role instead
+    int opt_finish_in_tails = 1;          // CA_OPT_FINISH_IN_TAILS: the short-tails kernel finishes the rows when it can
+    bool out_is_host = false;             // set by ca_attention_host around its launches: the rows go to host memory
 
     ca::Plan plan;  // scratch of ca_refresh_kernel_context (vectors keep their capacity)
     // what the launches need to know about the work list that is on the device
@@ -270,6 +272,10 @@ int ca_context_set_option(ca_context* c, int option, int64_t value) {
         return CA_OK;
     } else if (option == CA_OPT_TEST_WITHHOLD_ITEM) {
         c->opt_withhold_item = value < 0 ? -1 : (int)value;
+        return CA_OK;
+    } else if (option == CA_OPT_FINISH_IN_TAILS) {
+        if (value != 0 && value != 1) return fail(CA_ERR_INVALID, "CA_OPT_FINISH_IN_TAILS takes 0 or 1");
+        c->opt_finish_in_tails = (int)value;
         return CA_OK;
     } else if (option == CA_OPT_TRACE) {
         DeviceGuard guard(c->device);
@@ -482,7 +488,22 @@ static int check_attention_args(ca_context* c, const void* q, int n_seqs) {
     return CA_OK;
 }
 
-int ca_attn_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_stream stream_) {
+// True when the short-tails kernel finishes the step's rows itself: every row has a short tail item, and the batch is
+// one where that pays.  Measured on B200: 6-8 % of the step at 256 rows x 32 heads (a launch less), nothing at 1024
+// rows, -3 % at 2048 rows (the kernel is bound by the latency of its lookups, and the merge kernel hides that better
+// at its higher occupancy); with the output rows going to HOST memory it is 15-35 % of the end-to-end time at every size
+// (whole 256-byte rows per half-warp cross the bus better than the merge kernel's stores).
+static bool tails_can_finish(const ca_context* c) {
+    return c->fast && c->opt_finish_in_tails && !c->opt_overlap && !c->meta.split_phases && c->meta.n_items_short > 0 &&
+           c->meta.n_items_short == c->meta.n_seqs &&
+           (c->out_is_host || (long long)c->meta.n_seqs * c->geo.n_heads <= 32768);
+}
+
+// The partial results of a step.  finish != null and tails_can_finish(): the short-tails kernel goes LAST and stores the
+// output rows described by *finish; *finished tells the caller that no merge is needed.
+static int run_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_stream stream_, const ca::MergeParams* finish,
+                        bool* finished) {
+    if (finished) *finished = false;
     int rc = check_attention_args(c, q, n_seqs);
     if (rc != CA_OK) return rc;
     if (!c->fast) return fail(CA_ERR_INVALID, "partials exist only for fp16 / d_head 128 / chunk_size 64");
@@ -530,7 +551,9 @@ int ca_attn_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_st
     // first (the short tails before the wide runs, whose set-up then overlaps them) so that the persistent kernel's
     // tail leads straight into the merge.
     const int n_items = c->meta.n_items - c->meta.n_items_short - c->meta.n_items_wide;
-    const bool run_short = c->meta.n_items_short > 0 && (phases & 2) && !(c->meta.short_all_empty && c->delta_tokens == 0);
+    const bool finish_in_tails = finish && finished && phases == 3 && tails_can_finish(c);
+    const bool run_short = !finish_in_tails && c->meta.n_items_short > 0 && (phases & 2) &&
+                           !(c->meta.short_all_empty && c->delta_tokens == 0);
     const bool run_wide = c->meta.n_items_wide > 0 && (phases & 1);
     // The short tails are bound by memory, the wide runs by the tensor and special-function pipes, and they touch
     // disjoint partial rows: optionally (CA_OPT_OVERLAP_KERNELS) the short-tails kernel runs on a second stream
@@ -580,7 +603,33 @@ int ca_attn_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_st
         if (phases & 1) CA_CUDA(launch(0, c->meta.n_items_cf));
         if (phases & 2) CA_CUDA(launch(c->meta.n_items_cf, n_items));
     }
+    if (finish_in_tails) {
+        p.item_lo = n_items * H;
+        p.item_hi = (n_items + c->meta.n_items_short) * H;
+        CA_CUDA(ca::launch_attn_short_tails(p, stream, (c->opt_pdl & 2) != 0, finish));
+        *finished = true;
+    }
     return CA_OK;
+}
+
+int ca_attn_partials(ca_context* c, const void* q, int n_seqs, int phases, ca_stream stream_) {
+    return run_partials(c, q, n_seqs, phases, stream_, nullptr, nullptr);
+}
+
+static ca::MergeParams merge_params_of(const ca_context* c, void* out, int n_seqs) {
+    ca::MergeParams m;
+    m.part_o = c->part_o;
+    m.part_ml = c->part_ml;
+    m.merge_off = c->d_merge_off;
+    m.merge_slots = c->d_merge_slots;
+    m.out = out;
+    m.n_pairs = n_seqs * c->geo.n_heads;
+    m.n_merge_entries = (long long)c->meta.n_merge_slots;
+    m.max_list = c->meta.max_merge_len;
+    m.n_slots = c->meta.stats.n_slots;
+    m.status = c->status;
+    m.n_heads = c->geo.n_heads;
+    return m;
 }
 
 namespace {
@@ -642,7 +691,9 @@ int ca_attention_host(ca_context* c, const void* q_host, void* out_host, int n_s
         CA_CUDA(grow_host(c->host_out_stage, c->host_out_cap));
         if (!device_view_of_host(c->host_out_stage, &out_dev)) return fail(CA_ERR_CUDA, "pinned staging buffer is not mapped");
     }
+    c->out_is_host = true;
     int rc = ca_attention(c, c->q_stage, out_dev, n_seqs, partition, stream_);
+    c->out_is_host = false;
     if (rc != CA_OK) return rc;
     CA_CUDA(cudaStreamSynchronize(stream));
     if (!direct) std::memcpy(out_host, c->host_out_stage, bytes);
@@ -656,18 +707,7 @@ int ca_attn_merge(ca_context* c, void* out, int n_seqs, ca_stream stream_) {
     if (n_seqs == 0) return CA_OK;
     DeviceGuard guard(c->device);
     if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
-    ca::MergeParams m;
-    m.part_o = c->part_o;
-    m.part_ml = c->part_ml;
-    m.merge_off = c->d_merge_off;
-    m.merge_slots = c->d_merge_slots;
-    m.out = out;
-    m.n_pairs = n_seqs * c->geo.n_heads;
-    m.n_merge_entries = (long long)c->meta.n_merge_slots;
-    m.max_list = c->meta.max_merge_len;
-    m.n_slots = c->meta.stats.n_slots;
-    m.status = c->status;
-    m.n_heads = c->geo.n_heads;
+    const ca::MergeParams m = merge_params_of(c, out, n_seqs);
     CA_CUDA(ca::launch_attn_merge(m, static_cast<cudaStream_t>(stream_), (c->opt_pdl & 1) != 0));
     return CA_OK;
 }
@@ -702,27 +742,18 @@ int ca_attention_to_peers(ca_context* c, const void* q, void* const* peer_out, i
         if (!peer_out[i] || reinterpret_cast<uintptr_t>(peer_out[i]) % 16) return fail(CA_ERR_INVALID, "null or misaligned peer output");
     if (reinterpret_cast<uintptr_t>(multicast_out) % 16) return fail(CA_ERR_INVALID, "misaligned multicast output");
     if (n_seqs == 0) return CA_OK;
-    rc = ca_attn_partials(c, q, n_seqs, 3, stream_);
-    if (rc != CA_OK) return rc;
-    DeviceGuard guard(c->device);
-    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
-    ca::MergeParams m;
-    m.part_o = c->part_o;
-    m.part_ml = c->part_ml;
-    m.merge_off = c->d_merge_off;
-    m.merge_slots = c->d_merge_slots;
-    m.out = nullptr;
-    m.n_pairs = n_seqs * c->geo.n_heads;
-    m.n_merge_entries = (long long)c->meta.n_merge_slots;
-    m.max_list = c->meta.max_merge_len;
-    m.n_slots = c->meta.stats.n_slots;
-    m.status = c->status;
-    m.n_heads = c->geo.n_heads;
+    ca::MergeParams m = merge_params_of(c, nullptr, n_seqs);
     m.n_peers = n_peers;
     m.total_heads = total_heads;
     m.head_offset = head_offset;
     for (int i = 0; i < n_peers; i++) m.peer_out[i] = peer_out[i];
     m.mc_out = multicast_out;
+    bool finished = false;
+    rc = run_partials(c, q, n_seqs, 3, stream_, &m, &finished);
+    if (rc != CA_OK) return rc;
+    if (finished) return CA_OK;
+    DeviceGuard guard(c->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
     CA_CUDA(ca::launch_attn_merge(m, static_cast<cudaStream_t>(stream_), (c->opt_pdl & 1) != 0));
     return CA_OK;
 }
@@ -770,8 +801,10 @@ int ca_attention(ca_context* c, const void* q, void* out, int n_seqs, int partit
     if (n_seqs == 0) return CA_OK;
     if (!out) return fail(CA_ERR_INVALID, "out is null");
     if (c->fast && partition != CA_PARTITION_SEQ_FIRST) {
-        rc = ca_attn_partials(c, q, n_seqs, 3, stream_);
-        if (rc != CA_OK) return rc;
+        const ca::MergeParams m = merge_params_of(c, out, n_seqs);
+        bool finished = false;
+        rc = run_partials(c, q, n_seqs, 3, stream_, &m, &finished);
+        if (rc != CA_OK || finished) return rc;
         return ca_attn_merge(c, out, n_seqs, stream_);
     }
     DeviceGuard guard(c->device);
@@ -945,7 +978,8 @@ int ca_context_stats(const ca_context* c, ca_plan_stats* out) {
     if (!c || !out) return fail(CA_ERR_INVALID, "null argument");
     if (!c->valid) return fail(CA_ERR_STATE, "work list is stale");
     *out = c->meta.stats;
-    if (c->meta.short_all_empty && c->delta_tokens == 0) out->kernels_per_step -= 1;  // nothing to do for empty tails
+    if (tails_can_finish(c)) out->kernels_per_step -= 1;  // the short-tails kernel stores the rows: no merge launch
+    else if (c->meta.short_all_empty && c->delta_tokens == 0) out->kernels_per_step -= 1;  // nothing to do for empty tails
     return CA_OK;
 }
 

@@ -789,11 +789,20 @@ __global__ void __launch_bounds__(NUM_THREADS, 2) attn_partial_kernel(const Part
 // softmax needs no further exchange) and 16 bytes = 8 output elements of each V row.  The result is an
 // ordinary partial (max and sum in log2 units, un-normalised O), combined with the row's other partials by
 // the merge kernel.
+// FINISH: when EVERY row of the batch has such a tail (many requests with short suffixes over shared prompts) the
+// kernel runs LAST in the step and finishes the rows itself: the half-warp keeps its partial in registers, fetches
+// the row's other partials (the shared runs', written by the kernels before it), combines, normalises and stores the
+// fp16 output row — the tail's partial never travels through memory and the merge kernel is not launched.
+__device__ __forceinline__ int checked_slot(const MergeParams& p, int entry, int head);
+__device__ __forceinline__ void checked_bounds(const MergeParams& p, int& b, int& e);
+__device__ __forceinline__ void store_row8(const MergeParams& p, int row, int head, int g, const float (&o)[8], float inv);
+
 constexpr int SHORT_WARPS = 4;   // small CTAs: they fit beside the wide-runs kernel's CTAs when the two overlap
 constexpr int SHORT_ITEMS_PER_CTA = 2 * SHORT_WARPS;
 constexpr int SHORT_BLOCK = 8;   // tokens per round
 
-__global__ void __launch_bounds__(SHORT_WARPS * 32, 4) attn_short_tails_kernel(const PartialParams p) {
+template <bool FINISH>
+__global__ void __launch_bounds__(SHORT_WARPS * 32, 4) attn_short_tails_kernel(const PartialParams p, const MergeParams mp) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -818,6 +827,19 @@ __global__ void __launch_bounds__(SHORT_WARPS * 32, 4) attn_short_tails_kernel(c
         }
     }
     const int nt_warp = max(nt, __shfl_xor_sync(0xffffffffu, nt, 16));
+    // FINISH: where the row's other partials are is looked up now, in the shadow of the tail's own loads
+    constexpr int AHEAD = 4;   // lists of up to four other pieces cost one round trip after the tail
+    int lb = 0, le = 0, sl[AHEAD];
+#pragma unroll
+    for (int u = 0; u < AHEAD; u++) sl[u] = -1;
+    if (FINISH && slot >= 0) {
+        lb = __ldg(mp.merge_off + row);
+        le = __ldg(mp.merge_off + row + 1);
+        checked_bounds(mp, lb, le);
+#pragma unroll
+        for (int u = 0; u < AHEAD; u++)
+            if (lb + u < le) sl[u] = __ldg(mp.merge_slots + lb + u);   // entries; checked when they are used
+    }
     const uint8_t* ktile = p.pool + ((size_t)chunk * p.n_heads + head) * (size_t)FAST_STAGE_BYTES;
     const uint8_t* vtile = ktile + FAST_TILE_BYTES;
     uint4 qraw = make_uint4(0u, 0u, 0u, 0u);
@@ -893,12 +915,56 @@ __global__ void __launch_bounds__(SHORT_WARPS * 32, 4) attn_short_tails_kernel(c
         }
     }
     if (slot < 0) return;
-    if (nt > 0) {
-        float4* dst = reinterpret_cast<float4*>(p.part_o + (size_t)slot * FAST_D + 8 * g);
-        dst[0] = make_float4(o[0], o[1], o[2], o[3]);
-        dst[1] = make_float4(o[4], o[5], o[6], o[7]);
+    if (!FINISH) {
+        if (nt > 0) {
+            float4* dst = reinterpret_cast<float4*>(p.part_o + (size_t)slot * FAST_D + 8 * g);
+            dst[0] = make_float4(o[0], o[1], o[2], o[3]);
+            dst[1] = make_float4(o[4], o[5], o[6], o[7]);
+        }
+        if (g == 0) p.part_ml[slot] = make_float2(nt > 0 ? m : NEG_BIG, l);  // an empty reserved tail: (none, 0)
+        return;
     }
-    if (g == 0) p.part_ml[slot] = make_float2(nt > 0 ? m : NEG_BIG, l);  // an empty reserved tail: (none, 0)
+    // ---- the row's other partials (no shuffles from here on: half-warps proceed on their own)
+    if (nt == 0) m = NEG_BIG;
+    for (int b = lb; b < le; b += AHEAD) {
+        if (b > lb) {
+#pragma unroll
+            for (int u = 0; u < AHEAD; u++) sl[u] = b + u < le ? __ldg(mp.merge_slots + b + u) : -1;
+        }
+        float2 ml[AHEAD];
+        float4 v[AHEAD][2];
+#pragma unroll
+        for (int u = 0; u < AHEAD; u++) {
+            ml[u] = make_float2(NEG_BIG, 0.f);
+            v[u][0] = v[u][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (b + u < le) {
+                const int s = checked_slot(mp, sl[u], head);
+                if (s >= 0 && s != slot) {   // this half-warp's own piece is in its registers
+                    ml[u] = mp.part_ml[s];
+                    const float4* src = reinterpret_cast<const float4*>(mp.part_o + (size_t)s * FAST_D + 8 * g);
+                    v[u][0] = src[0];
+                    v[u][1] = src[1];
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < AHEAD; u++) {
+            if (!(ml[u].y > 0.f)) continue;   // no piece, this half-warp's own, or one without tokens (it has no O row)
+            const float mn = fmaxf(m, ml[u].x);
+            const float a = fast_exp2(m - mn), w = fast_exp2(ml[u].x - mn);
+            m = mn;
+            l = l * a + ml[u].y * w;
+            o[0] = o[0] * a + v[u][0].x * w;
+            o[1] = o[1] * a + v[u][0].y * w;
+            o[2] = o[2] * a + v[u][0].z * w;
+            o[3] = o[3] * a + v[u][0].w * w;
+            o[4] = o[4] * a + v[u][1].x * w;
+            o[5] = o[5] * a + v[u][1].y * w;
+            o[6] = o[6] * a + v[u][1].z * w;
+            o[7] = o[7] * a + v[u][1].w * w;
+        }
+    }
+    store_row8(mp, row, head, g, o, l > 0.f ? 1.f / l : 0.f);  // a row with no token yields zeros
 }
 
 // The un-normalised combination of the partials merge_slots[b .. e) by one warp: on return mm is their
@@ -1035,6 +1101,29 @@ __device__ __forceinline__ void store_row(const MergeParams& p, int pair, int la
 #pragma unroll
             for (int i = 0; i < MERGE_MAX_PEERS; i++)
                 if (i < p.n_peers) *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.peer_out[i]) + off) = packed;
+        }
+    }
+}
+
+// The same for a lane that owns eight consecutive output elements (granule g of the row)
+__device__ __forceinline__ void store_row8(const MergeParams& p, int row, int head, int g, const float (&o)[8], float inv) {
+    uint4 packed;
+    packed.x = pack_half2(o[0] * inv, o[1] * inv);
+    packed.y = pack_half2(o[2] * inv, o[3] * inv);
+    packed.z = pack_half2(o[4] * inv, o[5] * inv);
+    packed.w = pack_half2(o[6] * inv, o[7] * inv);
+    if (p.n_peers == 0) {
+        *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.out) + ((size_t)row * p.n_heads + head) * FAST_D + 8 * g) = packed;
+    } else {
+        const size_t off = ((size_t)row * p.total_heads + p.head_offset + head) * FAST_D + 8 * g;
+        if (p.mc_out) {
+            asm volatile("multimem.st.weak.global.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(reinterpret_cast<__half*>(p.mc_out) + off),
+                         "r"(packed.x), "r"(packed.y), "r"(packed.z), "r"(packed.w)
+                         : "memory");
+        } else {
+#pragma unroll
+            for (int i = 0; i < MERGE_MAX_PEERS; i++)
+                if (i < p.n_peers) *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.peer_out[i]) + off) = packed;
         }
     }
 }
@@ -1288,7 +1377,7 @@ cudaError_t launch_attn_partials(const PartialParams& p, int n_ctas, cudaStream_
     return err;
 }
 
-cudaError_t launch_attn_short_tails(const PartialParams& p, cudaStream_t stream, bool dependent_launch) {
+cudaError_t launch_attn_short_tails(const PartialParams& p, cudaStream_t stream, bool dependent_launch, const MergeParams* finish) {
     const int n = p.item_hi - p.item_lo;
     if (n <= 0) return cudaSuccess;
     static const bool pdl_disabled = std::getenv("CA_DISABLE_PDL") != nullptr;
@@ -1302,11 +1391,13 @@ cudaError_t launch_attn_short_tails(const PartialParams& p, cudaStream_t stream,
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (dependent_launch && !pdl_disabled) ? 1 : 0;
-    cudaError_t err = cudaLaunchKernelEx(&cfg, attn_short_tails_kernel, p);
+    auto* kernel = finish ? attn_short_tails_kernel<true> : attn_short_tails_kernel<false>;
+    const MergeParams mp = finish ? *finish : MergeParams{};
+    cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, p, mp);
     if (err != cudaSuccess && cfg.numAttrs == 1) {
         (void)cudaGetLastError();
         cfg.numAttrs = 0;
-        err = cudaLaunchKernelEx(&cfg, attn_short_tails_kernel, p);
+        err = cudaLaunchKernelEx(&cfg, kernel, p, mp);
     }
     return err;
 }

@@ -58,8 +58,12 @@ struct PartialParams {
 // grid = n_ctas (FAST_CTAS_PER_SM per SM).
 // dependent_launch: allow the CTAs to be set up while the preceding kernel of the stream is finishing
 cudaError_t launch_attn_partials(const PartialParams& p, int n_ctas, cudaStream_t stream, bool dependent_launch = false);
-// one warp per item over items [item_lo, item_hi): single-tile one-row items only (short private tails)
-cudaError_t launch_attn_short_tails(const PartialParams& p, cudaStream_t stream, bool dependent_launch = false);
+// one half-warp per item over items [item_lo, item_hi): single-tile one-row items only (short private tails).
+// finish != null: every row of the batch has such an item and every other partial of the step is already in the
+// stream; the kernel then combines each row's partials itself and stores the output rows (no merge launch follows)
+struct MergeParams;
+cudaError_t launch_attn_short_tails(const PartialParams& p, cudaStream_t stream, bool dependent_launch = false,
+                                    const MergeParams* finish = nullptr);
 cudaError_t configure_fast_kernels();  // once per device before the first launch
 
 // ---- wide shared runs on tcgen05 / TMEM (ca_attn_wide.cu): one CTA per item ---------------------------------

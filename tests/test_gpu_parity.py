@@ -273,6 +273,63 @@ def test_rows_written_into_peer_outputs():
         eng.ctx.attention_to_peers(q, [peers[0].data_ptr()], 6, 4)   # the slice does not fit in 6 heads
 
 
+@pytest.mark.parametrize("levels", [1, 2])
+def test_tails_kernel_finishes_the_rows(levels):
+    # every row has a short private tail: the short-tails kernel runs last, combines each row's partials in registers
+    # and stores the output (device buffer, peers' buffers, host memory) -- against the same step with the merge
+    # kernel, against the oracle, through appended tokens and with empty tails
+    H = 4
+    if levels == 1:
+        w = W.single_level("fin", H, 128, 64, torch.float16, 40, 5 * 64, 17, 96, 0.5)
+    else:   # root + four groups + a few private tokens: five and more partials per row
+        gen = torch.Generator().manual_seed(97)
+        mk = lambda toks: W.Segment(toks, torch.randn(len(toks), H, 128, generator=gen) * 0.5, torch.randn(len(toks), H, 128, generator=gen) * 0.5)
+        root = mk(list(range(7 * 64)))
+        groups = [mk([10_000 * (g + 1) + j for j in range(3 * 64)]) for g in range(4)]
+        w = W.Workload("fin2", H, 128, 64, torch.float16, 97, 0.5)
+        for s in range(44):
+            w.seqs.append([root, groups[s % 4], mk([1_000_000 * (s + 1) + j for j in range(1 + s % 9)])])
+        w.q = torch.randn(44, H, 128, generator=gen) * 0.5
+    eng = fast_engine(H=H, max_chunks=1024)
+    eng.ctx.set_option(cabi.CA_OPT_NUM_CTAS, 2)      # few CTAs: the tails are many by comparison and take their own kernel
+    ora, orows = oracle_for(w)
+    rows = W.populate(eng, w)
+    assert rows == orows
+    n = len(rows)
+    q = w.q[rows].to("cuda", torch.float16).contiguous()
+    eng.ctx.set_option(cabi.CA_OPT_FINISH_IN_TAILS, 0)
+    merged = eng.forward(q)
+    st0 = eng.ctx.stats()
+    assert st0["n_items_short"] == n * H
+    eng.ctx.set_option(cabi.CA_OPT_FINISH_IN_TAILS, 1)
+    out = eng.forward(q)
+    assert eng.ctx.stats()["kernels_per_step"] == st0["kernels_per_step"] - 1
+    assert (out.float() - merged.float()).abs().max().item() < 5e-4
+    ref = ora.forward(round_to(w.q[rows], torch.float16).numpy(), 0)
+    assert max_abs(out.float().cpu().numpy(), ref) < TOL_F16
+    # into two "ranks'" full-width buffers
+    total_heads, head_offset = 12, 4
+    peers = [torch.full((n, total_heads, 128), float("nan"), dtype=torch.float16, device="cuda") for _ in range(2)]
+    eng.ctx.attention_to_peers(q, [p.data_ptr() for p in peers], total_heads, head_offset)
+    torch.cuda.synchronize()
+    for p in peers:
+        assert torch.equal(p[:, head_offset:head_offset + H], out)
+        assert torch.isnan(p[:, :head_offset]).all() and torch.isnan(p[:, head_offset + H:]).all()
+    # into host memory
+    q_host, out_host = q.cpu().pin_memory(), torch.empty(n, H, 128, dtype=torch.float16).pin_memory()
+    eng.ctx.attention_host(q_host, out_host)
+    assert torch.equal(out_host, out.cpu())
+    # appended tokens (the work list is not rebuilt) ...
+    g = torch.Generator().manual_seed(98)
+    for step in range(3):
+        nk, nv = (torch.randn(n, H, 128, generator=g) * 0.5 for _ in range(2))
+        eng.append_token([5_000_000 + step] * n, nk, nv)
+        ora.append_token([5_000_000 + step] * n, round_to(nk, torch.float16).numpy(), round_to(nv, torch.float16).numpy())
+    out = eng.forward(q)
+    assert max_abs(out.float().cpu().numpy(), ora.forward(round_to(w.q[rows], torch.float16).numpy(), 0)) < TOL_F16
+    assert eng.ctx.status() == 0
+
+
 # ---- the drop-in class ------------------------------------------------------------------------------------
 def test_attention_class_matches_cabi_engine_and_reference_api():
     torch.set_default_dtype(torch.float32)

@@ -16,11 +16,13 @@ TOL = 1e-3
 class Mirror:
     """Row-ordered list of (tokens, k, v) histories kept next to the engine."""
 
-    def __init__(self, H, seed, memory_mb=1024, wide=None):
+    def __init__(self, H, seed, memory_mb=1024, wide=None, finish=None):
         self.H, self.d = H, 128
         self.attn = Attention(n_heads=H, d_head=128, chunk_size=64, memory_mb=memory_mb, dtype=torch.float16, device=DEV)
         if wide is not None:   # 2: every shared run on the tcgen05 kernel, 0: none (default: the planner decides)
             self.attn.set_option(cabi.CA_OPT_WIDE_RUNS, wide)
+        if finish is not None:  # 0: the short-tails kernel writes partial rows and the merge kernel always runs
+            self.attn.set_option(cabi.CA_OPT_FINISH_IN_TAILS, finish)
         self.g = torch.Generator(device=DEV).manual_seed(seed)
         self.rows = []
         self.next_token = 1
@@ -140,34 +142,37 @@ def test_one_very_long_sequence_and_short_neighbours():
     m.check()
 
 
-def test_many_short_tails_take_the_warp_per_item_kernel():
-    """400 rows whose private part is a fraction of one chunk: their items go to the warp-per-item kernel
-    (plan_stats n_items_short), through appended tokens without a rebuild and across the chunk boundary."""
-    m = Mirror(4, 13, memory_mb=512)
+@pytest.mark.parametrize("finish", [1, 0])
+def test_many_short_tails_take_the_warp_per_item_kernel(finish):
+    """400 rows whose private part is a fraction of one chunk: their items go to the half-warp-per-item kernel
+    (plan_stats n_items_short), through appended tokens without a rebuild and across the chunk boundary; with
+    finish = 1 that kernel also combines the rows' partials and stores the output whenever every row has such a tail."""
+    m = Mirror(4, 13, memory_mb=512, finish=finish)
     rnd = random.Random(13)
     m.add(None, 0, 256 + 3)
     for _ in range(399):
         m.add(0, 256, rnd.randint(1, 60))
     m.check()
     st = m.attn.plan_stats()
-    assert st["n_items_short"] >= 390 * 4 and st["kernels_per_step"] == 3
+    assert st["n_items_short"] >= 390 * 4
+    assert st["kernels_per_step"] == (2 if finish and st["n_items_short"] == 400 * 4 else 3)
     for step in range(70):  # every tail fills up and gets a successor on the way
         m.append_all()
         if step % 10 == 9:
             m.check()
     # rows without any shared prefix, all short: the persistent kernel has nothing to do
-    m2 = Mirror(4, 14, memory_mb=512)
+    m2 = Mirror(4, 14, memory_mb=512, finish=finish)
     for _ in range(320):
         m2.add(None, 0, rnd.randint(1, 64))
     m2.check()
     assert m2.attn.plan_stats()["n_items_short"] >= 300 * 4  # (a row of exactly 64 tokens has a full chunk + an empty tail)
 
 
-@pytest.mark.parametrize("wide", [0, 2])
-def test_large_batch_of_short_lists_takes_the_eight_lane_merge(wide):
+@pytest.mark.parametrize("wide,finish", [(0, 0), (2, 0), (0, 1), (2, 1)])
+def test_large_batch_of_short_lists_takes_the_eight_lane_merge(wide, finish):
     """600 rows over one 256-token prefix, a few private tokens each: 2400 (row, head) pairs of two to four pieces,
     the shape the eight-lanes-per-pair merge kernel serves; appended tokens and a removed row on the way."""
-    m = Mirror(4, 21, memory_mb=1024, wide=wide)
+    m = Mirror(4, 21, memory_mb=1024, wide=wide, finish=finish)
     rnd = random.Random(21)
     m.add(None, 0, 256 + 2)
     for _ in range(599):

@@ -140,12 +140,17 @@ def test_many_requests_over_one_system_prompt():
     st = attn.plan_stats()
     # 8 row blocks x 8 heads, each cut into as many pieces as fill one wave of CTAs
     assert st["n_items_wide"] > 0 and st["n_items_wide"] % 64 == 0 and st["n_items_cf"] == 0
-    assert st["n_items_short"] == 1024 * 8 and st["kernels_per_step"] == 3
+    # ... and the short-tails kernel, last in the step, stores the output rows itself: no merge launch
+    assert st["n_items_short"] == 1024 * 8 and st["kernels_per_step"] == 2
     gen = attn.forward(q=q, partition=2)
     assert (out.float() - gen.float()).abs().max().item() < TOL_F16
     g = torch.Generator().manual_seed(4)
     pairs = [(int(torch.randint(0, 1024, (1,), generator=g)), int(torch.randint(0, 8, (1,), generator=g))) for _ in range(8)]
     assert dense_rows(w, rows, out, q, pairs) < TOL_F16
+    attn.set_option(cabi.CA_OPT_FINISH_IN_TAILS, 0)      # the same step with partial rows for the tails and the merge kernel
+    out3 = attn.forward(q=q)
+    assert attn.plan_stats()["kernels_per_step"] == 3
+    assert (out.float() - out3.float()).abs().max().item() < 5e-4
     assert attn.device_status() == 0
 
 
