@@ -496,7 +496,10 @@ static int check_attention_args(ca_context* c, const void* q, int n_seqs) {
 static bool tails_can_finish(const ca_context* c) {
     return c->fast && c->opt_finish_in_tails && !c->opt_overlap && !c->meta.split_phases && c->meta.n_items_short > 0 &&
            c->meta.n_items_short == c->meta.n_seqs &&
-           (c->out_is_host || (long long)c->meta.n_seqs * c->geo.n_heads <= 32768);
+           (c->out_is_host || ((long long)c->meta.n_seqs * c->geo.n_heads <= 32768 &&
+                               // tails that are all empty cost no launch of their own: nothing to save (a fully shared
+                               // batch of 64 x 32 pairs with nine pieces each: 16.8 us with the merge kernel, 18.0 without)
+                               !(c->meta.short_all_empty && c->delta_tokens == 0)));
 }
 
 // The partial results of a step.  finish != null and tails_can_finish(): the short-tails kernel goes LAST and stores the

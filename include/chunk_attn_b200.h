@@ -116,8 +116,8 @@ CA_API void ca_context_destroy(ca_context* ctx);
  * on B200 the two orders take the same time within 3 %, the wide kernel's CTAs leave little room beside them. */
 #define CA_OPT_OVERLAP_KERNELS 9
 /* 1 (default): when EVERY row of the batch has a short private tail (the serving shape: many requests with short
- * suffixes over shared prompts) and the batch has at most 32 768 (row, head) pairs -- or the output goes to host
- * memory (ca_attention_host) --, the short-tails kernel runs last in ca_attention / ca_attention_host /
+ * suffixes over shared prompts), the tails are not all empty and the batch has at most 32 768 (row, head) pairs --
+ * or the output goes to host memory (ca_attention_host) --, the short-tails kernel runs last in ca_attention / ca_attention_host /
  * ca_attention_to_peers, keeps each tail's partial in registers, combines it with the row's other partials and
  * stores the output rows itself: no merge launch, and the tails' partials never travel through memory.
  * 0: the tails are written as partial rows and the merge kernel combines them. */
