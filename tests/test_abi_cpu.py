@@ -25,6 +25,18 @@ def test_header_and_library_agree():
         assert hasattr(cabi.lib, name), name
 
 
+def test_header_constants_match_the_ctypes_binding():
+    # every CA_OPT_*, CA_ERR_*, CA_DTYPE_* and CA_PARTITION_* the header defines has the same value in cabi.py
+    text = open(os.path.join(ROOT, "include", "chunk_attn_b200.h")).read()
+    defines = dict(re.findall(r"^#define\s+(CA_(?:OPT|ERR|DTYPE|PARTITION)_\w+)\s+\(?(-?\d+)\)?\s*$", text, re.M))
+    assert len([k for k in defines if k.startswith("CA_OPT_")]) >= 10
+    for name, value in defines.items():
+        if hasattr(cabi, name):
+            assert getattr(cabi, name) == int(value), name
+    for name in ("CA_OPT_WIDE_RUNS", "CA_OPT_WAIT_LIMIT_CYCLES", "CA_OPT_TRACE", "CA_OPT_FINISH_IN_TAILS", "CA_OPT_NUM_CTAS"):
+        assert name in defines and hasattr(cabi, name), name
+
+
 def test_host_only_entry_points():
     assert cabi.lib.ca_version() >= 100
     assert cabi.lib.ca_chunk_bytes(32, 128, 64, cabi.CA_DTYPE_F16) == 1 << 20
