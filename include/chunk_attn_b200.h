@@ -304,7 +304,8 @@ CA_API int ca_rotary_embedding(const int64_t* positions, void* query, void* key,
  *   q, out          [n_seqs, n_heads, 128] fp16, contiguous
  *   items, merge_off, merge_slots   the work list: the arrays ca_plan_build produces with wide_runs = 0
  *                   (this entry point launches the persistent kernel only)
- *                   (CA_PLAN_ITEMS with n_items entries of 16 ints, CA_PLAN_MERGE_OFF,
+ *                   (CA_PLAN_ITEMS with n_items entries of 16 ints -- the array holds every item once for all
+ *                   heads, so n_items = ca_plan_stats.n_items / n_heads --, CA_PLAN_MERGE_OFF,
  *                   CA_PLAN_MERGE_SLOTS), copied to the device by the caller
  *   n_ctas          persistent CTAs to launch (ca_plan_stats.n_ctas)
  *   n_slots         ca_plan_stats.n_slots of that plan; above CA_STATIC_MAX_SLOTS the call is refused
@@ -343,11 +344,14 @@ CA_API int ca_attention_static_status(int32_t* status, ca_stream stream);
 /* ---- host-only planner (no GPU needed) -------------------------------------------------------
  * The work-list builder used by ca_refresh_kernel_context, exposed so that it can be checked on
  * a machine without a GPU.  Arrays are owned by the plan. */
-#define CA_PLAN_ITEMS 0          /* int32[n_items][16]: n_tiles, head, row_begin, n_rows, slot_base,
-                                    flags (bit0: last tile is a tail; bits 8..: token splits, 0 =
-                                    CUDA-core walk), last_tokens, pool slots of up to 9 tiles      */
-#define CA_PLAN_MERGE_OFF 3      /* int32[n_seqs * n_heads + 1]                                  */
-#define CA_PLAN_MERGE_SLOTS 4    /* int32[]                                                      */
+#define CA_PLAN_ITEMS 0          /* int32[][16], every item ONCE for all heads (the kernels expand: piece v is
+                                    item v / n_heads for head v % n_heads): n_tiles, 0, row_begin, n_rows,
+                                    slot_base (head h's partial rows start at slot_base * n_heads + h, stride
+                                    n_heads), flags (bit 0: last tile is a tail; bit 1: an item of the tcgen05
+                                    kernel; bits 8..: token splits, 0 = CUDA-core walk), last_tokens, pool slots
+                                    of up to 9 tiles (wide item: offset into CA_PLAN_WIDE_CHUNKS)                */
+#define CA_PLAN_MERGE_OFF 3      /* int32[n_seqs + 1]: one list per ROW, shared by the row's heads               */
+#define CA_PLAN_MERGE_SLOTS 4    /* int32[]: partial rows as numbered per item; head h's is entry * n_heads + h  */
 #define CA_PLAN_PATH_OFF 5       /* int32[n_seqs + 1]   (sequence-first-only path lists)         */
 #define CA_PLAN_PATH_CHUNKS 6    /* int32[]: pool slots root -> leaf                             */
 #define CA_PLAN_PATH_TOKENS 7    /* int32[]: tokens in that chunk at refresh                     */
