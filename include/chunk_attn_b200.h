@@ -158,7 +158,8 @@ CA_API int ca_attention_host(ca_context* ctx, const void* q_host, void* out_host
                              ca_stream stream);
 
 /* Head-sharded variant of ca_attention (one process per GPU, this context holds n_heads of
- * total_heads, starting at head_offset): the merge kernel writes every output row straight into
+ * total_heads, starting at head_offset): the last kernel of the step (the merge kernel, or the short-tails
+ * kernel when it finishes the rows, CA_OPT_FINISH_IN_TAILS) writes every output row straight into
  * each rank's full-width buffer peer_out[i], fp16 [n_seqs, total_heads, d_head], with plain stores
  * to peer memory over NVLink — compute and gather in one kernel, no collective library call.
  * peer_out is a HOST array of n_peers (<= 8) device pointers that this GPU can address (the rank's
@@ -249,14 +250,16 @@ typedef struct ca_plan_stats {
     int32_t n_chunks;          /* live non-root chunks, empty tails included                      */
     int32_t n_shared_chunks;   /* chunks walked by the chunk-first phase                          */
     int32_t n_runs;            /* maximal chains of shared chunks with identical sharers          */
-    int32_t n_items;           /* self-scheduled pieces of work (at most 9 tiles each)            */
-    int32_t n_slots;           /* partial rows                                                    */
+    int32_t n_items;           /* pieces of work, (item, head) pairs (at most 9 tiles each); the item
+                                  array itself holds n_items / n_heads entries                    */
+    int32_t n_slots;           /* partial rows, all heads                                         */
     int32_t n_ctas;            /* persistent CTAs launched                                        */
     int32_t fast_path;         /* 1 when the tensor-core/TMA kernels serve this geometry          */
-    int32_t kernels_per_step;  /* launches one ca_attention call makes                            */
+    int32_t kernels_per_step;  /* launches one ca_attention call makes (from ca_context_stats: as the
+                                  context would launch them now, options and appended tokens included) */
     int32_t n_items_cf;        /* how many items are chunk-first items (they come first)          */
     int32_t n_items_short;     /* how many items, after the persistent kernel's, are short private tails
-                                  walked by the warp-per-item kernel instead of the persistent one */
+                                  walked by the half-warp-per-item kernel instead of the persistent one */
     int32_t n_items_wide;      /* how many items, at the end of the list, are pieces of wide shared runs
                                   for the tcgen05 / TMEM kernel                                       */
 } ca_plan_stats;
