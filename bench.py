@@ -439,7 +439,7 @@ def measure_cfg4(dev, args, passes=1, with_e2e=True):
     import synthetic_workloads as W
     attn = Attention(n_heads=32, d_head=128, chunk_size=64, memory_mb=1400, dtype=torch.float16, device=dev)
     ev = lambda: torch.cuda.Event(enable_timing=True)
-    step_ms, fwd_ms, kern_ms, host_ms, ukv, e2e_ms, pipe_ms, host_parts = [], [], [], [], [], [], [], []
+    step_ms, fwd_ms, kern_ms, host_ms, ukv, e2e_ms, pipe_ms, host_parts, pipe_host_ms = [], [], [], [], [], [], [], [], []
     parity = {"max_abs": 0.0, "samples": 0, "tol": PARITY_TOL, "against": "dense fp64 over prefill + appended rows",
               "steps_checked": []}
     q_host = out_host = k_host = v_host = None
@@ -478,7 +478,11 @@ def measure_cfg4(dev, args, passes=1, with_e2e=True):
                     pe0 = ev()
                     pe0.record()
                 q, nk, nv = pre.pop(0)
-                attn.append_token(tokens=[7_000_000 + step] * len(seqs), k=nk, v=nv)
+                toks = [7_000_000 + step] * len(seqs)
+                th0 = time.perf_counter()
+                attn.append_token(tokens=toks, k=nk, v=nv)
+                attn.refresh_kernel_context(False)
+                pipe_host_ms.append((time.perf_counter() - th0) * 1e3)
                 out = attn.forward(q=q)
                 if not pre:
                     pe1 = ev()
@@ -567,6 +571,10 @@ def measure_cfg4(dev, args, passes=1, with_e2e=True):
                                              for k in ("walk_us", "plan_us", "upload_us")} if churn_steps else None},
            "step_minus_forward_us": (statistics.mean(step_ms) - statistics.mean(fwd_ms)) * 1e3,
            "us_per_step_enqueued_back_to_back": statistics.mean(pipe_ms) * 1e3 if pipe_ms else None,
+           "host_us_append_and_update_back_to_back": {
+               "mean": statistics.mean(pipe_host_ms) * 1e3, "median": statistics.median(pipe_host_ms) * 1e3,
+               "mean_at_replace_steps": statistics.mean(pipe_host_ms[i] for i in range(len(pipe_host_ms))
+                                                        if i and i % cfg.churn_every == 0) * 1e3} if pipe_host_ms else None,
            "timing": "us_per_step: every step alone on an idle GPU, so the host's append + work-list update is inside it; "
                      "us_per_step_enqueued_back_to_back: the 16 steps between two replacements enqueued without a host "
                      "wait, as a decoder loop does (one more pass over the trace)",
@@ -1120,7 +1128,8 @@ def run_cfg4(args):
             "gpu_launches": res["steps"] * res["gpu_launches_per_step"]}
     for k in ("parity", "roofline", "e2e", "clocks", "device_status", "forward_us", "forward_us_median",
               "unique_kv_bytes_mean", "hbm_frac", "host_us_append_and_update", "step_minus_forward_us",
-              "us_per_step_enqueued_back_to_back", "timing", "value_median", "value_min", "value_max", "blocks"):
+              "us_per_step_enqueued_back_to_back", "host_us_append_and_update_back_to_back", "timing", "value_median",
+              "value_min", "value_max", "blocks"):
         line[k] = res.get(k)
     if not args.no_cpu_baseline:
         try:
