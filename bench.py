@@ -1074,7 +1074,7 @@ def run_b200(args):
                 line["reference_cuda"] = time_reference_cuda(name, dev, min(K, 100), W_)
             except Exception as exc:  # reported, never a gate
                 line["reference_cuda"] = {"us_per_step": None, "note": "failed: %s" % str(exc)[:200]}
-        if auto and name == "cfg2" and not args.no_other_configs:
+        if auto and not args.no_other_configs:   # also beside the cfg5 point of a series: every configuration in every one-GPU line
             line["other_configs"] = other_configs(dev, args, t_start)
         if not args.no_cpu_baseline and world == 1:
             try:
