@@ -876,6 +876,7 @@ def run_b200(args):
         gather_note = "nccl"
     stats = engine.plan_stats()
     assert stats["unique_kv_bytes"] == ukv_local
+    own_barrier_kernel = world > 1 and attn.gather_mode == "p2p" and attn.barrier_kind == "own"
     step = (lambda: attn.forward(q, gather=True)) if world > 1 else (lambda: attn.forward(q=q))
 
     # ---- parity of the tensor that is timed: sampled rows against dense fp64 from the seeded inputs ------------------
@@ -1044,7 +1045,9 @@ def run_b200(args):
                         "d2h_bytes_per_step": out_host.numel() * 2 * world, "call": e2e_call,
                         "via_forward_and_two_copies_us": e2e_alt},
                 "multi_gpu_breakdown": breakdown,
-                "gpu_launches": K * stats["kernels_per_step"],
+                # this library's kernels per step: the attention kernels, plus its own barrier kernel after the fused gather
+                # (an NCCL all-gather or torch's barrier are library kernels and not counted)
+                "gpu_launches": K * (stats["kernels_per_step"] + (1 if own_barrier_kernel else 0)),
                 "clocks": clocks, "device_status": status}
         line.update(spread_of([b * 1e3 for b in blocks]))
         if single:
